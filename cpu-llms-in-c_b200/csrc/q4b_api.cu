@@ -1,0 +1,735 @@
+// C ABI of libq4b200 (declared in include/q4b200.h): contexts, the weight-image
+// loader, matmul dispatch, completion/timing and graph replay.  Host code only;
+// the kernels live in q4b_pack.cu, q4b_gemv.cu and q4b_gemm.cu.
+#include "../../include/q4b200.h"
+#include "q4b_kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+using namespace q4b;
+
+struct q4b_context {
+    int device;
+    int sm_count;
+    int variant;
+    cudaStream_t stream;
+    cudaEvent_t timer_start, timer_stop;
+    bool timer_armed;
+    bool capturing;
+    uint64_t launches;
+};
+
+struct q4b_weight {
+    WeightView view;
+    uint64_t device_bytes;
+    uint32_t rows_total;  // rows of the source matrix
+    uint32_t row_begin;   // first source row held
+    int device;
+};
+
+struct q4b_graph {
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    uint64_t launches;  // kernels recorded
+};
+
+namespace {
+
+void set_error(char *message, size_t capacity, const char *format, ...) {
+    if (message == nullptr || capacity == 0) return;
+    va_list list;
+    va_start(list, format);
+    vsnprintf(message, capacity, format, list);
+    va_end(list);
+}
+
+int device_failure(char *message, size_t capacity, const char *what, cudaError_t status) {
+    set_error(message, capacity, "%s: %s", what, cudaGetErrorString(status));
+    return Q4B_DEVICE_FAILURE;
+}
+
+#define Q4B_CUDA(call, what)                                                     \
+    do {                                                                         \
+        cudaError_t status_ = (call);                                            \
+        if (status_ != cudaSuccess)                                              \
+            return device_failure(error_message, error_capacity, what, status_); \
+    } while (0)
+
+bool valid_activation_dtype(int dtype) { return dtype == Q4B_F16 || dtype == Q4B_F32; }
+size_t dtype_bytes(int dtype) { return dtype == Q4B_F32 ? 4 : 2; }
+bool aligned16(const void *pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
+
+int check_context(q4b_context *context, char *error_message, size_t error_capacity) {
+    if (context == nullptr) {
+        set_error(error_message, error_capacity, "context is NULL");
+        return Q4B_BAD_ARGUMENT;
+    }
+    cudaError_t status = cudaSetDevice(context->device);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "cudaSetDevice", status);
+    return Q4B_OK;
+}
+
+uint64_t tile_stream_bytes(uint32_t row_count, uint32_t groups) {
+    uint32_t row_tiles = ceil_div(row_count, kTileRows);
+    uint32_t padded = ceil_div(row_tiles, kRowTilePad) * kRowTilePad;
+    return (uint64_t)padded * groups * kTileBytes;
+}
+
+int validate_shape(uint32_t rows, uint32_t groups, uint32_t row_begin, uint32_t row_count,
+                   char *error_message, size_t error_capacity) {
+    if (rows == 0 || groups == 0 || row_count == 0 || row_begin >= rows ||
+        row_count > rows - row_begin) {
+        set_error(error_message, error_capacity,
+                  "invalid weight shape: rows=%u groups_per_row=%u slice=[%u,+%u)", rows, groups,
+                  row_begin, row_count);
+        return Q4B_BAD_ARGUMENT;
+    }
+    if ((uint64_t)groups * kGroup > 0x7fffffffull) {
+        set_error(error_message, error_capacity, "K = %llu is too large",
+                  (unsigned long long)groups * kGroup);
+        return Q4B_BAD_ARGUMENT;
+    }
+    return Q4B_OK;
+}
+
+// device planes -> tile stream in a fresh allocation
+int build_weight(q4b_context *context, const uint8_t *device_quants, const void *device_meta,
+                 const void *device_biases, int meta_dtype, uint32_t rows, uint32_t groups,
+                 uint32_t row_begin, uint32_t row_count, q4b_weight **out, char *error_message,
+                 size_t error_capacity) {
+    uint64_t bytes = tile_stream_bytes(row_count, groups);
+    uint8_t *tiles = nullptr;
+    cudaError_t status = cudaMalloc(&tiles, bytes);
+    if (status != cudaSuccess) {
+        set_error(error_message, error_capacity, "cudaMalloc of %llu bytes for the weight image: %s",
+                  (unsigned long long)bytes, cudaGetErrorString(status));
+        return Q4B_LOAD_FAILURE;
+    }
+    status = launch_repack(device_quants, device_meta, device_biases, meta_dtype, groups, row_begin,
+                           row_count, tiles, context->stream);
+    ++context->launches;
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    if (status != cudaSuccess) {
+        cudaFree(tiles);
+        return device_failure(error_message, error_capacity, "repack", status);
+    }
+    q4b_weight *weight = new (std::nothrow) q4b_weight();
+    if (weight == nullptr) {
+        cudaFree(tiles);
+        set_error(error_message, error_capacity, "out of host memory");
+        return Q4B_LOAD_FAILURE;
+    }
+    weight->view.tiles = tiles;
+    weight->view.rows = row_count;
+    weight->view.groups = groups;
+    weight->view.row_tiles = ceil_div(row_count, kTileRows);
+    weight->device_bytes = bytes;
+    weight->rows_total = rows;
+    weight->row_begin = row_begin;
+    weight->device = context->device;
+    *out = weight;
+    return Q4B_OK;
+}
+
+int upload_common(q4b_context *context, const void *quants, const void *meta, const void *biases,
+                  int meta_dtype, uint32_t rows, uint32_t groups, uint32_t row_begin,
+                  uint32_t row_count, q4b_weight **out, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (out == nullptr || quants == nullptr || meta == nullptr) {
+        set_error(error_message, error_capacity, "NULL segment or output pointer");
+        return Q4B_BAD_ARGUMENT;
+    }
+    *out = nullptr;
+    code = validate_shape(rows, groups, row_begin, row_count, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (context->capturing) {
+        set_error(error_message, error_capacity, "weights cannot be loaded while recording a graph");
+        return Q4B_BAD_ARGUMENT;
+    }
+    // only the slice's bytes cross PCIe
+    const size_t quant_bytes = (size_t)row_count * groups * 32;
+    const size_t record_bytes = biases == nullptr ? 4 : 2;
+    const size_t meta_bytes = (size_t)row_count * groups * record_bytes;
+    const uint8_t *host_quants = static_cast<const uint8_t *>(quants) + (size_t)row_begin * groups * 32;
+    const uint8_t *host_meta = static_cast<const uint8_t *>(meta) + (size_t)row_begin * groups * record_bytes;
+    uint8_t *staging = nullptr;
+    cudaError_t status = cudaMalloc(&staging, quant_bytes + 2 * meta_bytes + 64);
+    if (status != cudaSuccess) {
+        set_error(error_message, error_capacity, "cudaMalloc of upload staging: %s", cudaGetErrorString(status));
+        return Q4B_LOAD_FAILURE;
+    }
+    uint8_t *device_quants = staging;
+    uint8_t *device_meta = staging + ((quant_bytes + 15) & ~(size_t)15);
+    uint8_t *device_biases = biases == nullptr ? nullptr : device_meta + ((meta_bytes + 15) & ~(size_t)15);
+    status = cudaMemcpyAsync(device_quants, host_quants, quant_bytes, cudaMemcpyHostToDevice, context->stream);
+    if (status == cudaSuccess)
+        status = cudaMemcpyAsync(device_meta, host_meta, meta_bytes, cudaMemcpyHostToDevice, context->stream);
+    if (status == cudaSuccess && biases != nullptr) {
+        const uint8_t *host_biases = static_cast<const uint8_t *>(biases) + (size_t)row_begin * groups * 2;
+        status = cudaMemcpyAsync(device_biases, host_biases, meta_bytes, cudaMemcpyHostToDevice, context->stream);
+    }
+    if (status != cudaSuccess) {
+        cudaFree(staging);
+        return device_failure(error_message, error_capacity, "upload copy", status);
+    }
+    code = build_weight(context, device_quants, device_meta, device_biases, meta_dtype, rows, groups,
+                        0, row_count, out, error_message, error_capacity);
+    cudaFree(staging);
+    if (code == Q4B_OK) {
+        (*out)->row_begin = row_begin;
+    }
+    return code;
+}
+
+int check_matmul_arguments(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
+                           uint32_t m_rows, const void *y, int y_dtype, uint32_t ldy,
+                           char *error_message, size_t error_capacity) {
+    if (weight == nullptr || x == nullptr || y == nullptr) {
+        set_error(error_message, error_capacity, "NULL weight, x or y");
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (weight->device != context->device) {
+        set_error(error_message, error_capacity, "weight lives on device %d, context on %d",
+                  weight->device, context->device);
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (m_rows == 0) {
+        set_error(error_message, error_capacity, "batch_rows is 0");
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (!valid_activation_dtype(x_dtype) || !valid_activation_dtype(y_dtype)) {
+        set_error(error_message, error_capacity, "x and y must be fp16 or fp32");
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (ldy < weight->view.rows) {
+        set_error(error_message, error_capacity, "ldy=%u is smaller than the %u rows of the shard", ldy,
+                  weight->view.rows);
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (!aligned16(x)) {
+        set_error(error_message, error_capacity, "x must be 16-byte aligned");
+        return Q4B_BAD_ARGUMENT;
+    }
+    return Q4B_OK;
+}
+
+// one launch sequence for any M: GEMV kernel up to its row limit, row blocks above
+int run_projection(q4b_context *context, GemvArgs args, char *error_message, size_t error_capacity) {
+    const uint32_t limit = gemv_max_m();
+    const uint32_t total = args.m_rows;
+    const size_t K = (size_t)args.w[0].groups * kGroup;
+    for (uint32_t m0 = 0; m0 < total; m0 += limit) {
+        GemvArgs block = args;
+        block.m_rows = total - m0 < limit ? total - m0 : limit;
+        block.x = static_cast<const uint8_t *>(args.x) + (size_t)m0 * K * dtype_bytes(args.x_dtype);
+        for (int s = 0; s < args.segments; ++s) {
+            block.y[s] = static_cast<uint8_t *>(args.y[s]) + (size_t)m0 * args.ldy[s] * dtype_bytes(args.y_dtype);
+        }
+        if (args.residual != nullptr) {
+            block.residual = static_cast<const uint8_t *>(args.residual) +
+                             (size_t)m0 * args.ld_residual * dtype_bytes(args.residual_dtype);
+        }
+        cudaError_t status = launch_gemv(block, context->variant, context->sm_count, context->stream);
+        if (!context->capturing) ++context->launches;  // recorded launches count at replay
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv launch", status);
+    }
+    return Q4B_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int q4b_device_count(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) return 0;
+    return count;
+}
+
+q4b_context *q4b_context_open(int device, char *error_message, size_t error_capacity) {
+    int count = 0;
+    cudaError_t status = cudaGetDeviceCount(&count);
+    if (status != cudaSuccess || count == 0) {
+        set_error(error_message, error_capacity, "no CUDA device: %s (this library has no CPU path)",
+                  status != cudaSuccess ? cudaGetErrorString(status) : "device count is 0");
+        return nullptr;
+    }
+    if (device < 0 || device >= count) {
+        set_error(error_message, error_capacity, "device %d out of range (0..%d)", device, count - 1);
+        return nullptr;
+    }
+    cudaDeviceProp properties;
+    status = cudaGetDeviceProperties(&properties, device);
+    if (status != cudaSuccess) {
+        set_error(error_message, error_capacity, "cudaGetDeviceProperties: %s", cudaGetErrorString(status));
+        return nullptr;
+    }
+    if (properties.major != 10) {
+        set_error(error_message, error_capacity,
+                  "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                  properties.major, properties.minor);
+        return nullptr;
+    }
+    q4b_context *context = new (std::nothrow) q4b_context();
+    if (context == nullptr) {
+        set_error(error_message, error_capacity, "out of host memory");
+        return nullptr;
+    }
+    context->device = device;
+    context->sm_count = properties.multiProcessorCount;
+    const char *variant = getenv("Q4B_VARIANT");
+    context->variant = variant != nullptr ? (int)strtol(variant, nullptr, 0) : 0;
+    if ((status = cudaSetDevice(device)) != cudaSuccess ||
+        (status = cudaStreamCreateWithFlags(&context->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (status = cudaEventCreate(&context->timer_start)) != cudaSuccess ||
+        (status = cudaEventCreate(&context->timer_stop)) != cudaSuccess) {
+        set_error(error_message, error_capacity, "context setup: %s", cudaGetErrorString(status));
+        delete context;
+        return nullptr;
+    }
+    return context;
+}
+
+void q4b_context_close(q4b_context *context) {
+    if (context == nullptr) return;
+    cudaSetDevice(context->device);
+    cudaStreamSynchronize(context->stream);
+    cudaEventDestroy(context->timer_start);
+    cudaEventDestroy(context->timer_stop);
+    cudaStreamDestroy(context->stream);
+    delete context;
+}
+
+void *q4b_context_stream(q4b_context *context) { return context != nullptr ? context->stream : nullptr; }
+void q4b_context_set_variant(q4b_context *context, int variant) {
+    if (context != nullptr) context->variant = variant;
+}
+uint64_t q4b_context_launch_count(const q4b_context *context) {
+    return context != nullptr ? context->launches : 0;
+}
+
+int q4b_alloc(q4b_context *context, size_t bytes, void **device_pointer, char *error_message,
+              size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (device_pointer == nullptr) return Q4B_BAD_ARGUMENT;
+    Q4B_CUDA(cudaMalloc(device_pointer, bytes > 0 ? bytes : 1), "cudaMalloc");
+    return Q4B_OK;
+}
+int q4b_free(q4b_context *context, void *device_pointer) {
+    if (context != nullptr) cudaSetDevice(context->device);
+    return cudaFree(device_pointer) == cudaSuccess ? Q4B_OK : Q4B_DEVICE_FAILURE;
+}
+int q4b_alloc_host(q4b_context *context, size_t bytes, void **pinned_host_pointer, char *error_message,
+                   size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (pinned_host_pointer == nullptr) return Q4B_BAD_ARGUMENT;
+    Q4B_CUDA(cudaMallocHost(pinned_host_pointer, bytes > 0 ? bytes : 1), "cudaMallocHost");
+    return Q4B_OK;
+}
+int q4b_free_host(q4b_context *context, void *pinned_host_pointer) {
+    if (context != nullptr) cudaSetDevice(context->device);
+    return cudaFreeHost(pinned_host_pointer) == cudaSuccess ? Q4B_OK : Q4B_DEVICE_FAILURE;
+}
+int q4b_copy_to_device(q4b_context *context, void *device_destination, const void *host_source,
+                       size_t bytes, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    Q4B_CUDA(cudaMemcpyAsync(device_destination, host_source, bytes, cudaMemcpyHostToDevice, context->stream),
+             "copy to device");
+    return Q4B_OK;
+}
+int q4b_copy_to_host(q4b_context *context, void *host_destination, const void *device_source, size_t bytes,
+                     char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    Q4B_CUDA(cudaMemcpyAsync(host_destination, device_source, bytes, cudaMemcpyDeviceToHost, context->stream),
+             "copy to host");
+    return Q4B_OK;
+}
+
+int q4b_weight_upload(q4b_context *context, const void *quants, const void *meta, uint32_t rows,
+                      uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                      q4b_weight **weight, char *error_message, size_t error_capacity) {
+    return upload_common(context, quants, meta, nullptr, Q4B_F16, rows, groups_per_row, row_begin,
+                         row_count, weight, error_message, error_capacity);
+}
+
+int q4b_weight_upload_planes(q4b_context *context, const void *quants, const void *scales,
+                             const void *biases, int meta_dtype, uint32_t rows, uint32_t groups_per_row,
+                             uint32_t row_begin, uint32_t row_count, q4b_weight **weight,
+                             char *error_message, size_t error_capacity) {
+    if (biases == nullptr || (meta_dtype != Q4B_F16 && meta_dtype != Q4B_BF16)) {
+        set_error(error_message, error_capacity, "scale/bias planes must be fp16 or bf16 and non-NULL");
+        return Q4B_BAD_ARGUMENT;
+    }
+    return upload_common(context, quants, scales, biases, meta_dtype, rows, groups_per_row, row_begin,
+                         row_count, weight, error_message, error_capacity);
+}
+
+int q4b_weight_from_device(q4b_context *context, const void *device_quants, const void *device_meta,
+                           uint32_t rows, uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                           q4b_weight **weight, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weight == nullptr || device_quants == nullptr || device_meta == nullptr) {
+        set_error(error_message, error_capacity, "NULL segment or output pointer");
+        return Q4B_BAD_ARGUMENT;
+    }
+    *weight = nullptr;
+    code = validate_shape(rows, groups_per_row, row_begin, row_count, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (!aligned16(device_quants) || (reinterpret_cast<uintptr_t>(device_meta) & 3u) != 0) {
+        set_error(error_message, error_capacity, "device segments must be 16-byte (quants) / 4-byte (meta) aligned");
+        return Q4B_BAD_ARGUMENT;
+    }
+    return build_weight(context, static_cast<const uint8_t *>(device_quants), device_meta, nullptr, Q4B_F16,
+                        rows, groups_per_row, row_begin, row_count, weight, error_message, error_capacity);
+}
+
+int q4b_weight_synth(q4b_context *context, uint64_t seed, uint32_t projection, uint32_t rows,
+                     uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count, q4b_weight **weight,
+                     char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weight == nullptr) return Q4B_BAD_ARGUMENT;
+    *weight = nullptr;
+    code = validate_shape(rows, groups_per_row, row_begin, row_count, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    // generate only the slice, in the reference image layout, then load it
+    const uint64_t words = (uint64_t)row_count * groups_per_row * 8;
+    const uint64_t groups = (uint64_t)row_count * groups_per_row;
+    uint8_t *staging = nullptr;
+    cudaError_t status = cudaMalloc(&staging, words * 4 + groups * 4);
+    if (status != cudaSuccess) {
+        set_error(error_message, error_capacity, "cudaMalloc of synthesis staging: %s", cudaGetErrorString(status));
+        return Q4B_LOAD_FAILURE;
+    }
+    uint32_t *device_words = reinterpret_cast<uint32_t *>(staging);
+    __half *device_meta = reinterpret_cast<__half *>(staging + words * 4);
+    status = launch_synth_codes(seed, 1 + 2ull * projection, device_words,
+                                (uint64_t)row_begin * groups_per_row * 8, words, context->stream);
+    if (status == cudaSuccess)
+        status = launch_synth_meta(seed, 2 + 2ull * projection, device_meta,
+                                   (uint64_t)row_begin * groups_per_row, groups, context->stream);
+    context->launches += 2;
+    if (status != cudaSuccess) {
+        cudaFree(staging);
+        return device_failure(error_message, error_capacity, "synthesis", status);
+    }
+    code = build_weight(context, staging, device_meta, nullptr, Q4B_F16, rows, groups_per_row, 0, row_count,
+                        weight, error_message, error_capacity);
+    cudaFree(staging);
+    if (code == Q4B_OK) (*weight)->row_begin = row_begin;
+    return code;
+}
+
+int q4b_synth_x(q4b_context *context, uint64_t seed, uint64_t stream_id, void *device_x_f16, uint64_t begin,
+                uint64_t count, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (device_x_f16 == nullptr) return Q4B_BAD_ARGUMENT;
+    Q4B_CUDA(launch_synth_x(seed, stream_id, static_cast<__half *>(device_x_f16), begin, count, context->stream),
+             "synthesis of x");
+    ++context->launches;
+    return Q4B_OK;
+}
+
+void q4b_weight_free(q4b_context *context, q4b_weight *weight) {
+    if (weight == nullptr) return;
+    if (context != nullptr) {
+        cudaSetDevice(context->device);
+        cudaStreamSynchronize(context->stream);
+    }
+    cudaFree(const_cast<uint8_t *>(weight->view.tiles));
+    delete weight;
+}
+
+int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_per_row,
+                    uint64_t *device_bytes) {
+    if (weight == nullptr) return Q4B_BAD_ARGUMENT;
+    if (rows != nullptr) *rows = weight->view.rows;
+    if (groups_per_row != nullptr) *groups_per_row = weight->view.groups;
+    if (device_bytes != nullptr) *device_bytes = weight->device_bytes;
+    return Q4B_OK;
+}
+
+int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *codes, float *w32,
+                      uint16_t *w16, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weight == nullptr) {
+        set_error(error_message, error_capacity, "weight is NULL");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const size_t elements = (size_t)weight->view.rows * weight->view.groups * kGroup;
+    uint8_t *device_codes = nullptr;
+    float *device_w32 = nullptr;
+    __half *device_w16 = nullptr;
+    cudaError_t status = cudaSuccess;
+    if (codes != nullptr) status = cudaMalloc(&device_codes, elements);
+    if (status == cudaSuccess && w32 != nullptr) status = cudaMalloc(&device_w32, elements * 4);
+    if (status == cudaSuccess && w16 != nullptr) status = cudaMalloc(&device_w16, elements * 2);
+    if (status == cudaSuccess) {
+        status = launch_unpack(weight->view, device_codes, device_w32, device_w16, context->stream);
+        ++context->launches;
+    }
+    if (status == cudaSuccess && codes != nullptr)
+        status = cudaMemcpyAsync(codes, device_codes, elements, cudaMemcpyDeviceToHost, context->stream);
+    if (status == cudaSuccess && w32 != nullptr)
+        status = cudaMemcpyAsync(w32, device_w32, elements * 4, cudaMemcpyDeviceToHost, context->stream);
+    if (status == cudaSuccess && w16 != nullptr)
+        status = cudaMemcpyAsync(w16, device_w16, elements * 2, cudaMemcpyDeviceToHost, context->stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    cudaFree(device_codes);
+    cudaFree(device_w32);
+    cudaFree(device_w16);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "unpack", status);
+    return Q4B_OK;
+}
+
+int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype, uint32_t m_rows,
+               void *y, int y_dtype, uint32_t ldy, const void *residual, int residual_dtype,
+               uint32_t ld_residual, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    code = check_matmul_arguments(context, weight, x, x_dtype, m_rows, y, y_dtype, ldy, error_message,
+                                  error_capacity);
+    if (code != Q4B_OK) return code;
+    if (residual != nullptr && (!valid_activation_dtype(residual_dtype) || ld_residual < weight->view.rows)) {
+        set_error(error_message, error_capacity, "residual must be fp16 or fp32 with ld >= rows");
+        return Q4B_BAD_ARGUMENT;
+    }
+    GemvArgs args = {};
+    args.w[0] = weight->view;
+    args.y[0] = y;
+    args.ldy[0] = ldy;
+    args.segments = 1;
+    args.x = x;
+    args.x_dtype = x_dtype;
+    args.m_rows = m_rows;
+    args.y_dtype = y_dtype;
+    args.residual = residual;
+    args.residual_dtype = residual != nullptr ? residual_dtype : (int)kNone;
+    args.ld_residual = ld_residual;
+    return run_projection(context, args, error_message, error_capacity);
+}
+
+int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int count, const void *x,
+                     int x_dtype, uint32_t m_rows, void *const *y, int y_dtype, const uint32_t *ldy,
+                     char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weights == nullptr || y == nullptr || ldy == nullptr || count < 1 || count > kMaxSegments) {
+        set_error(error_message, error_capacity, "a group holds 1..%d matrices", kMaxSegments);
+        return Q4B_BAD_ARGUMENT;
+    }
+    GemvArgs args = {};
+    for (int s = 0; s < count; ++s) {
+        code = check_matmul_arguments(context, weights[s], x, x_dtype, m_rows, y[s], y_dtype, ldy[s],
+                                      error_message, error_capacity);
+        if (code != Q4B_OK) return code;
+        if (weights[s]->view.groups != weights[0]->view.groups) {
+            set_error(error_message, error_capacity, "matrices of a group must share K");
+            return Q4B_BAD_ARGUMENT;
+        }
+        args.w[s] = weights[s]->view;
+        args.y[s] = y[s];
+        args.ldy[s] = ldy[s];
+    }
+    args.segments = count;
+    args.x = x;
+    args.x_dtype = x_dtype;
+    args.m_rows = m_rows;
+    args.y_dtype = y_dtype;
+    args.residual_dtype = kNone;
+    return run_projection(context, args, error_message, error_capacity);
+}
+
+int q4b_gate_up_silu(q4b_context *context, const q4b_weight *gate, const q4b_weight *up, const void *x,
+                     int x_dtype, uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, char *error_message,
+                     size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    code = check_matmul_arguments(context, gate, x, x_dtype, m_rows, y, y_dtype, ldy, error_message,
+                                  error_capacity);
+    if (code != Q4B_OK) return code;
+    if (up == nullptr || up->device != gate->device || up->view.rows != gate->view.rows ||
+        up->view.groups != gate->view.groups) {
+        set_error(error_message, error_capacity, "gate and up must have the same shape and device");
+        return Q4B_BAD_ARGUMENT;
+    }
+    GemvArgs args = {};
+    args.w[0] = gate->view;
+    args.up = up->view;
+    args.fused_silu = 1;
+    args.y[0] = y;
+    args.ldy[0] = ldy;
+    args.segments = 1;
+    args.x = x;
+    args.x_dtype = x_dtype;
+    args.m_rows = m_rows;
+    args.y_dtype = y_dtype;
+    args.residual_dtype = kNone;
+    return run_projection(context, args, error_message, error_capacity);
+}
+
+static int host_call(q4b_context *context, const q4b_weight *gate, const q4b_weight *up, const void *x_host,
+                     int x_dtype, uint32_t m_rows, void *y_host, int y_dtype, double *gpu_ms,
+                     char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (gate == nullptr || x_host == nullptr || y_host == nullptr || m_rows == 0 ||
+        !valid_activation_dtype(x_dtype) || !valid_activation_dtype(y_dtype)) {
+        set_error(error_message, error_capacity, "invalid projection");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const size_t K = (size_t)gate->view.groups * kGroup, N = gate->view.rows;
+    const size_t x_bytes = (size_t)m_rows * K * dtype_bytes(x_dtype);
+    const size_t y_bytes = (size_t)m_rows * N * dtype_bytes(y_dtype);
+    uint8_t *device = nullptr;
+    const size_t x_padded = (x_bytes + 255) & ~(size_t)255;
+    Q4B_CUDA(cudaMalloc(&device, x_padded + y_bytes), "cudaMalloc of call buffers");
+    cudaError_t status = cudaMemcpyAsync(device, x_host, x_bytes, cudaMemcpyHostToDevice, context->stream);
+    cudaEvent_t start = nullptr, stop = nullptr;
+    if (status == cudaSuccess) status = cudaEventCreate(&start);
+    if (status == cudaSuccess) status = cudaEventCreate(&stop);
+    if (status == cudaSuccess) status = cudaEventRecord(start, context->stream);
+    if (status == cudaSuccess) {
+        if (up != nullptr) {
+            code = q4b_gate_up_silu(context, gate, up, device, x_dtype, m_rows, device + x_padded, y_dtype,
+                                    (uint32_t)N, error_message, error_capacity);
+        } else {
+            code = q4b_matmul(context, gate, device, x_dtype, m_rows, device + x_padded, y_dtype, (uint32_t)N,
+                              nullptr, Q4B_NONE, 0, error_message, error_capacity);
+        }
+    }
+    if (status == cudaSuccess && code == Q4B_OK) status = cudaEventRecord(stop, context->stream);
+    if (status == cudaSuccess && code == Q4B_OK)
+        status = cudaMemcpyAsync(y_host, device + x_padded, y_bytes, cudaMemcpyDeviceToHost, context->stream);
+    if (status == cudaSuccess && code == Q4B_OK) status = cudaStreamSynchronize(context->stream);
+    if (status == cudaSuccess && code == Q4B_OK && gpu_ms != nullptr) {
+        float ms = 0.0f;
+        status = cudaEventElapsedTime(&ms, start, stop);
+        *gpu_ms = ms;
+    }
+    if (start != nullptr) cudaEventDestroy(start);
+    if (stop != nullptr) cudaEventDestroy(stop);
+    cudaFree(device);
+    if (code != Q4B_OK) return code;
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "projection", status);
+    return Q4B_OK;
+}
+
+int q4b_matmul_host(q4b_context *context, const q4b_weight *weight, const void *x_host, int x_dtype,
+                    uint32_t m_rows, void *y_host, int y_dtype, double *gpu_ms, char *error_message,
+                    size_t error_capacity) {
+    return host_call(context, weight, nullptr, x_host, x_dtype, m_rows, y_host, y_dtype, gpu_ms,
+                     error_message, error_capacity);
+}
+
+int q4b_gate_up_silu_host(q4b_context *context, const q4b_weight *gate, const q4b_weight *up,
+                          const void *x_host, int x_dtype, uint32_t m_rows, void *y_host, int y_dtype,
+                          double *gpu_ms, char *error_message, size_t error_capacity) {
+    if (up == nullptr) {
+        set_error(error_message, error_capacity, "invalid projection");
+        return Q4B_BAD_ARGUMENT;
+    }
+    return host_call(context, gate, up, x_host, x_dtype, m_rows, y_host, y_dtype, gpu_ms, error_message,
+                     error_capacity);
+}
+
+int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    Q4B_CUDA(cudaEventRecord(context->timer_start, context->stream), "timer start");
+    context->timer_armed = true;
+    return Q4B_OK;
+}
+
+int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (device_ms != nullptr && context->timer_armed) {
+        Q4B_CUDA(cudaEventRecord(context->timer_stop, context->stream), "timer stop");
+    }
+    Q4B_CUDA(cudaStreamSynchronize(context->stream), "stream synchronize");
+    Q4B_CUDA(cudaGetLastError(), "asynchronous error");
+    if (device_ms != nullptr) {
+        *device_ms = 0.0;
+        if (context->timer_armed) {
+            float ms = 0.0f;
+            Q4B_CUDA(cudaEventElapsedTime(&ms, context->timer_start, context->timer_stop), "timer read");
+            *device_ms = ms;
+        }
+    }
+    return Q4B_OK;
+}
+
+int q4b_graph_begin(q4b_context *context, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (context->capturing) {
+        set_error(error_message, error_capacity, "already recording");
+        return Q4B_BAD_ARGUMENT;
+    }
+    Q4B_CUDA(cudaStreamBeginCapture(context->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
+    context->capturing = true;
+    return Q4B_OK;
+}
+
+int q4b_graph_end(q4b_context *context, q4b_graph **graph, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (!context->capturing || graph == nullptr) {
+        set_error(error_message, error_capacity, "not recording");
+        return Q4B_BAD_ARGUMENT;
+    }
+    context->capturing = false;
+    cudaGraph_t captured = nullptr;
+    Q4B_CUDA(cudaStreamEndCapture(context->stream, &captured), "end capture");
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t status = cudaGraphInstantiate(&exec, captured, 0);
+    if (status != cudaSuccess) {
+        cudaGraphDestroy(captured);
+        return device_failure(error_message, error_capacity, "graph instantiate", status);
+    }
+    size_t nodes = 0;
+    cudaGraphGetNodes(captured, nullptr, &nodes);
+    q4b_graph *result = new (std::nothrow) q4b_graph();
+    if (result == nullptr) {
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(captured);
+        set_error(error_message, error_capacity, "out of host memory");
+        return Q4B_DEVICE_FAILURE;
+    }
+    result->graph = captured;
+    result->exec = exec;
+    result->launches = nodes;
+    *graph = result;
+    return Q4B_OK;
+}
+
+int q4b_graph_launch(q4b_context *context, q4b_graph *graph, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (graph == nullptr) return Q4B_BAD_ARGUMENT;
+    Q4B_CUDA(cudaGraphLaunch(graph->exec, context->stream), "graph launch");
+    context->launches += graph->launches;
+    return Q4B_OK;
+}
+
+void q4b_graph_free(q4b_graph *graph) {
+    if (graph == nullptr) return;
+    cudaGraphExecDestroy(graph->exec);
+    cudaGraphDestroy(graph->graph);
+    delete graph;
+}
+
+}  // extern "C"

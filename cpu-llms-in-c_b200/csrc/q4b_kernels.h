@@ -1,0 +1,48 @@
+// Host-side launchers of the CUDA kernels (internal to the library).
+#pragma once
+#include "q4b_common.cuh"
+
+namespace q4b {
+
+// ---- q4b_pack.cu ----
+// raw image planes (device) -> tile stream.  rows_total/groups describe the
+// source matrix; rows [row_begin, row_begin+row_count) are packed.  meta is
+// interleaved fp16 {scale,bias} when biases == nullptr, else `meta` is the
+// scale plane and `biases` the bias plane (fp16 or bf16 by meta_dtype).
+cudaError_t launch_repack(const uint8_t *quants, const void *meta, const void *biases,
+                          int meta_dtype, uint32_t groups, uint32_t row_begin,
+                          uint32_t row_count, uint8_t *tiles, cudaStream_t stream);
+// tile stream -> codes u8 [rows][K], w32 [rows][K], w16 [rows][K] (any may be null)
+cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
+                          cudaStream_t stream);
+cudaError_t launch_synth_codes(uint64_t seed, uint64_t stream_id, uint32_t *words,
+                               uint64_t word_begin, uint64_t word_count, cudaStream_t stream);
+cudaError_t launch_synth_meta(uint64_t seed, uint64_t stream_id, __half *meta,
+                              uint64_t group_begin, uint64_t group_count, cudaStream_t stream);
+cudaError_t launch_synth_x(uint64_t seed, uint64_t stream_id, __half *x, uint64_t begin,
+                           uint64_t count, cudaStream_t stream);
+
+// ---- q4b_gemv.cu ----
+constexpr int kMaxSegments = 4;
+struct GemvArgs {
+    // up to kMaxSegments matrices that share x (same K); fused gate/up uses
+    // segment 0 = gate, `up` = the second matrix, one output
+    WeightView w[kMaxSegments];
+    void *y[kMaxSegments];
+    uint32_t ldy[kMaxSegments];
+    int segments;
+    WeightView up;       // valid when fused_silu
+    int fused_silu;
+    const void *x;       // [M][K]
+    int x_dtype;         // kF16 / kF32
+    uint32_t m_rows;
+    int y_dtype;         // kF16 / kF32
+    const void *residual;  // [M][ld_residual] or null (segment 0 only)
+    int residual_dtype;
+    uint32_t ld_residual;
+};
+// variant: 0 = default; other values select alternatives for A/B measurements
+cudaError_t launch_gemv(const GemvArgs &args, int variant, int sm_count, cudaStream_t stream);
+uint32_t gemv_max_m();
+
+}  // namespace q4b

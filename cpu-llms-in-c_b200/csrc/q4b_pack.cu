@@ -1,0 +1,235 @@
+// Image loader kernels: raw reference planes -> tile stream, its inverse
+// (the dequantisation-in-isolation hook, cf. qwen38_global.metal:13-28), and the
+// seeded synthetic generator.
+#include "q4b_kernels.h"
+
+namespace q4b {
+
+__device__ inline uint16_t meta_to_f16_bits(const void *plane, int dtype, size_t index) {
+    uint16_t bits = reinterpret_cast<const uint16_t *>(plane)[index];
+    if (dtype == kBF16) {
+        // BF16 plane -> fp16 record: widen, round once to nearest even
+        // (compiler/qwen3.8-27b/apple-m3-pro/qwen38_m3_pack.c:173-178)
+        float value = __uint_as_float((uint32_t)bits << 16);
+        return __half_as_ushort(__float2half_rn(value));
+    }
+    return bits;
+}
+
+// one thread per (tile, lane); lanes 0..7 also write the metadata records
+__global__ void __launch_bounds__(256)
+repack_kernel(const uint8_t *__restrict__ quants, const void *__restrict__ meta,
+              const void *__restrict__ biases, int meta_dtype, uint32_t groups,
+              uint32_t row_begin, uint32_t row_count, uint32_t padded_row_tiles,
+              uint8_t *__restrict__ tiles) {
+    uint64_t thread = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint64_t tile = thread >> 5;
+    uint32_t lane = thread & 31u;
+    if (tile >= (uint64_t)padded_row_tiles * groups) {
+        return;
+    }
+    uint32_t rt = (uint32_t)(tile / groups);
+    uint32_t g = (uint32_t)(tile % groups);
+    uint32_t gid = lane >> 2, t = lane & 3u;
+    uint32_t local_lo = rt * 16 + gid, local_hi = local_lo + 8;
+    uint64_t piece_lo = 0, piece_hi = 0;
+    if (local_lo < row_count) {
+        size_t byte = ((size_t)(row_begin + local_lo) * groups + g) * 32 + 8 * t;
+        piece_lo = *reinterpret_cast<const uint64_t *>(quants + byte);
+    }
+    if (local_hi < row_count) {
+        size_t byte = ((size_t)(row_begin + local_hi) * groups + g) * 32 + 8 * t;
+        piece_hi = *reinterpret_cast<const uint64_t *>(quants + byte);
+    }
+    uint8_t *out = tiles + tile * kTileBytes;
+    reinterpret_cast<uint4 *>(out)[lane] = swizzle_lane(piece_lo, piece_hi);
+    if (lane < 8) {
+        uint16_t record[4] = {0, 0, 0, 0};
+        uint32_t rows[2] = {rt * 16 + lane, rt * 16 + lane + 8};
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if (rows[half] < row_count) {
+                size_t block = (size_t)(row_begin + rows[half]) * groups + g;
+                if (biases == nullptr) {
+                    record[2 * half] = meta_to_f16_bits(meta, kF16, 2 * block);
+                    record[2 * half + 1] = meta_to_f16_bits(meta, kF16, 2 * block + 1);
+                } else {
+                    record[2 * half] = meta_to_f16_bits(meta, meta_dtype, block);
+                    record[2 * half + 1] = meta_to_f16_bits(biases, meta_dtype, block);
+                }
+            }
+        }
+        uint2 packed = make_uint2(record[0] | ((uint32_t)record[1] << 16),
+                                  record[2] | ((uint32_t)record[3] << 16));
+        reinterpret_cast<uint2 *>(out + kTileCodeBytes)[lane] = packed;
+    }
+}
+
+cudaError_t launch_repack(const uint8_t *quants, const void *meta, const void *biases,
+                          int meta_dtype, uint32_t groups, uint32_t row_begin,
+                          uint32_t row_count, uint8_t *tiles, cudaStream_t stream) {
+    uint32_t row_tiles = ceil_div(row_count, kTileRows);
+    uint32_t padded = ceil_div(row_tiles, kRowTilePad) * kRowTilePad;
+    uint64_t threads = (uint64_t)padded * groups * 32;
+    if (threads == 0) {
+        return cudaSuccess;
+    }
+    uint64_t blocks = (threads + 255) / 256;
+    repack_kernel<<<(unsigned)blocks, 256, 0, stream>>>(quants, meta, biases, meta_dtype,
+                                                         groups, row_begin, row_count, padded,
+                                                         tiles);
+    return cudaGetLastError();
+}
+
+// one thread per (tile, lane): 2 rows x 16 columns
+__global__ void __launch_bounds__(256)
+unpack_kernel(WeightView w, uint8_t *__restrict__ codes, float *__restrict__ w32,
+              __half *__restrict__ w16) {
+    uint64_t thread = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint64_t tile = thread >> 5;
+    uint32_t lane = thread & 31u;
+    if (tile >= (uint64_t)w.row_tiles * w.groups) {
+        return;
+    }
+    uint32_t rt = (uint32_t)(tile / w.groups);
+    uint32_t g = (uint32_t)(tile % w.groups);
+    uint32_t gid = lane >> 2, t = lane & 3u;
+    const uint8_t *in = w.tiles + tile * kTileBytes;
+    uint4 words = reinterpret_cast<const uint4 *>(in)[lane];
+    uint2 record = reinterpret_cast<const uint2 *>(in + kTileCodeBytes)[gid];
+    const uint32_t word[4] = {words.x, words.y, words.z, words.w};
+    size_t columns = (size_t)w.groups * kGroup;
+    uint32_t row[2] = {rt * 16 + gid, rt * 16 + gid + 8};
+    __half2 meta16[2] = {*reinterpret_cast<__half2 *>(&record.x),
+                         *reinterpret_cast<__half2 *>(&record.y)};
+    if (codes != nullptr) {
+        uint64_t piece[2];
+        unswizzle_lane(words, piece[0], piece[1]);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if (row[half] < w.rows) {
+                uint8_t *out = codes + (size_t)row[half] * columns + g * kGroup + 16 * t;
+                uint32_t bytes[4];
+#pragma unroll
+                for (int quad = 0; quad < 4; ++quad) {
+                    uint32_t nibbles = (uint32_t)(piece[half] >> (16 * quad)) & 0xffffu;
+                    bytes[quad] = (nibbles & 0xfu) | ((nibbles & 0xf0u) << 4) |
+                                  ((nibbles & 0xf00u) << 8) | ((nibbles & 0xf000u) << 12);
+                }
+                *reinterpret_cast<uint4 *>(out) = make_uint4(bytes[0], bytes[1], bytes[2], bytes[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 regs[4];
+        word_to_codes_f16(word[i], regs);  // the same extraction the matmul kernels use
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if (row[half] >= w.rows) {
+                continue;
+            }
+            size_t base = (size_t)row[half] * columns + g * kGroup + 16 * t + 4 * i;
+            __half2 scale = __half2half2(__low2half(meta16[half]));
+            __half2 bias = __half2half2(__high2half(meta16[half]));
+            __half2 pair01 = regs[half], pair23 = regs[2 + half];
+            if (w16 != nullptr) {
+                __half2 out01 = dequant_w16(pair01, scale, bias);
+                __half2 out23 = dequant_w16(pair23, scale, bias);
+                uint2 packed = make_uint2(*reinterpret_cast<uint32_t *>(&out01),
+                                          *reinterpret_cast<uint32_t *>(&out23));
+                *reinterpret_cast<uint2 *>(w16 + base) = packed;
+            }
+            if (w32 != nullptr) {
+                float s = __low2float(meta16[half]), b = __high2float(meta16[half]);
+                float4 out;
+                out.x = dequant_w32((uint32_t)__half2float(__low2half(pair01)), s, b);
+                out.y = dequant_w32((uint32_t)__half2float(__high2half(pair01)), s, b);
+                out.z = dequant_w32((uint32_t)__half2float(__low2half(pair23)), s, b);
+                out.w = dequant_w32((uint32_t)__half2float(__high2half(pair23)), s, b);
+                *reinterpret_cast<float4 *>(w32 + base) = out;
+            }
+        }
+    }
+}
+
+cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
+                          cudaStream_t stream) {
+    uint64_t threads = (uint64_t)w.row_tiles * w.groups * 32;
+    if (threads == 0) {
+        return cudaSuccess;
+    }
+    uint64_t blocks = (threads + 255) / 256;
+    unpack_kernel<<<(unsigned)blocks, 256, 0, stream>>>(w, codes, w32, w16);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// seeded generator
+// ---------------------------------------------------------------------------
+__global__ void synth_codes_kernel(uint64_t key, uint32_t *words, uint64_t word_begin,
+                                   uint64_t word_count) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t offset = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+         offset < word_count; offset += stride) {
+        uint64_t word = word_begin + offset;
+        uint64_t bits = keyed(key, word >> 1);
+        words[offset] = (uint32_t)(bits >> (32u * (word & 1u)));
+    }
+}
+
+__global__ void synth_meta_kernel(uint64_t key, __half *meta, uint64_t group_begin,
+                                  uint64_t group_count) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t offset = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+         offset < group_count; offset += stride) {
+        uint64_t group = group_begin + offset;
+        float uniform = (float)(keyed(key, 4ull * group) >> 40) * (1.0f / 16777216.0f);
+        __half scale = __float2half_rn(__fmaf_rn(uniform, 3.5e-3f, 5.0e-4f));
+        float noise = normal12(keyed(key, 4ull * group + 1), keyed(key, 4ull * group + 2),
+                               keyed(key, 4ull * group + 3));
+        float bias = __fmaf_rn(noise, 1.0e-3f, __fmul_rn(-8.0f, __half2float(scale)));
+        meta[2 * offset] = scale;
+        meta[2 * offset + 1] = __float2half_rn(bias);
+    }
+}
+
+__global__ void synth_x_kernel(uint64_t key, __half *x, uint64_t begin, uint64_t count) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t offset = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; offset < count;
+         offset += stride) {
+        uint64_t index = begin + offset;
+        x[offset] = __float2half_rn(normal12(keyed(key, 3ull * index),
+                                             keyed(key, 3ull * index + 1),
+                                             keyed(key, 3ull * index + 2)));
+    }
+}
+
+static unsigned synth_blocks(uint64_t count) {
+    uint64_t blocks = (count + 255) / 256;
+    return (unsigned)(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+}
+
+cudaError_t launch_synth_codes(uint64_t seed, uint64_t stream_id, uint32_t *words,
+                               uint64_t word_begin, uint64_t word_count, cudaStream_t stream) {
+    if (word_count == 0) return cudaSuccess;
+    synth_codes_kernel<<<synth_blocks(word_count), 256, 0, stream>>>(
+        stream_key(seed, stream_id), words, word_begin, word_count);
+    return cudaGetLastError();
+}
+cudaError_t launch_synth_meta(uint64_t seed, uint64_t stream_id, __half *meta,
+                              uint64_t group_begin, uint64_t group_count, cudaStream_t stream) {
+    if (group_count == 0) return cudaSuccess;
+    synth_meta_kernel<<<synth_blocks(group_count), 256, 0, stream>>>(
+        stream_key(seed, stream_id), meta, group_begin, group_count);
+    return cudaGetLastError();
+}
+cudaError_t launch_synth_x(uint64_t seed, uint64_t stream_id, __half *x, uint64_t begin,
+                           uint64_t count, cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    synth_x_kernel<<<synth_blocks(count), 256, 0, stream>>>(stream_key(seed, stream_id), x,
+                                                            begin, count);
+    return cudaGetLastError();
+}
+
+}  // namespace q4b

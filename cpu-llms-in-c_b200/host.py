@@ -1,0 +1,350 @@
+"""ctypes binding of libq4b200.so and thin object wrappers.
+
+Mirrors the reference's C conventions for this path (int status + caller-supplied
+error buffer, opaque handles, the library owns device memory): a nonzero status
+becomes a Q4Error carrying the library's message and the status code
+(1 bad argument, 2 device failure, 3 load failure -- qwen38_m3_decode.h:20-25).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import numpy as np
+
+F16, F32, BF16, NONE = 0, 1, 2, -1
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_HEADER = os.path.join(os.path.dirname(_HERE), "include", "q4b200.h")
+_ERR = 512
+
+
+class Q4Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libq4b200 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+def library_path() -> str:
+    return os.path.join(_HERE, "libq4b200.so")
+
+
+def declared_symbols() -> list[str]:
+    """Every function include/q4b200.h declares."""
+    with open(_HEADER) as handle:
+        text = handle.read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(q4b_[a-z0-9_]+)\s*\(", text)))
+
+
+_lib = None
+_vp, _cp, _sz = ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t
+_u32, _u64, _int = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int
+
+
+def library() -> ctypes.CDLL:
+    """Load libq4b200.so, building it first when nvcc is available.
+
+    Raises instead of degrading: there is no other implementation to fall to."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    from . import _build
+    try:
+        if _build.stale():
+            _build.build()
+    except Exception as error:  # no nvcc on this machine: use the shipped binary
+        if not os.path.exists(path):
+            raise RuntimeError(f"libq4b200.so is missing and cannot be built: {error}") from error
+    lib = ctypes.CDLL(path)
+    err = [_cp, _sz]
+    spec = {
+        "q4b_context_open": (_vp, [_int] + err),
+        "q4b_context_close": (None, [_vp]),
+        "q4b_device_count": (_int, []),
+        "q4b_context_stream": (_vp, [_vp]),
+        "q4b_context_set_variant": (None, [_vp, _int]),
+        "q4b_context_launch_count": (_u64, [_vp]),
+        "q4b_alloc": (_int, [_vp, _sz, ctypes.POINTER(_vp)] + err),
+        "q4b_free": (_int, [_vp, _vp]),
+        "q4b_alloc_host": (_int, [_vp, _sz, ctypes.POINTER(_vp)] + err),
+        "q4b_free_host": (_int, [_vp, _vp]),
+        "q4b_copy_to_device": (_int, [_vp, _vp, _vp, _sz] + err),
+        "q4b_copy_to_host": (_int, [_vp, _vp, _vp, _sz] + err),
+        "q4b_weight_upload": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_weight_upload_planes": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _u32, _u32, _u32,
+                                            ctypes.POINTER(_vp)] + err),
+        "q4b_weight_from_device": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_weight_synth": (_int, [_vp, _u64, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_synth_x": (_int, [_vp, _u64, _u64, _vp, _u64, _u64] + err),
+        "q4b_weight_free": (None, [_vp, _vp]),
+        "q4b_weight_info": (_int, [_vp, ctypes.POINTER(_u32), ctypes.POINTER(_u32), ctypes.POINTER(_u64)]),
+        "q4b_weight_unpack": (_int, [_vp, _vp, _vp, _vp, _vp] + err),
+        "q4b_matmul": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, _u32, _vp, _int, _u32] + err),
+        "q4b_matmul_group": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, _int, _u32, ctypes.POINTER(_vp),
+                                    _int, ctypes.POINTER(_u32)] + err),
+        "q4b_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int, _u32] + err),
+        "q4b_matmul_host": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
+                                         ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_timer_start": (_int, [_vp] + err),
+        "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_graph_begin": (_int, [_vp] + err),
+        "q4b_graph_end": (_int, [_vp, ctypes.POINTER(_vp)] + err),
+        "q4b_graph_launch": (_int, [_vp, _vp] + err),
+        "q4b_graph_free": (None, [_vp]),
+    }
+    for name, (restype, argtypes) in spec.items():
+        function = getattr(lib, name)
+        function.restype = restype
+        function.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def _np_dtype_code(array: np.ndarray) -> int:
+    if array.dtype == np.float16:
+        return F16
+    if array.dtype == np.float32:
+        return F32
+    raise TypeError(f"activations must be float16 or float32, not {array.dtype}")
+
+
+_NP_OF = {F16: np.float16, F32: np.float32}
+
+
+class DeviceBuffer:
+    """A plain device allocation owned by a context."""
+
+    def __init__(self, context: "Q4Context", nbytes: int):
+        self.context = context
+        self.nbytes = int(nbytes)
+        pointer = _vp()
+        context._check(library().q4b_alloc(context.handle, self.nbytes, ctypes.byref(pointer),
+                                           context._err, _ERR))
+        self.ptr = pointer.value
+
+    def upload(self, array: np.ndarray) -> "DeviceBuffer":
+        array = np.ascontiguousarray(array)
+        assert array.nbytes <= self.nbytes
+        self.context._check(library().q4b_copy_to_device(self.context.handle, self.ptr, array.ctypes.data,
+                                                         array.nbytes, self.context._err, _ERR))
+        self.context.sync()  # the NumPy temporary may die after this call
+        return self
+
+    def download(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        assert out.nbytes <= self.nbytes
+        self.context._check(library().q4b_copy_to_host(self.context.handle, out.ctypes.data, self.ptr,
+                                                       out.nbytes, self.context._err, _ERR))
+        self.context.sync()
+        return out
+
+    def free(self):
+        if self.ptr:
+            library().q4b_free(self.context.handle, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Q4Weight:
+    """One Q4 matrix (or the N-slice of one) resident in HBM as a tile stream."""
+
+    def __init__(self, context: "Q4Context", handle: int):
+        self.context = context
+        self.handle = handle
+        rows, groups, nbytes = _u32(), _u32(), _u64()
+        library().q4b_weight_info(handle, ctypes.byref(rows), ctypes.byref(groups), ctypes.byref(nbytes))
+        self.rows, self.groups, self.device_bytes = rows.value, groups.value, nbytes.value
+        self.columns = self.groups * 64
+
+    def unpack(self, codes=True, w32=True, w16=True):
+        """Device-side dequantisation of the whole shard -> host arrays."""
+        shape = (self.rows, self.columns)
+        c = np.empty(shape, np.uint8) if codes else None
+        a = np.empty(shape, np.float32) if w32 else None
+        b = np.empty(shape, np.uint16) if w16 else None
+        p = lambda v: None if v is None else v.ctypes.data
+        self.context._check(library().q4b_weight_unpack(self.context.handle, self.handle, p(c), p(a), p(b),
+                                                        self.context._err, _ERR))
+        return c, a, (None if b is None else b.view(np.float16))
+
+    def free(self):
+        if self.handle:
+            library().q4b_weight_free(self.context.handle, self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Q4Graph:
+    def __init__(self, context: "Q4Context", handle: int):
+        self.context, self.handle = context, handle
+
+    def launch(self):
+        self.context._check(library().q4b_graph_launch(self.context.handle, self.handle,
+                                                       self.context._err, _ERR))
+
+    def free(self):
+        if self.handle:
+            library().q4b_graph_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Q4Context:
+    """One GPU, one stream (q4b_context)."""
+
+    def __init__(self, device: int = 0):
+        self._err = ctypes.create_string_buffer(_ERR)
+        self.handle = library().q4b_context_open(device, self._err, _ERR)
+        if not self.handle:
+            raise Q4Error(2, self._err.value.decode(errors="replace"))
+        self.device = device
+
+    # -- plumbing ---------------------------------------------------------
+    def _check(self, status: int):
+        if status != 0:
+            raise Q4Error(status, self._err.value.decode(errors="replace"))
+
+    def close(self):
+        if self.handle:
+            library().q4b_context_close(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    @property
+    def stream(self) -> int:
+        return library().q4b_context_stream(self.handle)
+
+    @property
+    def launches(self) -> int:
+        return int(library().q4b_context_launch_count(self.handle))
+
+    def set_variant(self, variant: int):
+        library().q4b_context_set_variant(self.handle, int(variant))
+
+    def alloc(self, nbytes: int) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes)
+
+    def to_device(self, array: np.ndarray) -> DeviceBuffer:
+        array = np.ascontiguousarray(array)
+        return DeviceBuffer(self, max(array.nbytes, 16)).upload(array)
+
+    def timer_start(self):
+        self._check(library().q4b_timer_start(self.handle, self._err, _ERR))
+
+    def sync(self, timed: bool = False) -> float:
+        ms = ctypes.c_double(0.0)
+        self._check(library().q4b_sync(self.handle, ctypes.byref(ms) if timed else None, self._err, _ERR))
+        return ms.value
+
+    # -- loader -----------------------------------------------------------
+    def upload(self, quants: np.ndarray, meta: np.ndarray, rows: int, groups: int, row_begin: int = 0,
+               row_count: int | None = None) -> Q4Weight:
+        """Image segments (quants bytes, interleaved fp16 {scale,bias}) -> HBM."""
+        quants = np.ascontiguousarray(quants)
+        meta = np.ascontiguousarray(meta)
+        handle = _vp()
+        count = rows - row_begin if row_count is None else row_count
+        self._check(library().q4b_weight_upload(self.handle, quants.ctypes.data, meta.ctypes.data, rows, groups,
+                                                row_begin, count, ctypes.byref(handle), self._err, _ERR))
+        return Q4Weight(self, handle.value)
+
+    def upload_planes(self, quants, scales, biases, meta_dtype, rows, groups, row_begin=0, row_count=None):
+        quants, scales, biases = (np.ascontiguousarray(a) for a in (quants, scales, biases))
+        handle = _vp()
+        count = rows - row_begin if row_count is None else row_count
+        self._check(library().q4b_weight_upload_planes(self.handle, quants.ctypes.data, scales.ctypes.data,
+                                                       biases.ctypes.data, meta_dtype, rows, groups, row_begin,
+                                                       count, ctypes.byref(handle), self._err, _ERR))
+        return Q4Weight(self, handle.value)
+
+    def synth_weight(self, seed: int, projection: int, rows: int, groups: int, row_begin: int = 0,
+                     row_count: int | None = None) -> Q4Weight:
+        handle = _vp()
+        count = rows - row_begin if row_count is None else row_count
+        self._check(library().q4b_weight_synth(self.handle, seed, projection, rows, groups, row_begin, count,
+                                               ctypes.byref(handle), self._err, _ERR))
+        return Q4Weight(self, handle.value)
+
+    def synth_x(self, seed: int, stream_id: int, m_rows: int, columns: int) -> DeviceBuffer:
+        buffer = DeviceBuffer(self, m_rows * columns * 2)
+        self._check(library().q4b_synth_x(self.handle, seed, stream_id, buffer.ptr, 0, m_rows * columns,
+                                          self._err, _ERR))
+        return buffer
+
+    # -- compute on device pointers (asynchronous) --------------------------
+    def matmul(self, weight: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int, y_dtype: int = F16,
+               ldy: int | None = None, residual_ptr: int | None = None, residual_dtype: int = NONE,
+               ld_residual: int = 0):
+        self._check(library().q4b_matmul(self.handle, weight.handle, x_ptr, x_dtype, m_rows, y_ptr, y_dtype,
+                                         weight.rows if ldy is None else ldy, residual_ptr, residual_dtype,
+                                         ld_residual, self._err, _ERR))
+
+    def matmul_group(self, weights, x_ptr: int, x_dtype: int, m_rows: int, y_ptrs, y_dtype: int = F16,
+                     ldys=None):
+        count = len(weights)
+        handles = (_vp * count)(*[w.handle for w in weights])
+        outputs = (_vp * count)(*y_ptrs)
+        strides = (_u32 * count)(*(ldys if ldys is not None else [w.rows for w in weights]))
+        self._check(library().q4b_matmul_group(self.handle, handles, count, x_ptr, x_dtype, m_rows, outputs,
+                                               y_dtype, strides, self._err, _ERR))
+
+    def gate_up_silu(self, gate: Q4Weight, up: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int,
+                     y_dtype: int = F16, ldy: int | None = None):
+        self._check(library().q4b_gate_up_silu(self.handle, gate.handle, up.handle, x_ptr, x_dtype, m_rows,
+                                               y_ptr, y_dtype, gate.rows if ldy is None else ldy,
+                                               self._err, _ERR))
+
+    # -- operator-level calls on host arrays (synchronous) -------------------
+    def matmul_host(self, weight: Q4Weight, x: np.ndarray, y_dtype: int = F16):
+        """y = x @ W^T on host arrays; returns (y, device milliseconds)."""
+        x = np.ascontiguousarray(x)
+        m_rows = x.shape[0]
+        y = np.empty((m_rows, weight.rows), dtype=_NP_OF[y_dtype])
+        ms = ctypes.c_double(0.0)
+        self._check(library().q4b_matmul_host(self.handle, weight.handle, x.ctypes.data, _np_dtype_code(x),
+                                              m_rows, y.ctypes.data, y_dtype, ctypes.byref(ms),
+                                              self._err, _ERR))
+        return y, ms.value
+
+    def gate_up_silu_host(self, gate: Q4Weight, up: Q4Weight, x: np.ndarray, y_dtype: int = F16):
+        x = np.ascontiguousarray(x)
+        m_rows = x.shape[0]
+        y = np.empty((m_rows, gate.rows), dtype=_NP_OF[y_dtype])
+        ms = ctypes.c_double(0.0)
+        self._check(library().q4b_gate_up_silu_host(self.handle, gate.handle, up.handle, x.ctypes.data,
+                                                    _np_dtype_code(x), m_rows, y.ctypes.data, y_dtype,
+                                                    ctypes.byref(ms), self._err, _ERR))
+        return y, ms.value
+
+    # -- graph replay -------------------------------------------------------
+    def graph_begin(self):
+        self._check(library().q4b_graph_begin(self.handle, self._err, _ERR))
+
+    def graph_end(self) -> Q4Graph:
+        handle = _vp()
+        self._check(library().q4b_graph_end(self.handle, ctypes.byref(handle), self._err, _ERR))
+        return Q4Graph(self, handle.value)

@@ -1,0 +1,174 @@
+"""A stack of Q4 layers on one rank of a column-parallel job (BASELINE configs[4]).
+
+Every projection of every layer is split by output rows over `world` ranks;
+each rank owns its slice's tile stream, computes Y[:, n0:n1] from the full x and
+the slices are gathered so that every rank ends with the whole [M, N].
+
+Two gather paths:
+  * "nccl"  : torch.distributed all_gather_into_tensor per gather point, queued
+              on the context's stream (the baseline and the correctness check);
+  * "push"  : the kernels' epilogues store their slice straight into every
+              peer's output buffer over NVLink (see q4b_comm.cu), one bounded
+              arrival wait per layer.
+With world == 1 neither runs and the whole step is replayed from one recorded
+launch sequence.  torch is imported only when world > 1 (process group, NCCL).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from .host import F16, Q4Context, library
+from .layer import Q4Layer, slice_of
+
+
+class ShardedLayerStack:
+    def __init__(self, ctx: Q4Context, layer_set, n_layers: int, m_rows: int, rank: int = 0, world: int = 1,
+                 dist=None, gather: str = "nccl"):
+        self.ctx, self.layer_set, self.n_layers, self.m = ctx, tuple(layer_set), n_layers, m_rows
+        self.rank, self.world, self.dist, self.gather = rank, world, dist, gather
+        self.layers = [Q4Layer(ctx, layer_set, seed, rank, world) for seed in range(n_layers)]
+        self.ks = sorted({p.k for p in self.layer_set})
+        self.graph = None
+
+        # activations: per layer, one [M, K] fp16 block per distinct K
+        self.x_offsets, offset = {}, 0
+        for k in self.ks:
+            self.x_offsets[k] = offset
+            offset += m_rows * k * 2
+        self.x_layer_bytes = offset
+        self.x_all = ctx.alloc(self.x_layer_bytes * n_layers)
+        lib = library()
+        for index in range(n_layers):
+            for k in self.ks:
+                pointer = self.x_all.ptr + index * self.x_layer_bytes + self.x_offsets[k]
+                ctx._check(lib.q4b_synth_x(ctx.handle, index, 0, pointer, 0, m_rows * k, ctx._err, 512))
+        # outputs: per layer, the full [M, N] of every projection
+        self.y_offsets, offset = {}, 0
+        for p in self.layer_set:
+            self.y_offsets[p.name] = offset
+            offset += m_rows * p.n * 2
+        self.y_layer_bytes = offset
+        self.h2d_bytes_per_step = self.x_layer_bytes * n_layers
+        self.d2h_bytes_per_step = self.y_layer_bytes * n_layers
+        self._torch = None
+        if world > 1:
+            import torch
+            self._torch = torch
+            self.stream = torch.cuda.ExternalStream(ctx.stream)
+            self.y_torch = torch.zeros(self.y_layer_bytes * n_layers // 2, dtype=torch.float16, device="cuda")
+            self.y_base = self.y_torch.data_ptr()
+            # this rank's slices, one contiguous block per layer: [projection][M][n_local]
+            self.local_offsets, offset = {}, 0
+            for p in self.layer_set:
+                self.local_offsets[p.name] = offset
+                offset += m_rows * slice_of(p.n, rank, world)[1] * 2
+            self.local_layer_bytes = offset
+            self.local_torch = torch.zeros(offset * n_layers // 2, dtype=torch.float16, device="cuda")
+            self.local_base = self.local_torch.data_ptr()
+            self.staging = torch.zeros(max(m_rows * p.n for p in self.layer_set), dtype=torch.float16, device="cuda")
+        else:
+            self.y_all = ctx.alloc(self.y_layer_bytes * n_layers)
+            self.y_base = self.y_all.ptr
+        # pinned host mirrors for the end-to-end measurement
+        self.x_host = self._pinned(self.x_layer_bytes * n_layers)
+        self.y_host = self._pinned(self.y_layer_bytes * n_layers)
+        ctx._check(lib.q4b_copy_to_host(ctx.handle, self.x_host, self.x_all.ptr, self.x_layer_bytes * n_layers,
+                                        ctx._err, 512))
+        ctx.sync()
+
+    def _pinned(self, nbytes: int) -> int:
+        pointer = ctypes.c_void_p()
+        self.ctx._check(library().q4b_alloc_host(self.ctx.handle, nbytes, ctypes.byref(pointer), self.ctx._err, 512))
+        return pointer.value
+
+    # ------------------------------------------------------------------
+    def _x_ptrs(self, index: int):
+        base = self.x_all.ptr + index * self.x_layer_bytes
+        return {k: base + self.x_offsets[k] for k in self.ks}
+
+    def _queue_single_gpu(self):
+        for index, layer in enumerate(self.layers):
+            base = self.y_base + index * self.y_layer_bytes
+            layer.forward(self._x_ptrs(index), {p.name: base + self.y_offsets[p.name] for p in self.layer_set}, self.m)
+
+    def _queue_sharded_nccl(self):
+        torch, dist = self._torch, self.dist
+        with torch.cuda.stream(self.stream):
+            for index, layer in enumerate(self.layers):
+                local = self.local_base + index * self.local_layer_bytes
+                layer.forward(self._x_ptrs(index), {p.name: local + self.local_offsets[p.name] for p in self.layer_set},
+                              self.m)
+                for p in self.layer_set:
+                    n_local = slice_of(p.n, self.rank, self.world)[1]
+                    start = (index * self.local_layer_bytes + self.local_offsets[p.name]) // 2
+                    piece = self.local_torch[start:start + self.m * n_local]
+                    begin = (index * self.y_layer_bytes + self.y_offsets[p.name]) // 2
+                    full = self.y_torch[begin:begin + self.m * p.n]
+                    if self.m == 1:
+                        dist.all_gather_into_tensor(full, piece)
+                    else:
+                        staging = self.staging[:self.m * p.n]
+                        dist.all_gather_into_tensor(staging, piece)
+                        full.view(self.m, self.world, n_local).copy_(
+                            staging.view(self.world, self.m, n_local).permute(1, 0, 2))
+
+    def step(self):
+        """One pass over all layers, queued on the context stream."""
+        if self.world > 1:
+            self._queue_sharded_nccl()
+            return
+        if self.graph is None:
+            self._queue_single_gpu()  # plain launches once (also sets kernel attributes)
+            self.ctx.sync()
+            self.ctx.graph_begin()
+            self._queue_single_gpu()
+            self.graph = self.ctx.graph_end()
+        self.graph.launch()
+
+    def step_from_host(self):
+        """The same pass with x starting in pinned host memory and every output
+        copied back to pinned host memory."""
+        lib, ctx = library(), self.ctx
+        ctx._check(lib.q4b_copy_to_device(ctx.handle, self.x_all.ptr, self.x_host, self.h2d_bytes_per_step,
+                                          ctx._err, 512))
+        self.step()
+        ctx._check(lib.q4b_copy_to_host(ctx.handle, self.y_host, self.y_base, self.d2h_bytes_per_step,
+                                        ctx._err, 512))
+        ctx.sync()
+
+    def dominant_kernel_pass(self):
+        """The fused gate/up kernel alone, once per layer (distinct weights)."""
+        fused = next(p for p in self.layer_set if p.fused)
+        for index, layer in enumerate(self.layers):
+            gate, up = layer.weights[fused.name]
+            out = (self.local_base + index * self.local_layer_bytes + self.local_offsets[fused.name]
+                   if self.world > 1 else self.y_base + index * self.y_layer_bytes + self.y_offsets[fused.name])
+            self.ctx.gate_up_silu(gate, up, self._x_ptrs(index)[fused.k], F16, self.m, out, F16)
+
+    def outputs(self, index: int) -> dict[str, np.ndarray]:
+        """Host copies of layer `index`'s gathered outputs, for checks."""
+        self.ctx.sync()
+        result = {}
+        for p in self.layer_set:
+            out = np.empty((self.m, p.n), dtype=np.float16)
+            pointer = self.y_base + index * self.y_layer_bytes + self.y_offsets[p.name]
+            self.ctx._check(library().q4b_copy_to_host(self.ctx.handle, out.ctypes.data, pointer, out.nbytes,
+                                                       self.ctx._err, 512))
+            self.ctx.sync()
+            result[p.name] = out
+        return result
+
+    def ncu_traffic_bytes(self):
+        """DRAM bytes per launch of the dominant kernel from the committed ncu
+        capture (profiles/), or None when no capture has been taken."""
+        return None
+
+    def free(self):
+        for layer in self.layers:
+            layer.free()
+        if self.graph is not None:
+            self.graph.free()
+        library().q4b_free_host(self.ctx.handle, self.x_host)
+        library().q4b_free_host(self.ctx.handle, self.y_host)

@@ -1,0 +1,165 @@
+/*
+ * libq4b200 -- affine-Q4 matmul for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * Drop-in device side of llm-in-c's Q4 hot path: w = scale*q + bias, uint4 codes
+ * packed 8 per uint32 along K, one fp16 {scale, bias} record per 64-column group
+ * (the reference's packed-image segments, models/qwen3.8-27b/targets/apple-m3-pro/
+ * qwen38_m3_image.h:26-94, qwen38_q4.metal:10-37).  The library has no Python or
+ * PyTorch dependency; it links only the CUDA runtime.
+ *
+ * Conventions follow the reference runtime (qwen38_m3_decode.h:20-25):
+ *   - every call returns int: 0 ok, 1 bad argument or state, 2 device failure,
+ *     3 image / load failure; on failure a NUL-terminated message is written to
+ *     the caller's buffer (which may be NULL / 0);
+ *   - handles are opaque; the library owns device memory, the caller owns host
+ *     memory (host pointers passed to an upload may be freed on return);
+ *   - one stream per context, one thread per context at a time; work is queued
+ *     asynchronously on the context's stream unless the call is named *_host or
+ *     documented as synchronous.
+ */
+#ifndef Q4B200_H
+#define Q4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct q4b_context q4b_context;
+typedef struct q4b_weight q4b_weight;
+typedef struct q4b_graph q4b_graph;
+
+enum { Q4B_OK = 0, Q4B_BAD_ARGUMENT = 1, Q4B_DEVICE_FAILURE = 2, Q4B_LOAD_FAILURE = 3 };
+enum { Q4B_F16 = 0, Q4B_F32 = 1, Q4B_BF16 = 2, Q4B_NONE = -1 };
+
+/* ---- context: replaces qwen38_m3_model_open / _close for this path
+ * (qwen38_m3_decode.h:27-49, qwen38_m3_decode.m:1487).  NULL + message on
+ * failure.  Fails loudly when no sm_100 device is present: there is no CPU
+ * fallback. */
+q4b_context *q4b_context_open(int device, char *error_message, size_t error_capacity);
+void q4b_context_close(q4b_context *context);
+int q4b_device_count(void);
+/* cudaStream_t of the context, for callers that queue their own work */
+void *q4b_context_stream(q4b_context *context);
+/* Selects a kernel variant for A/B measurements (0 = library heuristics); the
+ * counterpart of QWEN38_PREFILL_MMA / QWEN38_VERIFY_MMA (qwen38_m3_decode.m:
+ * 1547-1555, :2757).  The environment variable Q4B_VARIANT sets the default. */
+void q4b_context_set_variant(q4b_context *context, int variant);
+/* number of kernels this context has launched since it was opened */
+uint64_t q4b_context_launch_count(const q4b_context *context);
+
+/* ---- plain device memory, for hosts without another CUDA allocator ---- */
+int q4b_alloc(q4b_context *context, size_t bytes, void **device_pointer,
+              char *error_message, size_t error_capacity);
+int q4b_free(q4b_context *context, void *device_pointer);
+int q4b_alloc_host(q4b_context *context, size_t bytes, void **pinned_host_pointer,
+                   char *error_message, size_t error_capacity);
+int q4b_free_host(q4b_context *context, void *pinned_host_pointer);
+/* asynchronous on the context stream */
+int q4b_copy_to_device(q4b_context *context, void *device_destination, const void *host_source,
+                       size_t bytes, char *error_message, size_t error_capacity);
+int q4b_copy_to_host(q4b_context *context, void *host_destination, const void *device_source,
+                     size_t bytes, char *error_message, size_t error_capacity);
+
+/* ---- weight-image loader: replaces mapped_buffer / load_*_layer
+ * (qwen38_m3_decode.m:398-407, :500-625).  Takes the two image segments of one
+ * matrix exactly as the reference packer wrote them (quants = MLX U32 [rows,
+ * K/8] bytes, PACK qwen38_m3_pack.c:395-418; meta = [rows, K/64] {fp16 scale,
+ * fp16 bias}, :420-446), repacks rows [row_begin, row_begin+row_count) -- the
+ * N-slice this GPU owns -- into the device tile stream and uploads them.
+ * Synchronous.  Rejects K % 64 != 0, NULL segments and empty slices. */
+int q4b_weight_upload(q4b_context *context, const void *quants, const void *meta,
+                      uint32_t rows, uint32_t groups_per_row, uint32_t row_begin,
+                      uint32_t row_count, q4b_weight **weight,
+                      char *error_message, size_t error_capacity);
+/* Same, from separate scale and bias planes in fp16 or bf16 -- the un-converted
+ * MLX metadata that minimax_h3_q4_projection carries (compiler/minimax-h3/
+ * apple-m3-pro/minimax_h3_q4_layer.h:14-24); bf16 is converted like the packer
+ * does (qwen38_m3_pack.c:173-178). */
+int q4b_weight_upload_planes(q4b_context *context, const void *quants, const void *scales,
+                             const void *biases, int meta_dtype, uint32_t rows,
+                             uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                             q4b_weight **weight, char *error_message, size_t error_capacity);
+/* Same as q4b_weight_upload with the two segments already in device memory. */
+int q4b_weight_from_device(q4b_context *context, const void *device_quants,
+                           const void *device_meta, uint32_t rows, uint32_t groups_per_row,
+                           uint32_t row_begin, uint32_t row_count, q4b_weight **weight,
+                           char *error_message, size_t error_capacity);
+/* Seeded synthetic matrix generated on the device in the image layout and then
+ * loaded like any other (the role of fill_weights, qwen38_m3.m:64-87).  The same
+ * counter-based generator exists in C for the CPU checker. */
+int q4b_weight_synth(q4b_context *context, uint64_t seed, uint32_t projection, uint32_t rows,
+                     uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                     q4b_weight **weight, char *error_message, size_t error_capacity);
+int q4b_synth_x(q4b_context *context, uint64_t seed, uint64_t stream_id, void *device_x_f16,
+                uint64_t begin, uint64_t count, char *error_message, size_t error_capacity);
+void q4b_weight_free(q4b_context *context, q4b_weight *weight);
+int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_per_row,
+                    uint64_t *device_bytes);
+/* Dequantisation in isolation (the job of qwen38_q4_embedding_lookup,
+ * qwen38_global.metal:13-28) over the whole shard, written to HOST buffers, any
+ * of which may be NULL: codes uint8 [rows][K], w32 float [rows][K] =
+ * scale*(float)q+bias, w16 fp16 bits [rows][K] = the value the tensor-core GEMM
+ * multiplies.  Synchronous. */
+int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *codes,
+                      float *w32, uint16_t *w16, char *error_message, size_t error_capacity);
+
+/* ---- matmul: replaces the decode row kernels and encode_prefill_gemm_f16 /
+ * encode_prefill_gemm_residual (qwen38_m3_decode.m:639-660, :885-1001).
+ * y[m][n] = sum_k w(n,k) x[m][k] (+ residual[m][n]), fp32 accumulation.
+ * x is [M][K] row-major fp16 or fp32, y is [M][ldy] fp16 or fp32 (ldy >= rows
+ * of the shard lets a shard write its column slice of a wider matrix),
+ * residual is [M][ld_residual] fp16 or fp32 or NULL.  DEVICE pointers, 16-byte
+ * aligned; asynchronous.  The kernel is chosen by M: GEMV for M <= 32, the
+ * tcgen05 GEMM above. */
+int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
+               uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, const void *residual,
+               int residual_dtype, uint32_t ld_residual,
+               char *error_message, size_t error_capacity);
+/* Up to 4 matrices that share x in one launch, e.g. q/k/v, which the reference
+ * fuses into one matrix (qwen38_attention.metal:4-8). */
+int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int count,
+                     const void *x, int x_dtype, uint32_t m_rows, void *const *y, int y_dtype,
+                     const uint32_t *ldy, char *error_message, size_t error_capacity);
+/* Fused gate/up with SiLU-gate epilogue: out = silu(gate x) * (up x), replaces
+ * qwen38_q4_gate_up_silu (qwen38_q4.metal:129-151, qwen38_m3_decode.m:643-651)
+ * and the prefill pair + qwen38_prefill_silu_mul (:1019-1033). */
+int q4b_gate_up_silu(q4b_context *context, const q4b_weight *gate, const q4b_weight *up,
+                     const void *x, int x_dtype, uint32_t m_rows, void *y, int y_dtype,
+                     uint32_t ldy, char *error_message, size_t error_capacity);
+
+/* ---- operator-level calls with HOST buffers: the shape of
+ * minimax_h3_m3_run_q4_projection_bf16 (minimax_h3_m3_gemm.h:57-66): copy in,
+ * run, copy out, report device milliseconds of the kernel.  Synchronous. */
+int q4b_matmul_host(q4b_context *context, const q4b_weight *weight, const void *x_host,
+                    int x_dtype, uint32_t m_rows, void *y_host, int y_dtype, double *gpu_ms,
+                    char *error_message, size_t error_capacity);
+int q4b_gate_up_silu_host(q4b_context *context, const q4b_weight *gate, const q4b_weight *up,
+                          const void *x_host, int x_dtype, uint32_t m_rows, void *y_host,
+                          int y_dtype, double *gpu_ms, char *error_message,
+                          size_t error_capacity);
+
+/* ---- completion and timing: replaces qwen38_m3_model_forward_wait
+ * (qwen38_m3_decode.h:77-92).  q4b_timer_start records an event on the stream;
+ * q4b_sync waits for all queued work, surfaces asynchronous errors as a nonzero
+ * status and, when device_ms is not NULL, returns the device time since the
+ * last q4b_timer_start. */
+int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity);
+int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_t error_capacity);
+
+/* ---- replay of a recorded call sequence (one command buffer per token in the
+ * reference, qwen38_m3_decode.m:1614-1690): calls between begin and end are
+ * captured instead of executed. */
+int q4b_graph_begin(q4b_context *context, char *error_message, size_t error_capacity);
+int q4b_graph_end(q4b_context *context, q4b_graph **graph, char *error_message,
+                  size_t error_capacity);
+int q4b_graph_launch(q4b_context *context, q4b_graph *graph, char *error_message,
+                     size_t error_capacity);
+void q4b_graph_free(q4b_graph *graph);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

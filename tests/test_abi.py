@@ -1,0 +1,51 @@
+"""CPU-side checks of the C-ABI library: it loads, exports everything the header
+declares, and refuses to work without a GPU instead of falling back."""
+import ctypes
+import os
+
+import pytest
+
+
+def test_library_exports_every_declared_symbol(q4b):
+    lib = q4b.library()
+    names = q4b.declared_symbols()
+    assert len(names) >= 30
+    missing = [name for name in names if not hasattr(lib, name)]
+    assert missing == []
+
+
+def test_header_cites_reference_for_each_entry_point():
+    header = os.path.join(os.path.dirname(os.path.dirname(__file__)), "include", "q4b200.h")
+    text = open(header).read()
+    for anchor in ("qwen38_m3_decode.m", "qwen38_q4.metal", "minimax_h3_m3_gemm.h", "qwen38_m3_pack.c"):
+        assert anchor in text
+
+
+def test_no_gpu_means_loud_failure(q4b):
+    lib = q4b.library()
+    if lib.q4b_device_count() > 0:
+        pytest.skip("a GPU is present")
+    with pytest.raises(q4b.Q4Error) as info:
+        q4b.Q4Context(0)
+    assert "no CUDA device" in info.value.message
+
+
+def test_null_arguments_are_rejected_without_touching_a_device(q4b):
+    lib = q4b.library()
+    err = ctypes.create_string_buffer(256)
+    assert lib.q4b_weight_info(None, None, None, None) == 1
+    assert lib.q4b_sync(None, None, err, 256) == 1
+    assert b"NULL" in err.value
+    assert lib.q4b_matmul(None, None, None, 0, 1, None, 0, 0, None, -1, 0, err, 256) == 1
+    assert lib.q4b_graph_launch(None, None, err, 256) == 1
+
+
+def test_algorithmic_bytes_match_the_stated_anchors(q4b):
+    # 27B layer: 191,692,800 weight bytes; config[0]: 1,769,472
+    weights = sum(q4b.shapes.weight_bytes(p) for p in q4b.LAYER_27B)
+    assert weights == 191_692_800
+    small = sum(q4b.shapes.weight_bytes(p) for p in q4b.LAYER_SMALL)
+    assert small == 8_257_536
+    single = q4b.Projection("config0", 1024, 3072)
+    assert q4b.shapes.weight_bytes(single) == 1_769_472
+    assert q4b.layer_flops(q4b.LAYER_27B, 1) == 681_574_400

@@ -1,0 +1,62 @@
+"""The layer launch sequence (grouped q/k/v, o, fused gate/up, down) and its
+recorded replay, against the oracle, on one GPU."""
+import importlib
+
+import numpy as np
+import pytest
+
+from q4_cases import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_layer(orc, layer_set, seed, m):
+    out, index = {}, 0
+    for p in layer_set:
+        groups = p.k // 64
+        x = orc.synth_x(seed, 0, m, p.k)
+        if p.fused:
+            gq, gm = orc.synth_weight(seed, index, p.n, groups)
+            uq, um = orc.synth_weight(seed, index + 1, p.n, groups)
+            out[p.name] = orc.gate_up_silu(gq, gm, uq, um, groups, x, want32=False)[1]
+            index += 2
+        else:
+            q, mt = orc.synth_weight(seed, index, p.n, groups)
+            out[p.name] = orc.matmul(q, mt, groups, x, want32=False)[1]
+            index += 1
+    return out
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_small_layer_stack_matches_oracle(q4b, orc, m):
+    sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
+    with q4b.Q4Context(0) as ctx:
+        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_SMALL, 3, m)
+        before = ctx.launches
+        stack.step()   # plain launches + recording
+        stack.step()   # replay
+        ctx.sync()
+        assert ctx.launches - before >= 3 * 4 * 2
+        for index in (0, 2):
+            got = stack.outputs(index)
+            want = oracle_layer(orc, q4b.LAYER_SMALL, index, m)
+            for name in want:
+                assert_close(got[name], want[name], f"layer {index} {name} M={m}")
+        stack.step_from_host()
+        got = stack.outputs(1)
+        want = oracle_layer(orc, q4b.LAYER_SMALL, 1, m)
+        for name in want:
+            assert_close(got[name], want[name], f"host path {name}")
+        stack.free()
+
+
+def test_27b_layer_matches_oracle_at_decode(q4b, orc):
+    sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
+    with q4b.Q4Context(0) as ctx:
+        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, 1, 1)
+        stack.step()
+        got = stack.outputs(0)
+        want = oracle_layer(orc, q4b.LAYER_27B, 0, 1)
+        for name in want:
+            assert_close(got[name], want[name], f"27B {name}")
+        stack.free()
