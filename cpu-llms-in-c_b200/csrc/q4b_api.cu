@@ -21,6 +21,12 @@ struct q4b_context {
     bool timer_armed;
     bool capturing;
     uint64_t launches;
+    uint32_t *status_host;    // pinned, device-mapped: kernels store a code here when a wait expires
+    uint32_t *status_device;  // the same word as the kernels see it
+    float *scratch;           // partial-sum slots of split row blocks (grown on demand)
+    size_t scratch_bytes;
+    uint32_t *counters;       // arrival counters, zero between launches
+    size_t counter_bytes;
 };
 
 struct q4b_weight {
@@ -218,6 +224,40 @@ int check_matmul_arguments(q4b_context *context, const q4b_weight *weight, const
     return Q4B_OK;
 }
 
+// Grow the context's split-K scratch to what a launch needs.  Never during
+// recording: an allocation cannot be captured, so the sequence must have run
+// once (or q4b_reserve_scratch been called) before q4b_graph_begin.
+int ensure_scratch(q4b_context *context, const GemvPlan &plan, char *error_message, size_t error_capacity) {
+    if (plan.scratch_bytes <= context->scratch_bytes && plan.counter_bytes <= context->counter_bytes) return Q4B_OK;
+    if (context->capturing) {
+        set_error(error_message, error_capacity,
+                  "the recorded sequence needs more scratch than the context holds; run it once before recording");
+        return Q4B_BAD_ARGUMENT;
+    }
+    cudaError_t status = cudaStreamSynchronize(context->stream);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "stream synchronize", status);
+    if (plan.scratch_bytes > context->scratch_bytes) {
+        cudaFree(context->scratch);
+        context->scratch = nullptr;
+        context->scratch_bytes = 0;
+        const size_t bytes = plan.scratch_bytes + plan.scratch_bytes / 2;
+        status = cudaMalloc(&context->scratch, bytes);
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "cudaMalloc of scratch", status);
+        context->scratch_bytes = bytes;
+    }
+    if (plan.counter_bytes > context->counter_bytes) {
+        cudaFree(context->counters);
+        context->counters = nullptr;
+        context->counter_bytes = 0;
+        const size_t bytes = plan.counter_bytes * 2 + 1024;
+        status = cudaMalloc(&context->counters, bytes);
+        if (status == cudaSuccess) status = cudaMemset(context->counters, 0, bytes);
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "cudaMalloc of counters", status);
+        context->counter_bytes = bytes;
+    }
+    return Q4B_OK;
+}
+
 // one launch sequence for any M: GEMV kernel up to its row limit, row blocks above
 int run_projection(q4b_context *context, GemvArgs args, char *error_message, size_t error_capacity) {
     const uint32_t limit = gemv_max_m();
@@ -234,7 +274,15 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
             block.residual = static_cast<const uint8_t *>(args.residual) +
                              (size_t)m0 * args.ld_residual * dtype_bytes(args.residual_dtype);
         }
-        cudaError_t status = launch_gemv(block, context->variant, context->sm_count, context->stream);
+        GemvPlan plan;
+        cudaError_t status = plan_gemv(block, context->variant, context->sm_count, &plan);
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv plan", status);
+        int code = ensure_scratch(context, plan, error_message, error_capacity);
+        if (code != Q4B_OK) return code;
+        block.status = context->status_device;
+        block.scratch = context->scratch;
+        block.counters = context->counters;
+        status = launch_gemv(block, plan, context->variant, context->stream);
         if (!context->capturing) ++context->launches;  // recorded launches count at replay
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv launch", status);
     }
@@ -287,11 +335,16 @@ q4b_context *q4b_context_open(int device, char *error_message, size_t error_capa
     if ((status = cudaSetDevice(device)) != cudaSuccess ||
         (status = cudaStreamCreateWithFlags(&context->stream, cudaStreamNonBlocking)) != cudaSuccess ||
         (status = cudaEventCreate(&context->timer_start)) != cudaSuccess ||
-        (status = cudaEventCreate(&context->timer_stop)) != cudaSuccess) {
+        (status = cudaEventCreate(&context->timer_stop)) != cudaSuccess ||
+        (status = cudaHostAlloc(reinterpret_cast<void **>(&context->status_host), sizeof(uint32_t),
+                                cudaHostAllocMapped)) != cudaSuccess ||
+        (status = cudaHostGetDevicePointer(reinterpret_cast<void **>(&context->status_device),
+                                           context->status_host, 0)) != cudaSuccess) {
         set_error(error_message, error_capacity, "context setup: %s", cudaGetErrorString(status));
         delete context;
         return nullptr;
     }
+    *context->status_host = 0;
     return context;
 }
 
@@ -302,6 +355,9 @@ void q4b_context_close(q4b_context *context) {
     cudaEventDestroy(context->timer_start);
     cudaEventDestroy(context->timer_stop);
     cudaStreamDestroy(context->stream);
+    cudaFreeHost(context->status_host);
+    cudaFree(context->scratch);
+    cudaFree(context->counters);
     delete context;
 }
 
@@ -661,6 +717,14 @@ int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_
     }
     Q4B_CUDA(cudaStreamSynchronize(context->stream), "stream synchronize");
     Q4B_CUDA(cudaGetLastError(), "asynchronous error");
+    if (*context->status_host != 0) {
+        const uint32_t code = *context->status_host;
+        *context->status_host = 0;
+        if (context->counters != nullptr) cudaMemset(context->counters, 0, context->counter_bytes);
+        set_error(error_message, error_capacity,
+                  "a device-side wait expired (code 0x%x); results of the queued work are invalid", code);
+        return Q4B_DEVICE_FAILURE;
+    }
     if (device_ms != nullptr) {
         *device_ms = 0.0;
         if (context->timer_armed) {

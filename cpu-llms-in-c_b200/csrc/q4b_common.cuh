@@ -7,8 +7,11 @@
 //   quants [N][G][32 bytes]   byte j>>1 of a group holds code j (low nibble even)
 //   meta   [N][G]{fp16 scale, fp16 bias}
 // On upload the two planes are fused into one linear stream of 576-byte tiles.
-// Tile (rt, g) covers rows 16*rt .. 16*rt+15 and columns 64*g .. 64*g+63 and
-// sits at byte offset (rt*G + g) * 576:
+// Tile (rt, g) covers rows 16*rt .. 16*rt+15 and columns 64*g .. 64*g+63.  Four
+// row tiles form a 64-row block; the stream is ordered [block][group][tile in
+// block], so tile (rt, g) sits at byte offset ((rt/4)*G + g) * 2304 + (rt%4) * 576
+// and everything one 64-row block needs for a range of groups is one contiguous
+// byte range (one bulk copy).  Inside a tile:
 //
 //   [  0,512)  32 lane pieces of 16 bytes.  Lane l = 4*gid + t owns rows
 //              (gid, gid+8) and columns 16*t .. 16*t+15 of the tile.  Its four
@@ -23,9 +26,9 @@
 //   [512,576)  8 records of 8 bytes, record gid = {scale[gid], bias[gid],
 //              scale[gid+8], bias[gid+8]} as fp16.
 //
-// One warp reads a whole tile with one coalesced 16-byte load per lane plus an
-// 8-byte metadata load; a CTA of the tensor-core GEMM fetches the same bytes
-// with bulk copies.  Rows are padded with zero tiles up to a multiple of 128.
+// A warp consumes a tile with one 16-byte read per lane plus an 8-byte metadata
+// read; CTAs fetch whole [block][group range] byte ranges with bulk copies.
+// Rows are padded with zero tiles up to a multiple of 128.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -41,6 +44,8 @@ constexpr int kTileCodeBytes = 512;  // 16 rows x 64 codes / 2
 constexpr int kTileMetaBytes = 64;   // 16 x {scale, bias} fp16
 constexpr int kTileBytes = kTileCodeBytes + kTileMetaBytes;  // 576
 constexpr int kRowTilePad = 8;       // row tiles padded to a multiple of this
+constexpr int kBlockTiles = 4;       // row tiles per 64-row block
+constexpr int kUnitBytes = kBlockTiles * kTileBytes;  // one block x one group: 2304
 
 enum DType : int { kF16 = 0, kF32 = 1, kBF16 = 2, kNone = -1 };
 
@@ -53,6 +58,11 @@ struct WeightView {
 
 __host__ __device__ inline uint32_t ceil_div(uint32_t a, uint32_t b) {
     return (a + b - 1) / b;
+}
+
+// byte offset of tile (rt, g) in a stream with G groups per row
+__host__ __device__ inline size_t tile_offset(uint32_t rt, uint32_t g, uint32_t G) {
+    return ((size_t)(rt / kBlockTiles) * G + g) * kUnitBytes + (size_t)(rt % kBlockTiles) * kTileBytes;
 }
 
 // ---------------------------------------------------------------------------

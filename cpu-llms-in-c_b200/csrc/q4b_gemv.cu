@@ -1,4 +1,4 @@
-// Decode GEMV (M = 1) and small-M verify GEMM (M <= 32) on the Q4 tile stream.
+// Decode GEMV (M = 1) and small-M verify GEMM (M <= 16) on the Q4 tile stream.
 //
 // Replaces the reference's row kernels: qwen38_q4_matvec / qwen38_q4_gate_up_silu
 // (qwen38_q4.metal:111-151), the fused in-projections (qwen38_layer.metal:71-100,
@@ -6,460 +6,571 @@
 // (qwen38_layer.metal:193-255) and the small-batch verify GEMMs
 // (qwen38_prefill.metal:144-248, :1090-1363).
 //
-// HBM bound: every weight byte is read once, straight into registers, with one
-// coalesced 16-byte load per lane per tile and several tiles in flight per warp.
-// The arithmetic is y[m][n] = sum_g ( s[n][g] * sum_j q[n][g][j] x[m][64g+j]
-//                                   + b[n][g] * sum_j x[m][64g+j] ):
-// the inner integer-code dot products run on the tensor pipe (m16n8k16, fp16
-// operands that hold the exact codes, fp32 accumulate), the per-group scale and
-// bias are applied in fp32 on the CUDA cores, and the group sums of x are
-// computed once per CTA.  K is split over the warps of a CTA and, for short
-// matrices, over the CTAs of a thread-block cluster whose partial sums meet in
-// the leader's shared memory (distributed shared memory, no global scratch).
+// HBM bound: every weight byte is read once.  The work of one launch is the
+// linear sequence of "units" (one 64-row block x one 64-column group, 2304
+// contiguous bytes of the tile stream; two matrices for fused gate/up).  The
+// grid is persistent -- one or two CTAs per SM -- and CTA c owns the contiguous
+// unit range [c*U/n, (c+1)*U/n): equal bytes for every CTA whatever the shape,
+// and a single contiguous byte range per CTA, which a producer warp streams into
+// a shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier)
+// several stages ahead of the consumer warps.
+//
+// Arithmetic: y[m][n] = sum_g ( s[n][g] * sum_j q[n][g][j] x[m][64g+j]
+//                             + b[n][g] * sum_j x[m][64g+j] ).
+// The integer-code dot products run on the tensor pipe (m16n8k16; the fp16
+// operands hold the exact codes, fp32 accumulate), scale and bias are applied per
+// group in fp32 on the CUDA cores, x and its group sums are staged once per CTA.
+// Consumer warp w takes units w, w+W, ... of the CTA's range and keeps the
+// 64 x M accumulators of the current row block in registers; when its row block
+// changes it adds them into the CTA's shared-memory block sums.  A row block that
+// one CTA covered completely is finished locally; otherwise each contributing CTA
+// parks its partial sums in a global scratch slot and the last one to arrive adds
+// the slots in CTA order (deterministic) and writes the output.
+// Every wait is bounded: on expiry the kernel records a code in the status word
+// and runs to its normal end.
 #include "q4b_kernels.h"
-
-#include <cooperative_groups.h>
-
-namespace cg = cooperative_groups;
 
 namespace q4b {
 
 namespace {
+
+constexpr int kMaxStages = 8;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // every wait gives up after ~2 s of SM clocks
 
 struct GemvParams {
     WeightView w[kMaxSegments];
     WeightView up;
     void *y[kMaxSegments];
     uint32_t ldy[kMaxSegments];
-    uint32_t tile_begin[kMaxSegments + 1];  // prefix sums of CTA row-tile blocks
+    uint32_t block_begin[kMaxSegments + 1];  // prefix sums of 64-row blocks
     int segments;
     const void *x;
     const void *residual;
+    uint32_t *status;
+    float *scratch;        // [blocks][slots][PER_CTA] partial sums
+    uint32_t *counters;    // [blocks] units contributed so far (self-resetting)
+    uint32_t slots;
     uint32_t ld_residual;
     uint32_t m_rows;
     uint32_t groups;
-    uint32_t row_tiles_per_cta;  // R
-    int x_dtype, y_dtype, residual_dtype;
+    uint32_t stages;
+    uint32_t x_groups;     // groups of x staged per row (min(range, G))
+    uint32_t local_blocks; // row blocks a CTA's range can touch
+    uint32_t total_units;
+    int y_dtype, residual_dtype;
 };
 
-__device__ inline uint4 load_stream_16(const void *address) {
-    uint4 value;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w)
-                 : "l"(address));
-    return value;
+__device__ inline uint32_t smem_u32(const void *pointer) {
+    return (uint32_t)__cvta_generic_to_shared(pointer);
 }
-__device__ inline uint2 load_stream_8(const void *address) {
-    uint2 value;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
-                 : "=r"(value.x), "=r"(value.y)
-                 : "l"(address));
-    return value;
+__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-
-__device__ inline void mma_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+__device__ inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ inline void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// false when the wait expired
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > kWaitLimitCycles) return false;
+    }
+    return true;
+}
+__device__ inline void bulk_copy_to_shared(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(destination), "l"(source), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ inline void consumer_barrier(uint32_t threads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
-// 16 consecutive activations of row m as 8 half2 registers (zeros past M)
-template <bool X32>
-__device__ inline void load_x16(const void *x, size_t element, bool valid, uint32_t out[8]) {
-    if (!valid) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) out[i] = 0u;
-        return;
-    }
-    if constexpr (X32) {
-        const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + element);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float4 v = __ldg(p + i);
-            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-            out[2 * i] = *reinterpret_cast<uint32_t *>(&lo);
-            out[2 * i + 1] = *reinterpret_cast<uint32_t *>(&hi);
-        }
+// D = A * B + C with C given (first == false) or zero (first == true)
+__device__ inline void mma_16816(float d[4], const uint32_t a[4], uint32_t b0, uint32_t b1, bool first) {
+    if (first) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+            "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
     } else {
-        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(x) + element);
-        uint4 a = __ldg(p), b = __ldg(p + 1);
-        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
-        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+            "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
 }
-
-template <bool X32>
-__device__ inline float sum_x16(const void *x, size_t element) {
-    float total = 0.0f;
-    if constexpr (X32) {
-        const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + element);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float4 v = __ldg(p + i);
-            // the tensor pipe sees x rounded to fp16; sum the same values
-            float2 lo = __half22float2(__floats2half2_rn(v.x, v.y));
-            float2 hi = __half22float2(__floats2half2_rn(v.z, v.w));
-            total += (lo.x + lo.y) + (hi.x + hi.y);
-        }
-    } else {
-        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(x) + element);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint4 v = __ldg(p + i);
-            const uint32_t r[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&r[k]));
-                total += f.x + f.y;
-            }
-        }
-    }
-    return total;
-}
-
-struct TileRegs {
-    uint4 codes;
-    uint2 meta;
-};
 
 // NT   : 8-column output tiles per warp (M <= 8*NT)
 // FUSED: second matrix (`up`) shares x; epilogue silu(gate) * up
 // SUBN : feed the codes to the tensor pipe as fp16 subnormals (no unpack math)
-// U    : tiles in flight per warp
-template <int NT, bool FUSED, bool SUBN, bool X32, int U>
-__global__ void __launch_bounds__(256)
+// X32  : x arrives as fp32 and is rounded to fp16 while it is staged
+//
+// Warps 0..7 consume, warp 8 produces.  A ring stage holds up to 8 "sub-units"
+// (2304 bytes: the four tiles of one 64-row block x one group of one matrix) that
+// all belong to the same row block: 8 consecutive groups, or 4 groups of gate
+// followed by the same 4 groups of up.  Consumer warp w takes sub-unit w: four
+// independent tiles per stage, accumulated in registers across stages.
+template <int NT, bool FUSED, bool SUBN, bool X32>
+__global__ void __launch_bounds__(288, NT > 1 ? 2 : 3)
 gemv_kernel(const GemvParams p) {
     constexpr int NW = FUSED ? 2 : 1;
-    extern __shared__ __align__(16) float smem[];
+    constexpr int W = 8;                             // consumer warps
+    constexpr uint32_t S = W / NW;                   // groups per full stage
+    constexpr uint32_t MC = 8 * NT;                  // output columns held per warp
+    constexpr uint32_t PER_CTA = NW * NT * 4 * 128;  // partial sums of one 64-row block
+    constexpr uint32_t kStageBytes = W * kUnitBytes;
+    constexpr uint32_t kConsumers = W * 32;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    // dependents may start at once: all they do before their own wait is prefetch weights
+    asm volatile("griddepcontrol.launch_dependents;");
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int warps = blockDim.x >> 5;
     const int gid = lane >> 2, t = lane & 3;
-    const uint32_t R = p.row_tiles_per_cta;
-    const uint32_t ksplit = gridDim.x, kslice = blockIdx.x;
+    const uint32_t G = p.groups, U = p.total_units, ctas = gridDim.x, cta = blockIdx.x;
+    const uint32_t u0 = (uint32_t)((uint64_t)U * cta / ctas);
+    const uint32_t u1 = (uint32_t)((uint64_t)U * (cta + 1) / ctas);
+    const uint32_t range = u1 - u0;
+    const uint32_t stages = p.stages;
+    const uint32_t grb0 = u0 / G, g_first = u0 % G;
+    const bool windowed = p.x_groups < G;  // x is staged per unit of the range, not per group
+    const uint32_t x_count = windowed ? range : G;
+    const uint32_t x_stride = p.x_groups * kGroup + 8;  // halves; +16 bytes de-phases the rows
 
-    // which matrix and which block of row tiles
-    int segment = 0;
-#pragma unroll
-    for (int s = 1; s < kMaxSegments; ++s) {
-        if (s < p.segments && blockIdx.y >= p.tile_begin[s]) segment = s;
-    }
-    const WeightView w0 = p.w[segment];
-    const uint32_t rt0 = (blockIdx.y - p.tile_begin[segment]) * R;
-    const uint32_t G = p.groups;
-    const uint32_t g0 = (uint32_t)((uint64_t)G * kslice / ksplit);
-    const uint32_t g1 = (uint32_t)((uint64_t)G * (kslice + 1) / ksplit);
-    const uint32_t slice_groups = g1 - g0;
-    // this warp's groups: g0 + warp, g0 + warp + warps, ...
-    const uint32_t ns = slice_groups > (uint32_t)warp ? (slice_groups - warp + warps - 1) / warps : 0;
-    const uint32_t row_tiles_here = min(R, w0.row_tiles > rt0 ? w0.row_tiles - rt0 : 0u);
-    const uint32_t total = ns * row_tiles_here;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[kMaxStages], empty[kMaxStages]
+    uint8_t *ring = smem_raw + 128;
+    __half *xs = reinterpret_cast<__half *>(ring + (size_t)stages * kStageBytes);  // [M][x_stride]
+    float *sx = reinterpret_cast<float *>(xs + (size_t)p.m_rows * x_stride);      // [x_groups][MC]
+    float *red = sx + (size_t)p.x_groups * MC;                                     // [L][PER_CTA]
+    uint32_t *flags = reinterpret_cast<uint32_t *>(red + (size_t)p.local_blocks * PER_CTA);  // [L]
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
+    const uint32_t ring0 = smem_u32(ring);
 
-    // shared memory carve-up
-    float *sx = smem;                                       // [slice_groups][8*NT]
-    float *red = smem + (size_t)(((G + ksplit - 1) / ksplit) + 1) * 8 * NT;  // [R][warps][NW*NT][32][4]
-    float *part = red + (size_t)R * warps * NW * NT * 128;  // [ksplit][R][NW*NT][128] (leader)
-
-    const uint8_t *base[NW];
-    base[0] = w0.tiles;
-    if constexpr (FUSED) base[1] = p.up.tiles;
-
-    auto tile_offset = [&](uint32_t r, uint32_t j) -> size_t {
-        return ((size_t)(rt0 + r) * G + g0 + warp + (size_t)j * warps) * kTileBytes;
-    };
-
-    // ---- start the weight stream before anything else ----
-    TileRegs buffer[U][NW];
-    uint32_t load_r = 0, load_j = 0, issued = 0;
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-        if (issued < total) {
-            size_t offset = tile_offset(load_r, load_j);
-#pragma unroll
-            for (int k = 0; k < NW; ++k) {
-                buffer[u][k].codes = load_stream_16(base[k] + offset + lane * 16);
-                buffer[u][k].meta = load_stream_8(base[k] + offset + kTileCodeBytes + gid * 8);
-            }
-            ++issued;
-            if (++load_j == ns) { load_j = 0; ++load_r; }
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, W);
         }
-    }
-
-    // ---- group sums of x for this K slice (overlaps the loads above) ----
-    {
-        const uint32_t items = slice_groups * (8 * NT) * 4;  // (group, m, quarter)
-        const size_t K = (size_t)G * kGroup;
-        for (uint32_t first = warp * 32; first < items; first += blockDim.x) {
-            uint32_t item = first + lane;
-            uint32_t quarter = item & 3u, m = (item >> 2) % (8 * NT), g = (item >> 2) / (8 * NT);
-            float value = 0.0f;
-            if (item < items && m < p.m_rows) {
-                value = sum_x16<X32>(p.x, (size_t)m * K + (size_t)(g0 + g) * kGroup + 16 * quarter);
-            }
-            value += __shfl_xor_sync(0xffffffffu, value, 1);
-            value += __shfl_xor_sync(0xffffffffu, value, 2);
-            if (quarter == 0 && item < items) sx[g * (8 * NT) + m] = value;
-        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
 
-    float acc[NW][NT][4];
+    bool ok = true;
+    if (warp == W && lane == 0) {
+        // ---- producer: stream this CTA's byte range of the tile stream(s) ----
+        uint32_t issued = 0, ua = u0, g = g_first;
+        for (uint32_t it = 0; ua < u1; ++it) {
+            const uint32_t s = it % stages;
+            if (it >= stages && !mbar_wait(empty0 + 8 * s, ((it / stages) - 1) & 1)) {
+                ok = false;
+                break;
+            }
+            const uint32_t count = min(min(S, G - g), u1 - ua);  // never across a row block
+            const uint32_t bytes = count * kUnitBytes;
+            mbar_expect_tx(full0 + 8 * s, NW * bytes);
+            const uint32_t grb = ua / G;
+            int segment = 0;
 #pragma unroll
-    for (int k = 0; k < NW; ++k)
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[k][n][j] = 0.0f;
+            for (int q = 1; q < kMaxSegments; ++q) {
+                if (q < p.segments && grb >= p.block_begin[q]) segment = q;
+            }
+            const size_t offset = (size_t)(ua - p.block_begin[segment] * G) * kUnitBytes;
+            bulk_copy_to_shared(ring0 + s * kStageBytes, p.w[segment].tiles + offset, bytes, full0 + 8 * s);
+            if constexpr (FUSED) {
+                bulk_copy_to_shared(ring0 + s * kStageBytes + S * kUnitBytes, p.up.tiles + offset, bytes,
+                                    full0 + 8 * s);
+            }
+            ua += count;
+            g += count;
+            if (g == G) g = 0;
+            issued = it + 1;
+        }
+        if (!ok) {
+            atomicExch(p.status, 0x51u);
+            // let the copies already issued land before this CTA's memory is released
+            for (uint32_t it = issued > stages ? issued - stages : 0; it < issued; ++it) {
+                mbar_wait(full0 + 8 * (it % stages), (it / stages) & 1);
+            }
+        }
+    }
 
-    const size_t K = (size_t)G * kGroup;
-    uint32_t cur_r = 0, cur_j = 0;
-    for (uint32_t s0 = 0; s0 < total; s0 += U) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (s0 + u >= total) break;
-            TileRegs cur[NW];
-#pragma unroll
-            for (int k = 0; k < NW; ++k) cur[k] = buffer[u][k];
-            if (issued < total) {  // refill this slot with the tile U steps ahead
-                size_t offset = tile_offset(load_r, load_j);
-#pragma unroll
-                for (int k = 0; k < NW; ++k) {
-                    buffer[u][k].codes = load_stream_16(base[k] + offset + lane * 16);
-                    buffer[u][k].meta = load_stream_8(base[k] + offset + kTileCodeBytes + gid * 8);
-                }
-                ++issued;
-                if (++load_j == ns) { load_j = 0; ++load_r; }
+    // The weights never depend on the previous kernels of the stream; x and y may.
+    // Under programmatic dependent launch this kernel starts while its predecessors
+    // still run: the copies above overlap them, everything below waits for them.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp < W) {
+        const size_t K = (size_t)G * kGroup;
+        const uint32_t m_rows = p.m_rows;
+        const uint32_t k_mine = FUSED ? (uint32_t)warp / S : 0u;  // matrix of this warp's sub-unit
+        const uint32_t j_mine = FUSED ? (uint32_t)warp % S : (uint32_t)warp;
+        // ---- stage x (fp16) for the groups this CTA meets; clear the block sums ----
+        for (uint32_t i = threadIdx.x; i < m_rows * x_count * 8; i += kConsumers) {
+            const uint32_t m = i / (x_count * 8), rest = i % (x_count * 8), li = rest >> 3, c8 = rest & 7u;
+            uint32_t g = windowed ? g_first + li : li;
+            if (g >= G) g %= G;
+            const size_t element = (size_t)m * K + (size_t)g * kGroup + 8 * c8;
+            uint4 value;
+            if constexpr (X32) {
+                const float4 *src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + element);
+                float4 a = __ldg(src), b = __ldg(src + 1);
+                __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+                __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+                value = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                   *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+            } else {
+                value = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.x) + element));
             }
-            const uint32_t g_local = warp + cur_j * warps;  // group index inside the slice
-            const uint32_t g = g0 + g_local;
-            // B fragments: x[m][64 g + 16 t .. +15]
-            uint32_t xb[NT][8];
+            *reinterpret_cast<uint4 *>(xs + (size_t)m * x_stride + li * kGroup + 8 * c8) = value;
+        }
+        for (uint32_t i = threadIdx.x; i < p.local_blocks * PER_CTA; i += kConsumers) red[i] = 0.0f;
+        consumer_barrier(kConsumers);
+        // ---- group sums of the staged x; columns past M stay zero ----
+        for (uint32_t i = threadIdx.x; i < x_count * MC; i += kConsumers) {
+            const uint32_t li = i / MC, m = i % MC;
+            float total = 0.0f;
+            if (m < m_rows) {
+                const uint4 *row = reinterpret_cast<const uint4 *>(xs + (size_t)m * x_stride + li * kGroup);
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                uint32_t m = n * 8 + gid;
-                load_x16<X32>(p.x, (size_t)m * K + (size_t)g * kGroup + 16 * t, m < p.m_rows, xb[n]);
-            }
-            float c[NW][NT][4];
+                for (int c = 0; c < 8; ++c) {
+                    uint4 v = row[c];
+                    const uint32_t reg[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int k = 0; k < NW; ++k)
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) c[k][n][j] = 0.0f;
-#pragma unroll
-            for (int k = 0; k < NW; ++k) {
-                const uint32_t word[4] = {cur[k].codes.x, cur[k].codes.y, cur[k].codes.z, cur[k].codes.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t a[4];
-                    if constexpr (SUBN) {
-                        word_to_codes_subnormal(word[i], a);
-                    } else {
-                        __half2 h[4];
-                        word_to_codes_f16(word[i], h);
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<uint32_t *>(&h[r]);
+                    for (int q = 0; q < 4; ++q) {
+                        float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&reg[q]));
+                        total += f.x + f.y;
                     }
-#pragma unroll
-                    for (int n = 0; n < NT; ++n) mma_16816(c[k][n], a, xb[n][2 * i], xb[n][2 * i + 1]);
                 }
             }
-            // per-group scale and bias in fp32
+            sx[i] = total;
+        }
+        consumer_barrier(kConsumers);
+
+        float acc[4][NT][4];
 #pragma unroll
-            for (int k = 0; k < NW; ++k) {
-                float2 lo = __half22float2(*reinterpret_cast<__half2 *>(&cur[k].meta.x));
-                float2 hi = __half22float2(*reinterpret_cast<__half2 *>(&cur[k].meta.y));
-                if constexpr (SUBN) {
-                    lo.x *= 16777216.0f;  // codes arrived as q * 2^-24
-                    hi.x *= 1048576.0f;   // and 16 q * 2^-24
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[r][n][j] = 0.0f;
+        // Add every warp's sums of a finished row block into the CTA's block sums,
+        // one warp at a time in warp order, so the result does not depend on timing.
+        auto flush = [&](uint32_t lrb) {
+            float *target = red + (size_t)lrb * PER_CTA + k_mine * (NT * 512);
+            for (int turn = 0; turn < W; ++turn) {
+                if (warp == turn) {
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            float4 *at = reinterpret_cast<float4 *>(target) + (n * 4 + r) * 32 + lane;
+                            float4 v = *at;
+                            v.x += acc[r][n][0]; v.y += acc[r][n][1]; v.z += acc[r][n][2]; v.w += acc[r][n][3];
+                            *at = v;
+                            acc[r][n][0] = acc[r][n][1] = acc[r][n][2] = acc[r][n][3] = 0.0f;
+                        }
                 }
+                consumer_barrier(kConsumers);
+            }
+        };
+
+        // ---- main loop: the same stage sequence the producer issues ----
+        uint32_t ua = u0, g = g_first, cur_grb = grb0, grb = grb0;
+        for (uint32_t it = 0; ua < u1; ++it) {
+            const uint32_t s = it % stages;
+            const uint32_t count = min(min(S, G - g), u1 - ua);
+            if (grb != cur_grb) {
+                flush(cur_grb - grb0);
+                cur_grb = grb;
+            }
+            if (!mbar_wait(full0 + 8 * s, (it / stages) & 1)) {
+                ok = false;
+                break;
+            }
+            if (j_mine < count) {
+                const uint32_t li = windowed ? ua - u0 + j_mine : g + j_mine;
+                uint32_t xb[NT][8];
+                float2 sums[NT];
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    float2 sums = *reinterpret_cast<const float2 *>(&sx[g_local * (8 * NT) + n * 8 + 2 * t]);
-                    acc[k][n][0] = fmaf(lo.x, c[k][n][0], fmaf(lo.y, sums.x, acc[k][n][0]));
-                    acc[k][n][1] = fmaf(lo.x, c[k][n][1], fmaf(lo.y, sums.y, acc[k][n][1]));
-                    acc[k][n][2] = fmaf(hi.x, c[k][n][2], fmaf(hi.y, sums.x, acc[k][n][2]));
-                    acc[k][n][3] = fmaf(hi.x, c[k][n][3], fmaf(hi.y, sums.y, acc[k][n][3]));
-                }
-            }
-            if (++cur_j == ns) {  // row tile finished: park this warp's partial sums
+                    const uint32_t m = n * 8 + gid;
+                    if (m < m_rows) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(xs + (size_t)m * x_stride + li * kGroup + 16 * t);
+                        uint4 a = src[0], b = src[1];
+                        xb[n][0] = a.x; xb[n][1] = a.y; xb[n][2] = a.z; xb[n][3] = a.w;
+                        xb[n][4] = b.x; xb[n][5] = b.y; xb[n][6] = b.z; xb[n][7] = b.w;
+                    } else {
 #pragma unroll
-                for (int k = 0; k < NW; ++k)
+                        for (int i = 0; i < 8; ++i) xb[n][i] = 0u;
+                    }
+                    sums[n] = *reinterpret_cast<const float2 *>(&sx[li * MC + n * 8 + 2 * t]);
+                }
+                const uint8_t *unit = ring + (size_t)s * kStageBytes + (size_t)(k_mine * S + j_mine) * kUnitBytes;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const uint8_t *tile = unit + r * kTileBytes;
+                    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + lane * 16);
+                    const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
+                    const uint32_t word[4] = {codes.x, codes.y, codes.z, codes.w};
+                    float c[NT][4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t a[4];
+                        if constexpr (SUBN) {
+                            word_to_codes_subnormal(word[i], a);
+                        } else {
+                            __half2 h[4];
+                            word_to_codes_f16(word[i], h);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) a[q] = *reinterpret_cast<uint32_t *>(&h[q]);
+                        }
+#pragma unroll
+                        for (int n = 0; n < NT; ++n) mma_16816(c[n], a, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
+                    }
+                    float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
+                    float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
+                    if constexpr (SUBN) {
+                        lo.x *= 16777216.0f;  // codes arrived as q * 2^-24
+                        hi.x *= 1048576.0f;   // and 16 q * 2^-24
+                    }
 #pragma unroll
                     for (int n = 0; n < NT; ++n) {
-                        float4 v = make_float4(acc[k][n][0], acc[k][n][1], acc[k][n][2], acc[k][n][3]);
-                        reinterpret_cast<float4 *>(red)[(((size_t)cur_r * warps + warp) * (NW * NT) + k * NT + n) * 32 + lane] = v;
-                        acc[k][n][0] = acc[k][n][1] = acc[k][n][2] = acc[k][n][3] = 0.0f;
+                        acc[r][n][0] = fmaf(lo.x, c[n][0], fmaf(lo.y, sums[n].x, acc[r][n][0]));
+                        acc[r][n][1] = fmaf(lo.x, c[n][1], fmaf(lo.y, sums[n].y, acc[r][n][1]));
+                        acc[r][n][2] = fmaf(hi.x, c[n][2], fmaf(hi.y, sums[n].x, acc[r][n][2]));
+                        acc[r][n][3] = fmaf(hi.x, c[n][3], fmaf(hi.y, sums[n].y, acc[r][n][3]));
                     }
-                cur_j = 0;
-                ++cur_r;
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+            ua += count;
+            g += count;
+            if (g == G) { g = 0; ++grb; }
         }
+        if (ok && range > 0) flush(cur_grb - grb0);
+        if (!ok && lane == 0) atomicExch(p.status, 0x52u);
     }
     __syncthreads();
 
-    // ---- sum over warps, then over the cluster, then the epilogue ----
-    const uint32_t active_warps = min((uint32_t)warps, slice_groups);
-    const uint32_t per_tile = NW * NT * 128;
-    const uint32_t outputs = row_tiles_here * per_tile;
-    cg::cluster_group cluster = cg::this_cluster();
-    float *leader_part = ksplit > 1 ? cluster.map_shared_rank(part, 0) : part;
-    for (uint32_t o = threadIdx.x; o < outputs; o += blockDim.x) {
-        uint32_t r = o / per_tile, inner = o % per_tile;
-        float total_value = 0.0f;
-        for (uint32_t wv = 0; wv < active_warps; ++wv) {
-            total_value += red[((size_t)r * warps + wv) * per_tile + inner];
-        }
-        leader_part[(size_t)kslice * R * per_tile + o] = total_value;
+    // ---- finish every row block this CTA touched ----
+    if (range == 0) return;
+    const uint32_t grb_last = (u1 - 1) / G;
+    // (1) park the sums of row blocks that other CTAs share
+    for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
+        const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
+        if (contributed == G) continue;
+        const uint32_t first_cta = (uint32_t)((((uint64_t)grb * G + 1) * ctas + U - 1) / U) - 1;
+        const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
+        float *slot = p.scratch + ((size_t)grb * p.slots + (cta - first_cta)) * PER_CTA;
+        for (uint32_t o = threadIdx.x; o < PER_CTA; o += blockDim.x) slot[o] = mine[o];
     }
-    if (ksplit > 1) {
-        cluster.sync();
-        if (kslice != 0) return;
-    } else {
-        __syncthreads();
+    __syncthreads();
+    // (2) one thread publishes them and learns which blocks this CTA completes
+    if (threadIdx.x == 0) {
+        __threadfence();
+        for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
+            const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
+            uint32_t finish = 1;
+            if (contributed != G) {
+                const uint32_t before = atomicAdd(p.counters + grb, contributed);
+                finish = before + contributed == G ? 2u : 0u;
+                if (finish) p.counters[grb] = 0;  // ready for the next launch
+            }
+            flags[grb - grb0] = finish;
+        }
+        __threadfence();
     }
-
-    const uint32_t results = row_tiles_here * NT * 128;  // fused: gate/up pairs collapse
-    for (uint32_t o = threadIdx.x; o < results; o += blockDim.x) {
-        uint32_t r = o / (NT * 128), inner = o % (NT * 128);
-        uint32_t n = inner >> 7, ln = (inner >> 2) & 31u, j = inner & 3u;
-        uint32_t row = (rt0 + r) * kTileRows + (ln >> 2) + 8 * (j >> 1);
-        uint32_t m = n * 8 + 2 * (ln & 3u) + (j & 1u);
-        if (row >= w0.rows || m >= p.m_rows) continue;
-        float value = 0.0f, second = 0.0f;
-        for (uint32_t ks = 0; ks < ksplit; ++ks) {
-            const float *src = part + ((size_t)ks * R + r) * per_tile;
-            value += src[inner];
-            if constexpr (FUSED) second += src[NT * 128 + inner];
+    __syncthreads();
+    // (3) outputs of the blocks that are complete here
+    for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
+        const uint32_t finish = flags[grb - grb0];
+        if (finish == 0) continue;
+        const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
+        const uint32_t first_cta = (uint32_t)((((uint64_t)grb * G + 1) * ctas + U - 1) / U) - 1;
+        const uint32_t last_cta = (uint32_t)((((uint64_t)(grb + 1) * G) * ctas + U - 1) / U) - 1;
+        const uint32_t contributors = last_cta - first_cta + 1;
+        const float *slots = p.scratch + ((size_t)grb * p.slots) * PER_CTA;
+        int segment = 0;
+#pragma unroll
+        for (int q = 1; q < kMaxSegments; ++q) {
+            if (q < p.segments && grb >= p.block_begin[q]) segment = q;
         }
-        if constexpr (FUSED) {
-            // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
-            value = (value / (1.0f + __expf(-value))) * second;
-        }
-        if (p.residual != nullptr && segment == 0) {
-            size_t at = (size_t)m * p.ld_residual + row;
-            value += p.residual_dtype == kF32 ? reinterpret_cast<const float *>(p.residual)[at]
-                                              : __half2float(reinterpret_cast<const __half *>(p.residual)[at]);
-        }
-        size_t at = (size_t)m * p.ldy[segment] + row;
-        if (p.y_dtype == kF32) {
-            reinterpret_cast<float *>(p.y[segment])[at] = value;
-        } else {
-            reinterpret_cast<__half *>(p.y[segment])[at] = __float2half_rn(value);
+        const uint32_t rb = grb - p.block_begin[segment];
+        const uint32_t rows = p.w[segment].rows;
+        for (uint32_t o = threadIdx.x; o < NT * 4 * 128; o += blockDim.x) {
+            const uint32_t n = o / 512, rr = (o >> 7) & 3u, ln = (o >> 2) & 31u, j = o & 3u;
+            const uint32_t row = rb * 64 + rr * kTileRows + (ln >> 2) + 8 * (j >> 1);
+            const uint32_t m = n * 8 + 2 * (ln & 3u) + (j & 1u);
+            if (row >= rows || m >= p.m_rows) continue;
+            float value = 0.0f, second = 0.0f;
+            if (finish == 1) {
+                value = mine[o];
+                if constexpr (FUSED) second = mine[NT * 512 + o];
+            } else {  // the slots in CTA order: the same sum whichever CTA arrives last
+                for (uint32_t q = 0; q < contributors; ++q) {
+                    value += __ldcg(slots + (size_t)q * PER_CTA + o);
+                    if constexpr (FUSED) second += __ldcg(slots + (size_t)q * PER_CTA + NT * 512 + o);
+                }
+            }
+            if constexpr (FUSED) {
+                // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
+                value = (value / (1.0f + __expf(-value))) * second;
+            }
+            if (p.residual != nullptr && segment == 0) {
+                const size_t at = (size_t)m * p.ld_residual + row;
+                value += p.residual_dtype == kF32 ? reinterpret_cast<const float *>(p.residual)[at]
+                                                  : __half2float(reinterpret_cast<const __half *>(p.residual)[at]);
+            }
+            const size_t at = (size_t)m * p.ldy[segment] + row;
+            if (p.y_dtype == kF32) {
+                reinterpret_cast<float *>(p.y[segment])[at] = value;
+            } else {
+                reinterpret_cast<__half *>(p.y[segment])[at] = __float2half_rn(value);
+            }
         }
     }
 }
 
-template <int NT, bool FUSED, bool SUBN, bool X32, int U>
-cudaError_t launch_instance(const GemvParams &p, dim3 grid, int threads, size_t smem_bytes,
-                            cudaStream_t stream) {
-    auto kernel = gemv_kernel<NT, FUSED, SUBN, X32, U>;
-    if (smem_bytes > 48 * 1024) {
+template <int NT, bool FUSED, bool SUBN, bool X32>
+cudaError_t launch_instance(const GemvParams &p, unsigned ctas, int threads, size_t smem_bytes,
+                            bool dependent_launch, cudaStream_t stream) {
+    auto kernel = gemv_kernel<NT, FUSED, SUBN, X32>;
+    static size_t configured = 0;  // per instantiation
+    if (smem_bytes > configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)smem_bytes);
         if (status != cudaSuccess) return status;
+        configured = smem_bytes;
     }
     cudaLaunchConfig_t config = {};
-    config.gridDim = grid;
+    config.gridDim = dim3(ctas);
     config.blockDim = dim3(threads);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = grid.x;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = 1;
+    config.numAttrs = dependent_launch ? 1 : 0;
     return cudaLaunchKernelEx(&config, kernel, p);
 }
 
-template <int NT, bool FUSED, bool X32>
-cudaError_t launch_by_flags(const GemvParams &p, bool subnormal, int depth, dim3 grid, int threads,
-                            size_t smem_bytes, cudaStream_t stream) {
+template <int NT, bool FUSED>
+cudaError_t launch_by_flags(const GemvParams &p, bool subnormal, bool x32, unsigned ctas, int threads,
+                            size_t smem_bytes, bool pdl, cudaStream_t stream) {
     if (subnormal) {
-        return depth >= 8 ? launch_instance<NT, FUSED, true, X32, (FUSED || NT > 1) ? 4 : 8>(p, grid, threads, smem_bytes, stream)
-                          : launch_instance<NT, FUSED, true, X32, (FUSED || NT > 2) ? 2 : 4>(p, grid, threads, smem_bytes, stream);
+        return x32 ? launch_instance<NT, FUSED, true, true>(p, ctas, threads, smem_bytes, pdl, stream)
+                   : launch_instance<NT, FUSED, true, false>(p, ctas, threads, smem_bytes, pdl, stream);
     }
-    return depth >= 8 ? launch_instance<NT, FUSED, false, X32, (FUSED || NT > 1) ? 4 : 8>(p, grid, threads, smem_bytes, stream)
-                      : launch_instance<NT, FUSED, false, X32, (FUSED || NT > 2) ? 2 : 4>(p, grid, threads, smem_bytes, stream);
+    return x32 ? launch_instance<NT, FUSED, false, true>(p, ctas, threads, smem_bytes, pdl, stream)
+               : launch_instance<NT, FUSED, false, false>(p, ctas, threads, smem_bytes, pdl, stream);
 }
 
 }  // namespace
 
-uint32_t gemv_max_m() { return 32; }
+uint32_t gemv_max_m() { return 16; }
 
-// variant encoding (0 = heuristics): bits 0-3 ksplit, 4-7 warps, 8-11 R,
-// bit 12 deep prefetch, bit 13 exact-fp16 code path instead of subnormals
-cudaError_t launch_gemv(const GemvArgs &args, int variant, int sm_count, cudaStream_t stream) {
-    GemvParams p = {};
+// variant encoding (0 = heuristics): bits 0-3 CTAs per SM, 8-11 ring stages,
+// bit 13 exact-fp16 codes instead of subnormals, bit 14 no programmatic
+// dependent launch
+cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan) {
     const uint32_t G = args.w[0].groups;
-    uint32_t total_row_tiles = 0;
-    for (int s = 0; s < args.segments; ++s) total_row_tiles += args.w[s].row_tiles;
+    const int NT = args.m_rows <= 8 ? 1 : 2;
+    const int NW = args.fused_silu ? 2 : 1;
+    uint32_t blocks = 0;
+    for (int s = 0; s < args.segments; ++s) blocks += ceil_div(args.w[s].row_tiles, kBlockTiles);
+    const uint64_t units64 = (uint64_t)blocks * G;
+    if (units64 == 0 || units64 > 0x7fffffffull) return cudaErrorInvalidValue;
+    const uint32_t units = (uint32_t)units64;
 
-    int ksplit = variant & 0xf, warps = (variant >> 4) & 0xf, R = (variant >> 8) & 0xf;
-    const bool deep = (variant >> 12) & 1, exact_codes = (variant >> 13) & 1;
-    if (warps == 0) warps = 8;
-    const int NT = args.m_rows <= 8 ? 1 : (args.m_rows <= 16 ? 2 : 4);
-    if (R == 0) {
-        // enough CTAs for ~4 per SM, but rows*K per CTA not tiny
-        R = 1;
-        while (R < 4 && NT == 1 && total_row_tiles / (R * 2) >= (uint32_t)sm_count * 4 && G * R < 256) R *= 2;
-    }
-    if (ksplit == 0) {
-        ksplit = 1;
-        uint32_t ctas = ceil_div(total_row_tiles, R);
-        while (ksplit < 8 && ctas * ksplit < (uint32_t)sm_count * 4 && G / (ksplit * 2) >= (uint32_t)warps * 2) ksplit *= 2;
-    }
-    if ((uint32_t)ksplit > G) ksplit = 1;
+    int per_sm = variant & 0xf, stages = (variant >> 8) & 0xf;
+    if (per_sm == 0) per_sm = 1;
+    if (stages == 0) stages = 3;
+    if (stages > kMaxStages) stages = kMaxStages;
+    uint32_t ctas = (uint32_t)sm_count * per_sm;
+    const uint32_t stage_groups = 8 / NW;
+    const uint32_t by_work = units / stage_groups > 0 ? units / stage_groups : 1;  // a stage or more per CTA
+    if (ctas > by_work) ctas = by_work;
+    const uint32_t max_range = ceil_div(units, ctas);
+    const uint32_t needed = ceil_div(max_range, stage_groups) + 1;
+    if ((uint32_t)stages > needed) stages = needed < 2 ? 2 : needed;
 
+    plan->ctas = ctas;
+    plan->threads = 9 * 32;
+    plan->stages = stages;
+    plan->stage_units = stage_groups;
+    plan->total_units = units;
+    plan->blocks = blocks;
+    plan->x_groups = max_range < G ? max_range : G;
+    plan->local_blocks = (max_range - 1) / G + 2;
+    plan->slots = ceil_div(G, units / ctas > 0 ? units / ctas : 1) + 1;
+    const size_t per_cta_floats = (size_t)NW * NT * 4 * 128;
+    plan->scratch_bytes = (size_t)blocks * plan->slots * per_cta_floats * 4;
+    plan->counter_bytes = (size_t)blocks * 4;
+    plan->smem_bytes = 128 + (size_t)stages * 8 * kUnitBytes +
+                       (size_t)args.m_rows * (plan->x_groups * kGroup + 8) * 2 +
+                       (size_t)plan->x_groups * 8 * NT * 4 +
+                       (size_t)plan->local_blocks * per_cta_floats * 4 + (size_t)plan->local_blocks * 4 + 16;
+    if (plan->smem_bytes > 220 * 1024) return cudaErrorInvalidValue;
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant, cudaStream_t stream) {
+    GemvParams p = {};
     uint32_t blocks = 0;
     for (int s = 0; s < args.segments; ++s) {
         p.w[s] = args.w[s];
         p.y[s] = args.y[s];
         p.ldy[s] = args.ldy[s];
-        p.tile_begin[s] = blocks;
-        blocks += ceil_div(args.w[s].row_tiles, R);
+        p.block_begin[s] = blocks;
+        blocks += ceil_div(args.w[s].row_tiles, kBlockTiles);
     }
-    p.tile_begin[args.segments] = blocks;
+    for (int s = args.segments; s <= kMaxSegments; ++s) p.block_begin[s] = blocks;
     p.segments = args.segments;
     p.up = args.up;
     p.x = args.x;
     p.residual = args.residual;
+    p.status = args.status;
+    p.scratch = args.scratch;
+    p.counters = args.counters;
+    p.slots = plan.slots;
     p.ld_residual = args.ld_residual;
     p.m_rows = args.m_rows;
-    p.groups = G;
-    p.row_tiles_per_cta = R;
-    p.x_dtype = args.x_dtype;
+    p.groups = args.w[0].groups;
+    p.stages = plan.stages;
+    p.x_groups = plan.x_groups;
+    p.local_blocks = plan.local_blocks;
+    p.total_units = plan.total_units;
     p.y_dtype = args.y_dtype;
     p.residual_dtype = args.residual_dtype;
-    if (blocks == 0) return cudaSuccess;
-
-    const int NW = args.fused_silu ? 2 : 1;
-    size_t smem_floats = (size_t)(ceil_div(G, ksplit) + 1) * 8 * NT      // sx
-                         + (size_t)R * warps * NW * NT * 128             // red
-                         + (size_t)ksplit * R * NW * NT * 128;           // part
-    size_t smem_bytes = smem_floats * sizeof(float);
-    if (smem_bytes > 200 * 1024) return cudaErrorInvalidValue;
-    dim3 grid(ksplit, blocks);
-    const int threads = warps * 32;
-    const bool subnormal = !exact_codes;
-    const bool x32 = args.x_dtype == kF32;
-    const int depth = deep ? 8 : 4;
-
-#define Q4B_DISPATCH(NTV, FUSEDV)                                                                   \
-    return x32 ? launch_by_flags<NTV, FUSEDV, true>(p, subnormal, depth, grid, threads, smem_bytes, stream) \
-               : launch_by_flags<NTV, FUSEDV, false>(p, subnormal, depth, grid, threads, smem_bytes, stream)
+    const bool exact_codes = (variant >> 13) & 1, pdl = ((variant >> 14) & 1) == 0;
+    const bool subnormal = !exact_codes, x32 = args.x_dtype == kF32;
+    const int NT = args.m_rows <= 8 ? 1 : 2;
     if (args.fused_silu) {
-        if (NT == 1) { Q4B_DISPATCH(1, true); }
-        if (NT == 2) { Q4B_DISPATCH(2, true); }
-        Q4B_DISPATCH(4, true);
+        return NT == 1 ? launch_by_flags<1, true>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream)
+                       : launch_by_flags<2, true>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream);
     }
-    if (NT == 1) { Q4B_DISPATCH(1, false); }
-    if (NT == 2) { Q4B_DISPATCH(2, false); }
-    Q4B_DISPATCH(4, false);
-#undef Q4B_DISPATCH
+    return NT == 1 ? launch_by_flags<1, false>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream)
+                   : launch_by_flags<2, false>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream);
 }
 
 }  // namespace q4b

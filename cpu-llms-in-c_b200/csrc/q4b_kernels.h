@@ -40,9 +40,19 @@ struct GemvArgs {
     const void *residual;  // [M][ld_residual] or null (segment 0 only)
     int residual_dtype;
     uint32_t ld_residual;
+    uint32_t *status;      // device-visible word that receives a code when a wait expires
+    float *scratch;        // global partial-sum slots (plan.scratch_bytes)
+    uint32_t *counters;    // zero-initialised, self-resetting (plan.counter_bytes)
+};
+// launch geometry and the scratch a launch needs, derived from the shapes alone
+struct GemvPlan {
+    uint32_t ctas, threads, stages, stage_units, total_units, blocks;
+    uint32_t x_groups, local_blocks, slots;
+    size_t smem_bytes, scratch_bytes, counter_bytes;
 };
 // variant: 0 = default; other values select alternatives for A/B measurements
-cudaError_t launch_gemv(const GemvArgs &args, int variant, int sm_count, cudaStream_t stream);
+cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan);
+cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant, cudaStream_t stream);
 uint32_t gemv_max_m();
 
 }  // namespace q4b
