@@ -277,8 +277,6 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
         GemvPlan plan;
         cudaError_t status = plan_gemv(block, context->variant, context->sm_count, &plan);
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv plan", status);
-        int code = ensure_scratch(context, plan, error_message, error_capacity);
-        if (code != Q4B_OK) return code;
         block.status = context->status_device;
         block.scratch = context->scratch;
         block.counters = context->counters;
@@ -743,6 +741,38 @@ int q4b_graph_begin(q4b_context *context, char *error_message, size_t error_capa
         set_error(error_message, error_capacity, "already recording");
         return Q4B_BAD_ARGUMENT;
     }
+int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
+                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second, char *error_message,
+                   size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (gigabytes_per_second == nullptr || bytes < (1u << 20) || iterations < 1 || ctas_per_sm < 1 || mode < 0 ||
+        mode > 2 || context->capturing) {
+        set_error(error_message, error_capacity, "invalid probe arguments");
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (mode != 0 && stage_bytes != 0) bytes -= bytes % ((size_t)stage_bytes);
+    uint8_t *buffer = nullptr;
+    Q4B_CUDA(cudaMalloc(&buffer, bytes + 4), "cudaMalloc of the probe buffer");
+    cudaError_t status = cudaMemsetAsync(buffer, 0x5a, bytes + 4, context->stream);
+    uint32_t *sink = reinterpret_cast<uint32_t *>(buffer + bytes);
+    const int ctas = context->sm_count * ctas_per_sm;
+    if (status == cudaSuccess) status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_start, context->stream);
+    for (int i = 0; i < iterations && status == cudaSuccess; ++i) {
+        status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
+    }
+    context->launches += iterations + 1;
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_stop, context->stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    float ms = 0.0f;
+    if (status == cudaSuccess) status = cudaEventElapsedTime(&ms, context->timer_start, context->timer_stop);
+    cudaFree(buffer);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "probe", status);
+    *gigabytes_per_second = (double)bytes * iterations / (ms * 1e-3) / 1e9;
+    return Q4B_OK;
+}
+
     Q4B_CUDA(cudaStreamBeginCapture(context->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
     context->capturing = true;
     return Q4B_OK;

@@ -30,6 +30,22 @@
 // and runs to its normal end.
 #include "q4b_kernels.h"
 
+#ifdef Q4B_TRACE
+__device__ long long q4b_trace_buffer[1024 * 16];
+#define Q4B_STAMP(slot) do { if (threadIdx.x == 0) q4b_trace_buffer[blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+#define Q4B_ADD(slot, value) do { if (threadIdx.x == 0) q4b_trace_buffer[blockIdx.x * 16 + (slot)] += (value); } while (0)
+extern "C" int q4b_trace_read(long long *out, int count) {
+    return (int)cudaMemcpyFromSymbol(out, q4b_trace_buffer, sizeof(long long) * count);
+}
+extern "C" int q4b_trace_clear(void) {
+    static long long zeros[1024 * 16];
+    return (int)cudaMemcpyToSymbol(q4b_trace_buffer, zeros, sizeof(zeros));
+}
+#else
+#define Q4B_STAMP(slot) do { } while (0)
+#define Q4B_ADD(slot, value) do { } while (0)
+#endif
+
 namespace q4b {
 
 namespace {
@@ -142,6 +158,7 @@ gemv_kernel(const GemvParams p) {
     // dependents may start at once: all they do before their own wait is prefetch weights
     asm volatile("griddepcontrol.launch_dependents;");
 
+    Q4B_STAMP(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, t = lane & 3;
     const uint32_t G = p.groups, U = p.total_units, ctas = gridDim.x, cta = blockIdx.x;
@@ -215,7 +232,9 @@ gemv_kernel(const GemvParams p) {
     // The weights never depend on the previous kernels of the stream; x and y may.
     // Under programmatic dependent launch this kernel starts while its predecessors
     // still run: the copies above overlap them, everything below waits for them.
+    Q4B_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    Q4B_STAMP(2);
 
     if (warp < W) {
         const size_t K = (size_t)G * kGroup;
@@ -243,6 +262,7 @@ gemv_kernel(const GemvParams p) {
         }
         for (uint32_t i = threadIdx.x; i < p.local_blocks * PER_CTA; i += kConsumers) red[i] = 0.0f;
         consumer_barrier(kConsumers);
+        Q4B_STAMP(3);
         // ---- group sums of the staged x; columns past M stay zero ----
         for (uint32_t i = threadIdx.x; i < x_count * MC; i += kConsumers) {
             const uint32_t li = i / MC, m = i % MC;
@@ -263,6 +283,7 @@ gemv_kernel(const GemvParams p) {
             sx[i] = total;
         }
         consumer_barrier(kConsumers);
+        Q4B_STAMP(4);
 
         float acc[4][NT][4];
 #pragma unroll
@@ -301,10 +322,15 @@ gemv_kernel(const GemvParams p) {
                 flush(cur_grb - grb0);
                 cur_grb = grb;
             }
+#ifdef Q4B_TRACE
+            const long long wait_begin = clock64();
+#endif
             if (!mbar_wait(full0 + 8 * s, (it / stages) & 1)) {
                 ok = false;
                 break;
             }
+            Q4B_ADD(8, clock64() - wait_begin);
+            Q4B_ADD(9, 1);
             if (j_mine < count) {
                 const uint32_t li = windowed ? ua - u0 + j_mine : g + j_mine;
                 uint32_t xb[NT][8];
@@ -366,10 +392,12 @@ gemv_kernel(const GemvParams p) {
             g += count;
             if (g == G) { g = 0; ++grb; }
         }
+        Q4B_STAMP(5);
         if (ok && range > 0) flush(cur_grb - grb0);
         if (!ok && lane == 0) atomicExch(p.status, 0x52u);
     }
     __syncthreads();
+    Q4B_STAMP(6);
 
     // ---- finish every row block this CTA touched ----
     if (range == 0) return;
@@ -448,6 +476,7 @@ gemv_kernel(const GemvParams p) {
             }
         }
     }
+    Q4B_STAMP(7);
 }
 
 template <int NT, bool FUSED, bool SUBN, bool X32>

@@ -55,4 +55,8 @@ cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan 
 cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant, cudaStream_t stream);
 uint32_t gemv_max_m();
 
+// ---- q4b_probe.cu ----
+cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,
+                         uint32_t *sink, cudaStream_t stream);
+
 }  // namespace q4b

@@ -50,10 +50,10 @@ def library() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = library_path()
+    path = os.environ.get("Q4B_LIBRARY") or library_path()  # another build of the same library
     from . import _build
     try:
-        if _build.stale():
+        if path == library_path() and _build.stale():
             _build.build()
     except Exception as error:  # no nvcc on this machine: use the shipped binary
         if not os.path.exists(path):
@@ -90,6 +90,7 @@ def library() -> ctypes.CDLL:
         "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
                                          ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
+        "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_graph_begin": (_int, [_vp] + err),
         "q4b_graph_end": (_int, [_vp, ctypes.POINTER(_vp)] + err),
@@ -347,4 +348,12 @@ class Q4Context:
     def graph_end(self) -> Q4Graph:
         handle = _vp()
         self._check(library().q4b_graph_end(self.handle, ctypes.byref(handle), self._err, _ERR))
+    def probe_read(self, mode: int = 0, nbytes: int = 2 << 30, ctas_per_sm: int = 2, stages: int = 4,
+                   stage_bytes: int = 18432, iterations: int = 5) -> float:
+        """HBM read bandwidth in GB/s (see q4b_probe_read)."""
+        out = ctypes.c_double(0.0)
+        self._check(library().q4b_probe_read(self.handle, mode, nbytes, ctas_per_sm, stages, stage_bytes,
+                                             iterations, ctypes.byref(out), self._err, _ERR))
+        return out.value
+
         return Q4Graph(self, handle.value)

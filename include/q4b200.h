@@ -163,3 +163,14 @@ void q4b_graph_free(q4b_graph *graph);
 }
 #endif
 #endif
+/* ---- read-bandwidth probe: the role of the reference's device-memory probe
+ * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):
+ * reads `bytes` of device memory `iterations` times and reports GB/s from CUDA
+ * events.  mode 0 = plain 16-byte loads; 1 = the GEMV kernel's bulk-copy ring
+ * with idle consumers; 2 = the same ring with the consumers reading the staged
+ * bytes.  ctas_per_sm, stages and stage_bytes shape the ring modes.  Synchronous;
+ * allocates and frees its own buffer. */
+int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
+                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second,
+                   char *error_message, size_t error_capacity);
+
