@@ -258,8 +258,11 @@ int ensure_scratch(q4b_context *context, const GemvPlan &plan, char *error_messa
     return Q4B_OK;
 }
 
-// one launch sequence for any M: GEMV kernel up to its row limit, row blocks above
-int run_projection(q4b_context *context, GemvArgs args, char *error_message, size_t error_capacity) {
+// one launch sequence for any M: GEMV kernel up to its row limit, row blocks above.
+// With built_in_scratch the split-K scratch is the library's file-scope device
+// array and nothing is allocated, grown or freed.
+int run_projection(q4b_context *context, GemvArgs args, char *error_message, size_t error_capacity,
+                   bool built_in_scratch = false) {
     const uint32_t limit = gemv_max_m();
     const uint32_t total = args.m_rows;
     const size_t K = (size_t)args.w[0].groups * kGroup;
@@ -278,8 +281,26 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
         cudaError_t status = plan_gemv(block, context->variant, context->sm_count, &plan);
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv plan", status);
         block.status = context->status_device;
-        block.scratch = context->scratch;
-        block.counters = context->counters;
+        if (built_in_scratch) {
+            size_t scratch_bytes = 0, counter_bytes = 0;
+            status = gemv_static_scratch(&block.scratch, &block.counters, &scratch_bytes, &counter_bytes);
+            if (status != cudaSuccess) return device_failure(error_message, error_capacity, "built-in scratch", status);
+            if (plan.scratch_bytes > scratch_bytes || plan.counter_bytes > counter_bytes) {
+                set_error(error_message, error_capacity,
+                          "this shape needs %zu bytes of scratch and %zu of counters; the built-in scratch holds "
+                          "%zu and %zu -- use q4b_matmul, which allocates",
+                          plan.scratch_bytes, plan.counter_bytes, scratch_bytes, counter_bytes);
+                return Q4B_BAD_ARGUMENT;
+            }
+            // the array keeps whatever the previous call left: the counters must start at zero
+            status = cudaMemsetAsync(block.counters, 0, plan.counter_bytes, context->stream);
+            if (status != cudaSuccess) return device_failure(error_message, error_capacity, "counter reset", status);
+        } else {
+            int code = ensure_scratch(context, plan, error_message, error_capacity);
+            if (code != Q4B_OK) return code;
+            block.scratch = context->scratch;
+            block.counters = context->counters;
+        }
         status = launch_gemv(block, plan, context->variant, context->stream);
         if (!context->capturing) ++context->launches;  // recorded launches count at replay
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv launch", status);
@@ -575,6 +596,27 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
     return run_projection(context, args, error_message, error_capacity);
 }
 
+int q4b_matmul_no_alloc(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
+                        uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, char *error_message,
+                        size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    code = check_matmul_arguments(context, weight, x, x_dtype, m_rows, y, y_dtype, ldy, error_message,
+                                  error_capacity);
+    if (code != Q4B_OK) return code;
+    GemvArgs args = {};
+    args.w[0] = weight->view;
+    args.y[0] = y;
+    args.ldy[0] = ldy;
+    args.segments = 1;
+    args.x = x;
+    args.x_dtype = x_dtype;
+    args.m_rows = m_rows;
+    args.y_dtype = y_dtype;
+    args.residual_dtype = kNone;
+    return run_projection(context, args, error_message, error_capacity, true);
+}
+
 int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int count, const void *x,
                      int x_dtype, uint32_t m_rows, void *const *y, int y_dtype, const uint32_t *ldy,
                      char *error_message, size_t error_capacity) {
@@ -699,6 +741,38 @@ int q4b_gate_up_silu_host(q4b_context *context, const q4b_weight *gate, const q4
                      error_capacity);
 }
 
+int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
+                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second, char *error_message,
+                   size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (gigabytes_per_second == nullptr || bytes < (1u << 20) || iterations < 1 || ctas_per_sm < 1 || mode < 0 ||
+        mode > 2 || context->capturing) {
+        set_error(error_message, error_capacity, "invalid probe arguments");
+        return Q4B_BAD_ARGUMENT;
+    }
+    if (mode != 0 && stage_bytes != 0) bytes -= bytes % ((size_t)stage_bytes);
+    uint8_t *buffer = nullptr;
+    Q4B_CUDA(cudaMalloc(&buffer, bytes + 4), "cudaMalloc of the probe buffer");
+    cudaError_t status = cudaMemsetAsync(buffer, 0x5a, bytes + 4, context->stream);
+    uint32_t *sink = reinterpret_cast<uint32_t *>(buffer + bytes);
+    const int ctas = context->sm_count * ctas_per_sm;
+    if (status == cudaSuccess) status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_start, context->stream);
+    for (int i = 0; i < iterations && status == cudaSuccess; ++i) {
+        status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
+    }
+    context->launches += iterations + 1;
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_stop, context->stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    float ms = 0.0f;
+    if (status == cudaSuccess) status = cudaEventElapsedTime(&ms, context->timer_start, context->timer_stop);
+    cudaFree(buffer);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "probe", status);
+    *gigabytes_per_second = (double)bytes * iterations / (ms * 1e-3) / 1e9;
+    return Q4B_OK;
+}
+
 int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
@@ -741,38 +815,6 @@ int q4b_graph_begin(q4b_context *context, char *error_message, size_t error_capa
         set_error(error_message, error_capacity, "already recording");
         return Q4B_BAD_ARGUMENT;
     }
-int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
-                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second, char *error_message,
-                   size_t error_capacity) {
-    int code = check_context(context, error_message, error_capacity);
-    if (code != Q4B_OK) return code;
-    if (gigabytes_per_second == nullptr || bytes < (1u << 20) || iterations < 1 || ctas_per_sm < 1 || mode < 0 ||
-        mode > 2 || context->capturing) {
-        set_error(error_message, error_capacity, "invalid probe arguments");
-        return Q4B_BAD_ARGUMENT;
-    }
-    if (mode != 0 && stage_bytes != 0) bytes -= bytes % ((size_t)stage_bytes);
-    uint8_t *buffer = nullptr;
-    Q4B_CUDA(cudaMalloc(&buffer, bytes + 4), "cudaMalloc of the probe buffer");
-    cudaError_t status = cudaMemsetAsync(buffer, 0x5a, bytes + 4, context->stream);
-    uint32_t *sink = reinterpret_cast<uint32_t *>(buffer + bytes);
-    const int ctas = context->sm_count * ctas_per_sm;
-    if (status == cudaSuccess) status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
-    if (status == cudaSuccess) status = cudaEventRecord(context->timer_start, context->stream);
-    for (int i = 0; i < iterations && status == cudaSuccess; ++i) {
-        status = launch_probe(mode, buffer, bytes, ctas, stages, stage_bytes, sink, context->stream);
-    }
-    context->launches += iterations + 1;
-    if (status == cudaSuccess) status = cudaEventRecord(context->timer_stop, context->stream);
-    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
-    float ms = 0.0f;
-    if (status == cudaSuccess) status = cudaEventElapsedTime(&ms, context->timer_start, context->timer_stop);
-    cudaFree(buffer);
-    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "probe", status);
-    *gigabytes_per_second = (double)bytes * iterations / (ms * 1e-3) / 1e9;
-    return Q4B_OK;
-}
-
     Q4B_CUDA(cudaStreamBeginCapture(context->stream, cudaStreamCaptureModeThreadLocal), "begin capture");
     context->capturing = true;
     return Q4B_OK;

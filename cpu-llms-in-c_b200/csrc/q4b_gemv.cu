@@ -518,6 +518,44 @@ cudaError_t launch_by_flags(const GemvParams &p, bool subnormal, bool x32, unsig
 
 uint32_t gemv_max_m() { return 16; }
 
+// ---------------------------------------------------------------------------
+// Scratch that exists without any allocation call: file-scope device arrays,
+// part of the library image, held by every GPU that loads it until the process
+// exits.  In host code the names below are only stand-ins for the symbols; the
+// device addresses come from cudaGetSymbolAddress, looked up once per device
+// with that device current.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB of partial-sum slots
+constexpr size_t kStaticCounterCount = 4096;      // one arrival counter per 64-row block
+static __device__ __align__(256) float q4b_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) uint32_t q4b_static_counters[kStaticCounterCount];
+
+cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
+                                size_t *counter_bytes) {
+    constexpr int kMaxDevices = 64;
+    static float *scratch_of[kMaxDevices];
+    static uint32_t *counters_of[kMaxDevices];
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return status;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (scratch_of[device] == nullptr) {
+        float *scratch_address = nullptr;
+        uint32_t *counter_address = nullptr;
+        status = cudaGetSymbolAddress(reinterpret_cast<void **>(&scratch_address), q4b_static_scratch);
+        if (status != cudaSuccess) return status;
+        status = cudaGetSymbolAddress(reinterpret_cast<void **>(&counter_address), q4b_static_counters);
+        if (status != cudaSuccess) return status;
+        counters_of[device] = counter_address;
+        scratch_of[device] = scratch_address;
+    }
+    *scratch = scratch_of[device];
+    *counters = counters_of[device];
+    *scratch_bytes = kStaticScratchBytes;
+    *counter_bytes = kStaticCounterCount * sizeof(uint32_t);
+    return cudaSuccess;
+}
+
 // variant encoding (0 = heuristics): bits 0-3 CTAs per SM, 8-11 ring stages,
 // bit 13 exact-fp16 codes instead of subnormals, bit 14 no programmatic
 // dependent launch

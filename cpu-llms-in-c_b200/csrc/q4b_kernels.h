@@ -54,6 +54,9 @@ struct GemvPlan {
 cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan);
 cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant, cudaStream_t stream);
 uint32_t gemv_max_m();
+// device addresses and sizes of the library's built-in (never allocated) scratch on the current device
+cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
+                                size_t *counter_bytes);
 
 // ---- q4b_probe.cu ----
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,

@@ -83,14 +83,15 @@ def library() -> ctypes.CDLL:
         "q4b_weight_info": (_int, [_vp, ctypes.POINTER(_u32), ctypes.POINTER(_u32), ctypes.POINTER(_u64)]),
         "q4b_weight_unpack": (_int, [_vp, _vp, _vp, _vp, _vp] + err),
         "q4b_matmul": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, _u32, _vp, _int, _u32] + err),
+        "q4b_matmul_no_alloc": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, _u32] + err),
         "q4b_matmul_group": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, _int, _u32, ctypes.POINTER(_vp),
                                     _int, ctypes.POINTER(_u32)] + err),
         "q4b_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int, _u32] + err),
         "q4b_matmul_host": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
                                          ctypes.POINTER(ctypes.c_double)] + err),
-        "q4b_timer_start": (_int, [_vp] + err),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_graph_begin": (_int, [_vp] + err),
         "q4b_graph_end": (_int, [_vp, ctypes.POINTER(_vp)] + err),
@@ -304,6 +305,12 @@ class Q4Context:
                                          weight.rows if ldy is None else ldy, residual_ptr, residual_dtype,
                                          ld_residual, self._err, _ERR))
 
+    def matmul_no_alloc(self, weight: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int,
+                        y_dtype: int = F16, ldy: int | None = None):
+        """q4b_matmul with the library's built-in scratch array: allocates nothing."""
+        self._check(library().q4b_matmul_no_alloc(self.handle, weight.handle, x_ptr, x_dtype, m_rows, y_ptr,
+                                                  y_dtype, weight.rows if ldy is None else ldy, self._err, _ERR))
+
     def matmul_group(self, weights, x_ptr: int, x_dtype: int, m_rows: int, y_ptrs, y_dtype: int = F16,
                      ldys=None):
         count = len(weights)
@@ -341,13 +348,6 @@ class Q4Context:
                                                     ctypes.byref(ms), self._err, _ERR))
         return y, ms.value
 
-    # -- graph replay -------------------------------------------------------
-    def graph_begin(self):
-        self._check(library().q4b_graph_begin(self.handle, self._err, _ERR))
-
-    def graph_end(self) -> Q4Graph:
-        handle = _vp()
-        self._check(library().q4b_graph_end(self.handle, ctypes.byref(handle), self._err, _ERR))
     def probe_read(self, mode: int = 0, nbytes: int = 2 << 30, ctas_per_sm: int = 2, stages: int = 4,
                    stage_bytes: int = 18432, iterations: int = 5) -> float:
         """HBM read bandwidth in GB/s (see q4b_probe_read)."""
@@ -356,4 +356,11 @@ class Q4Context:
                                              iterations, ctypes.byref(out), self._err, _ERR))
         return out.value
 
+    # -- graph replay -------------------------------------------------------
+    def graph_begin(self):
+        self._check(library().q4b_graph_begin(self.handle, self._err, _ERR))
+
+    def graph_end(self) -> Q4Graph:
+        handle = _vp()
+        self._check(library().q4b_graph_end(self.handle, ctypes.byref(handle), self._err, _ERR))
         return Q4Graph(self, handle.value)

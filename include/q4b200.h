@@ -118,6 +118,33 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
                uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, const void *residual,
                int residual_dtype, uint32_t ld_residual,
                char *error_message, size_t error_capacity);
+/* The same product for callers that must not allocate.  (This entry point has no
+ * counterpart in the reference; it exists for hosts built around this library.)
+ *
+ * q4b_matmul keeps a scratch buffer for row blocks whose K range is split over
+ * several thread blocks, and grows it with cudaMalloc the first time a shape
+ * needs more.  That is wrong for a caller that has handed all device memory to
+ * its own pool, that runs where an implicit device-wide synchronisation (which
+ * cudaMalloc and cudaFree cause) would stall other streams mid-token, or that
+ * must give the same latency on the first token as on the thousandth.  This
+ * variant runs the same kernel with its scratch in an array that is part of the
+ * library image itself: 4 MiB of partial sums plus 4096 arrival counters, held
+ * by every GPU that loads the library until the process exits.  It calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits and rules:
+ *   - shapes whose split-K scratch exceeds the array are refused with status 1
+ *     and a message that states both sizes (all BASELINE shapes fit);
+ *   - no residual input; otherwise the arguments of q4b_matmul;
+ *   - the first call on a device looks the array's device address up (once per
+ *     device); make that first call before any stream capture begins;
+ *   - every call on a device shares the one array and finds what the last call
+ *     left in it: the call clears its counters itself, but two calls whose
+ *     kernels overlap on the GPU (two contexts, two streams) race on it -- keep
+ *     calls to this entry point on one stream per device. */
+int q4b_matmul_no_alloc(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
+                        uint32_t m_rows, void *y, int y_dtype, uint32_t ldy,
+                        char *error_message, size_t error_capacity);
 /* Up to 4 matrices that share x in one launch, e.g. q/k/v, which the reference
  * fuses into one matrix (qwen38_attention.metal:4-8). */
 int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int count,
@@ -149,6 +176,17 @@ int q4b_gate_up_silu_host(q4b_context *context, const q4b_weight *gate, const q4
 int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity);
 int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_t error_capacity);
 
+/* ---- read-bandwidth probe: the role of the reference's device-memory probe
+ * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):
+ * reads `bytes` of device memory `iterations` times and reports GB/s from CUDA
+ * events.  mode 0 = plain 16-byte loads; 1 = the GEMV kernel's bulk-copy ring
+ * with idle consumers; 2 = the same ring with the consumers reading the staged
+ * bytes.  ctas_per_sm, stages and stage_bytes shape the ring modes.  Synchronous;
+ * allocates and frees its own buffer. */
+int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
+                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second,
+                   char *error_message, size_t error_capacity);
+
 /* ---- replay of a recorded call sequence (one command buffer per token in the
  * reference, qwen38_m3_decode.m:1614-1690): calls between begin and end are
  * captured instead of executed. */
@@ -163,14 +201,3 @@ void q4b_graph_free(q4b_graph *graph);
 }
 #endif
 #endif
-/* ---- read-bandwidth probe: the role of the reference's device-memory probe
- * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):
- * reads `bytes` of device memory `iterations` times and reports GB/s from CUDA
- * events.  mode 0 = plain 16-byte loads; 1 = the GEMV kernel's bulk-copy ring
- * with idle consumers; 2 = the same ring with the consumers reading the staged
- * bytes.  ctas_per_sm, stages and stage_bytes shape the ring modes.  Synchronous;
- * allocates and frees its own buffer. */
-int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm, uint32_t stages,
-                   uint32_t stage_bytes, int iterations, double *gigabytes_per_second,
-                   char *error_message, size_t error_capacity);
-
