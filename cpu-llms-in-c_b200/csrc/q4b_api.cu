@@ -27,6 +27,8 @@ struct q4b_context {
     size_t scratch_bytes;
     uint32_t *counters;       // arrival counters, zero between launches
     size_t counter_bytes;
+    __half *x16;              // fp16 copy of fp32 activations for the tensor-core GEMM (grown on demand)
+    size_t x16_bytes;
 };
 
 struct q4b_weight {
@@ -258,6 +260,55 @@ int ensure_scratch(q4b_context *context, const GemvPlan &plan, char *error_messa
     return Q4B_OK;
 }
 
+// M above the small-M kernel's limit: the tcgen05 GEMM, one launch per matrix
+int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_message, size_t error_capacity) {
+    const size_t K = (size_t)args.w[0].groups * kGroup;
+    const void *x = args.x;
+    if (args.x_dtype == kF32) {
+        const size_t bytes = (size_t)args.m_rows * K * sizeof(__half);
+        if (bytes > context->x16_bytes) {
+            if (context->capturing) {
+                set_error(error_message, error_capacity,
+                          "the recorded sequence needs a larger fp16 staging buffer; run it once before recording");
+                return Q4B_BAD_ARGUMENT;
+            }
+            cudaError_t status = cudaStreamSynchronize(context->stream);
+            if (status == cudaSuccess) {
+                cudaFree(context->x16);
+                context->x16 = nullptr;
+                context->x16_bytes = 0;
+                status = cudaMalloc(&context->x16, bytes);
+            }
+            if (status != cudaSuccess) return device_failure(error_message, error_capacity, "fp16 staging buffer", status);
+            context->x16_bytes = bytes;
+        }
+        cudaError_t status = launch_convert_f32_to_f16(static_cast<const float *>(args.x), context->x16,
+                                                       (size_t)args.m_rows * K, context->stream);
+        if (!context->capturing) ++context->launches;
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "activation convert", status);
+        x = context->x16;
+    }
+    for (int s = 0; s < args.segments; ++s) {
+        TcGemmArgs gemm = {};
+        gemm.w = args.w[s];
+        gemm.up = args.up;
+        gemm.fused_silu = args.fused_silu;
+        gemm.x = x;
+        gemm.m_rows = args.m_rows;
+        gemm.y = args.y[s];
+        gemm.y_dtype = args.y_dtype;
+        gemm.ldy = args.ldy[s];
+        gemm.residual = s == 0 ? args.residual : nullptr;
+        gemm.residual_dtype = args.residual_dtype;
+        gemm.ld_residual = args.ld_residual;
+        gemm.status = context->status_device;
+        cudaError_t status = launch_tc_gemm(gemm, context->sm_count, context->stream);
+        if (!context->capturing) ++context->launches;
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "tensor-core gemm launch", status);
+    }
+    return Q4B_OK;
+}
+
 // one launch sequence for any M: GEMV kernel up to its row limit, row blocks above.
 // With built_in_scratch the split-K scratch is the library's file-scope device
 // array and nothing is allocated, grown or freed.
@@ -266,6 +317,10 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
     const uint32_t limit = gemv_max_m();
     const uint32_t total = args.m_rows;
     const size_t K = (size_t)args.w[0].groups * kGroup;
+    // variant bit 15 keeps large M on the small-M kernel (row blocks of 16), for A/B runs
+    if (total > limit && !built_in_scratch && ((context->variant >> 15) & 1) == 0) {
+        return run_tensor_core(context, args, error_message, error_capacity);
+    }
     for (uint32_t m0 = 0; m0 < total; m0 += limit) {
         GemvArgs block = args;
         block.m_rows = total - m0 < limit ? total - m0 : limit;
@@ -377,6 +432,7 @@ void q4b_context_close(q4b_context *context) {
     cudaFreeHost(context->status_host);
     cudaFree(context->scratch);
     cudaFree(context->counters);
+    cudaFree(context->x16);
     delete context;
 }
 

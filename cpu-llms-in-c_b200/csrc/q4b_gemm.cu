@@ -1,0 +1,431 @@
+// Prefill GEMM on the Q4 tile stream: tcgen05 tensor cores, accumulators in TMEM.
+//
+// Replaces the reference's batched tensor kernels: qwen38_prefill_q4_gemm_*_mma /
+// _mma2 / _mma3 (qwen38_prefill.metal:811-1502) and minimax_h3_q4_gemm_f16_mma[_wide]
+// (minimax_h3_attention.metal:211-404): Y[m][n] = sum_k w(n,k) X[m][k], fp16
+// operands, fp32 accumulation over the whole K (no half-precision window).
+//
+// One CTA computes a 128 (weight rows) x BN (activation rows) output tile:
+//   D[128][BN] (TMEM, fp32) += A[128][64] (TMEM, fp16) * B[BN][64]^T (shared memory)
+// per quantisation group.  The WEIGHTS are the A operand and never exist as fp16
+// in shared memory: warp 0 brings the group's 4.6 KB of Q4 tiles in with bulk
+// copies and the X tile with a TMA tensor copy (128-byte swizzle); eight
+// dequantisation warps (thread = weight row) turn the codes into
+// w16 = fma(scale, q, bias) -- the bit-exact W16 contract -- and write them
+// straight into TMEM with tcgen05.st; warp 1 issues four tcgen05.mma (K = 16 each)
+// per group and commits to mbarriers that free the A slot and the stage.  A
+// dequantised tile written to and re-read from shared memory next to the X tile
+// would exceed one SM's shared-memory bandwidth; through TMEM it costs none.
+// After the last group the same eight warps read D with tcgen05.ld, apply the
+// epilogue (optional residual, optional silu(gate)*up over two accumulators) and
+// store Y.  Every wait is bounded; on expiry the kernel records a code in the
+// status word, releases its TMEM and returns.
+#include "q4b_kernels.h"
+
+#include <cuda.h>
+
+namespace q4b {
+
+namespace {
+
+constexpr int kTcStages = 4;     // ring stages (one quantisation group each)
+constexpr int kTcSlots = 4;      // A-operand slots in TMEM (32 columns each)
+constexpr int kTcThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2..9 dequantise + epilogue
+constexpr long long kTcWaitLimit = 4000000000ll;
+
+struct TcParams {
+    CUtensorMap x_map;  // X [M][K] fp16, box 64 x BN, 128-byte swizzle
+    WeightView w;
+    WeightView up;      // second matrix when two accumulators are fused
+    void *y;
+    const void *residual;
+    uint32_t *status;
+    uint32_t ldy, ld_residual;
+    uint32_t m_rows, groups, n_blocks, m_blocks;
+    int y_dtype, residual_dtype;
+};
+
+__device__ inline uint32_t tc_smem_u32(const void *pointer) {
+    return (uint32_t)__cvta_generic_to_shared(pointer);
+}
+__device__ inline void tc_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ inline void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ inline void tc_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline bool tc_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// false when the wait expired
+__device__ inline bool tc_wait(uint32_t bar, uint32_t parity) {
+    if (tc_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!tc_try_wait(bar, parity)) {
+        if (clock64() - start > kTcWaitLimit) return false;
+    }
+    return true;
+}
+__device__ inline void tc_bulk_copy(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(destination), "l"(source), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ inline void tc_tensor_copy_2d(uint32_t destination, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(destination), "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ inline void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem_d] (+)= A[tmem_a] * B[desc]^T, M = 128, K = 16
+__device__ inline void tc_mma(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ inline void tc_store_32(uint32_t address, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ inline void tc_load_16(uint32_t address, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address));
+}
+
+
+// BN  : activation rows per tile (columns of D)
+// NACC: accumulators per tile: 1, or 2 for fused gate/up (epilogue silu(gate) * up)
+template <int BN, int NACC>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_kernel(const __grid_constant__ TcParams p) {
+    constexpr uint32_t kXBytes = BN * 128;               // one group of X: BN rows x 64 halves
+    constexpr uint32_t kWBytes = NACC * 2 * kUnitBytes;  // 128 weight rows of each matrix, one group
+    constexpr uint32_t kDCols = NACC * BN;
+    constexpr uint32_t kTmemCols = kDCols + kTcSlots * 32 <= 256 ? 256 : 512;
+    static_assert(kDCols + kTcSlots * 32 <= 512, "accumulators and A slots must fit the 512 TMEM columns");
+    extern __shared__ uint8_t tc_smem_raw[];
+    // 128-byte swizzle atoms need 1024-byte alignment in the shared window
+    uint8_t *base = tc_smem_raw + ((1024u - (tc_smem_u32(tc_smem_raw) & 1023u)) & 1023u);
+    uint8_t *xbuf = base;
+    uint8_t *wbuf = base + kTcStages * kXBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wbuf + kTcStages * kWBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kTcStages + 2 * kTcSlots + 2);
+    const uint32_t full0 = tc_smem_u32(bars), empty0 = full0 + 8 * kTcStages;
+    const uint32_t a_full0 = empty0 + 8 * kTcStages, a_free0 = a_full0 + 8 * kTcSlots;
+    const uint32_t d_full = a_free0 + 8 * kTcSlots, d_free = d_full + 8;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t G = p.groups;
+    const uint32_t tiles = p.n_blocks * p.m_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            tc_mbar_init(full0 + 8 * s, 1);
+            tc_mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < kTcSlots; ++a) {
+            tc_mbar_init(a_full0 + 8 * a, 4);
+            tc_mbar_init(a_free0 + 8 * a, 1);
+        }
+        tc_mbar_init(d_full, 1);
+        tc_mbar_init(d_free, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(tc_smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;          // D: columns [0, NACC*BN)
+    const uint32_t tmem_a = tmem_d + kDCols;     // A slots: 32 columns each
+
+    bool ok = true;
+    if (warp == 0) {
+        // ---- producer: Q4 tiles by bulk copy, X tile by TMA tensor copy ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const uint32_t nb = tile / p.m_blocks, mb = tile % p.m_blocks;
+                for (uint32_t g = 0; g < G; ++g, ++it) {
+                    const uint32_t s = it % kTcStages;
+                    if (it >= kTcStages && !tc_wait(empty0 + 8 * s, ((it / kTcStages) - 1) & 1)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = full0 + 8 * s;
+                    tc_mbar_expect_tx(bar, kWBytes + kXBytes);
+                    const uint32_t wdst = tc_smem_u32(wbuf) + s * kWBytes;
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k) {
+                        const uint8_t *stream = k == 0 ? p.w.tiles : p.up.tiles;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const size_t offset = ((size_t)(nb * 2 + h) * G + g) * kUnitBytes;
+                            tc_bulk_copy(wdst + (k * 2 + h) * kUnitBytes, stream + offset, kUnitBytes, bar);
+                        }
+                    }
+                    tc_tensor_copy_2d(tc_smem_u32(xbuf) + s * kXBytes, &p.x_map, (int)(g * kGroup), (int)(mb * BN), bar);
+                }
+            }
+            if (!ok) {
+                atomicExch(p.status, 0x71u);
+                // let copies already issued land before the shared memory is released
+                for (uint32_t back = 0; back < kTcStages && back < it; ++back) {
+                    const uint32_t j = it - 1 - back;
+                    tc_wait(full0 + 8 * (j % kTcStages), (j / kTcStages) & 1);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            const uint64_t desc_base = ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+                                       ((uint64_t)2 << 61);
+            uint32_t it = 0, unit = 0, tile_iter = 0;
+            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
+                if (tile_iter > 0 && !tc_wait(d_free, (tile_iter - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                for (uint32_t g = 0; g < G && ok; ++g, ++it) {
+                    const uint32_t s = it % kTcStages;
+                    if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
+                    const uint32_t xaddr = tc_smem_u32(xbuf) + s * kXBytes;
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k, ++unit) {
+                        const uint32_t a = unit % kTcSlots;
+                        if (!tc_wait(a_full0 + 8 * a, (unit / kTcSlots) & 1)) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint64_t desc = desc_base | (uint64_t)(((xaddr + kk * 32) >> 4) & 0x3fffu);
+                            tc_mma(tmem_d + k * BN, tmem_a + a * 32 + kk * 8, desc, idesc, (g > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit(a_free0 + 8 * a);  // the slot may be rewritten once these MMAs retire
+                    }
+                    tc_commit(empty0 + 8 * s);       // and the stage refilled
+                }
+                if (ok) tc_commit(d_full);
+            }
+            if (!ok) atomicExch(p.status, 0x72u);
+        }
+    } else {
+        // ---- dequantisation (thread = weight row) and epilogue ----
+        const uint32_t wg = (uint32_t)(warp - 2) >> 2, quad = warp & 3;
+        const uint32_t row = quad * 32 + lane;  // row of the 128-row tile == TMEM lane
+        const uint32_t lane_field = (quad * 32) << 16;
+        const uint32_t r64 = row & 63, gid = r64 & 7, hi = (r64 >> 3) & 1;
+        const uint32_t tile_offset_bytes = (row >> 6) * kUnitBytes + (r64 >> 4) * kTileBytes;
+        // rows gid+8 sit in the odd nibbles: 0x6400 | (q << 4) is 1024 + 16 q
+        const uint32_t mask = hi ? 0x00F000F0u : 0x000F000Fu;
+        const __half2 to_code_mul = __half2half2(__ushort_as_half(hi ? 0x2c00 : 0x3c00));  // 1/16 or 1
+        const __half2 to_code_add = __half2half2(__ushort_as_half(hi ? 0xd400 : 0xe400));  // -64 or -1024
+        uint32_t it = 0, unit = 0, tile_iter = 0;
+        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
+            const uint32_t nb = tile / p.m_blocks, mb = tile % p.m_blocks;
+            for (uint32_t g = 0; g < G && ok; ++g, ++it) {
+                const uint32_t s = it % kTcStages;
+#pragma unroll
+                for (int k = 0; k < NACC; ++k, ++unit) {
+                    const bool mine = NACC == 2 ? (uint32_t)k == wg : (g & 1u) == wg;
+                    if (!mine) continue;
+                    const uint32_t a = unit % kTcSlots;
+                    if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
+                    const uint8_t *tile_bytes = wbuf + s * kWBytes + k * 2 * kUnitBytes + tile_offset_bytes;
+                    const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
+                    const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
+                    const __half2 scale = __half2half2(__low2half(sb)), bias = __half2half2(__high2half(sb));
+                    uint32_t regs[32];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const uint4 piece = *reinterpret_cast<const uint4 *>(tile_bytes + (gid * 4 + t) * 16);
+                        const uint32_t word[4] = {piece.x, piece.y, piece.z, piece.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t v01, v23;
+                            const uint32_t w8 = word[i] >> 8;
+                            asm("lop3.b32 %0, %1, %2, 0x64006400, 0xEA;" : "=r"(v01) : "r"(word[i]), "r"(mask));
+                            asm("lop3.b32 %0, %1, %2, 0x64006400, 0xEA;" : "=r"(v23) : "r"(w8), "r"(mask));
+                            const __half2 q01 = __hfma2(*reinterpret_cast<__half2 *>(&v01), to_code_mul, to_code_add);
+                            const __half2 q23 = __hfma2(*reinterpret_cast<__half2 *>(&v23), to_code_mul, to_code_add);
+                            const __half2 w01 = dequant_w16(q01, scale, bias);
+                            const __half2 w23 = dequant_w16(q23, scale, bias);
+                            regs[8 * t + 2 * i] = *reinterpret_cast<const uint32_t *>(&w01);
+                            regs[8 * t + 2 * i + 1] = *reinterpret_cast<const uint32_t *>(&w23);
+                        }
+                    }
+                    if (unit >= kTcSlots && !tc_wait(a_free0 + 8 * a, ((unit / kTcSlots) - 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    tc_store_32(tmem_a + a * 32 + lane_field, regs);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) tc_mbar_arrive(a_full0 + 8 * a);
+                }
+            }
+            if (!ok) break;
+            // ---- epilogue: this warp's 32 rows x half of the columns ----
+            if (!tc_wait(d_full, tile_iter & 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t n = nb * 128 + row;
+            const bool row_valid = n < p.w.rows;
+#pragma unroll 1
+            for (uint32_t c = wg * (BN / 2); c < (wg + 1) * (BN / 2); c += 16) {
+                uint32_t d0[16], d1[16];
+                tc_load_16(tmem_d + c + lane_field, d0);
+                if (NACC == 2) tc_load_16(tmem_d + BN + c + lane_field, d1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t m = mb * BN + c + j;
+                    if (!row_valid || m >= p.m_rows) continue;
+                    float value = __uint_as_float(d0[j]);
+                    if (NACC == 2) {
+                        // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
+                        value = (value / (1.0f + __expf(-value))) * __uint_as_float(d1[j]);
+                    }
+                    if (p.residual != nullptr) {
+                        const size_t at = (size_t)m * p.ld_residual + n;
+                        value += p.residual_dtype == kF32 ? reinterpret_cast<const float *>(p.residual)[at]
+                                                          : __half2float(reinterpret_cast<const __half *>(p.residual)[at]);
+                    }
+                    const size_t at = (size_t)m * p.ldy + n;
+                    if (p.y_dtype == kF32) {
+                        reinterpret_cast<float *>(p.y)[at] = value;
+                    } else {
+                        reinterpret_cast<__half *>(p.y)[at] = __float2half_rn(value);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(d_free);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, 0x73u);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime, so the library links libcudart only
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn function = nullptr;
+    if (function == nullptr) {
+        void *pointer = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess) {
+            function = reinterpret_cast<EncodeTiledFn>(pointer);
+        }
+    }
+    return function;
+}
+
+template <int BN, int NACC>
+cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
+    EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)args.w.groups * kGroup, (cuuint64_t)args.m_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)args.w.groups * kGroup * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kGroup, (cuuint32_t)BN};
+    const cuuint32_t element_strides[2] = {1, 1};
+    if (encode(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(args.x), dims, strides, box,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        return cudaErrorInvalidValue;
+    }
+    p.m_blocks = ceil_div(args.m_rows, BN);
+    const uint32_t tiles = p.n_blocks * p.m_blocks;
+    const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + NACC * 2 * kUnitBytes) +
+                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + 1024;
+    auto kernel = tc_gemm_kernel<BN, NACC>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (status != cudaSuccess) return status;
+        configured = true;
+    }
+    const unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
+    kernel<<<grid, kTcThreads, smem_bytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
+    if (args.m_rows == 0 || args.w.rows == 0) return cudaSuccess;
+    if ((reinterpret_cast<uintptr_t>(args.x) & 15u) != 0) return cudaErrorInvalidValue;
+    TcParams p = {};
+    p.w = args.w;
+    p.up = args.up;
+    p.y = args.y;
+    p.residual = args.residual;
+    p.status = args.status;
+    p.ldy = args.ldy;
+    p.ld_residual = args.ld_residual;
+    p.m_rows = args.m_rows;
+    p.groups = args.w.groups;
+    p.n_blocks = ceil_div(args.w.rows, 128);
+    p.y_dtype = args.y_dtype;
+    p.residual_dtype = args.residual_dtype;
+    if (args.fused_silu) return launch_tc_instance<128, 2>(p, args, sm_count, stream);
+    if (args.m_rows <= 128) return launch_tc_instance<128, 1>(p, args, sm_count, stream);
+    return launch_tc_instance<256, 1>(p, args, sm_count, stream);
+}
+
+// fp32 activations -> fp16 (the tensor pipe multiplies fp16)
+__global__ void convert_f32_to_f16_kernel(const float *in, __half *out, size_t count) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        out[i] = __float2half_rn(in[i]);
+    }
+}
+
+cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    size_t blocks = (count + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    convert_f32_to_f16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(in, out, count);
+    return cudaGetLastError();
+}
+
+}  // namespace q4b

@@ -58,6 +58,24 @@ uint32_t gemv_max_m();
 cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
                                 size_t *counter_bytes);
 
+// ---- q4b_gemm.cu: tcgen05 prefill GEMM ----
+struct TcGemmArgs {
+    WeightView w;
+    WeightView up;        // valid when fused_silu
+    int fused_silu;
+    const void *x;        // [M][K] fp16, 16-byte aligned
+    uint32_t m_rows;
+    void *y;              // [M][ldy]
+    int y_dtype;
+    uint32_t ldy;
+    const void *residual; // [M][ld_residual] or null
+    int residual_dtype;
+    uint32_t ld_residual;
+    uint32_t *status;
+};
+cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream);
+cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream);
+
 // ---- q4b_probe.cu ----
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,
                          uint32_t *sink, cudaStream_t stream);

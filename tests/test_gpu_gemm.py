@@ -1,0 +1,102 @@
+"""Parity of the tcgen05 prefill GEMM (M > 16, through the C ABI) with the oracle.
+
+Outputs: max|y - ref| / max|ref| <= 2e-3 against the oracle's double sum on
+sampled weight rows (the oracle is a scalar loop); the multiplied weights are the
+bit-exact W16 values (gate in test_gpu_parity.py).  At BASELINE's full sizes the
+check is a property: the GEMM must agree with the small-M kernel on sampled
+activation rows.
+"""
+import numpy as np
+import pytest
+
+from q4_cases import assert_close, relative_error
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(q4b):
+    context = q4b.Q4Context(0)
+    yield context
+    context.close()
+
+
+def oracle_rows(orc, quants, meta, groups, x, rows, residual=None):
+    """Oracle output for a sample of weight rows: [M, len(rows)] in double."""
+    cols = []
+    for row in rows:
+        res = None if residual is None else np.ascontiguousarray(residual[:, row:row + 1])
+        cols.append(orc.matmul(quants, meta, groups, x, row_begin=int(row), row_count=1, residual=res,
+                               want32=False)[1])
+    return np.concatenate(cols, axis=1)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 128, 64), (128, 64, 17), (384, 320, 300), (1024, 2048, 128),
+                                   (1000, 1024, 257), (2048, 5120, 512)])
+def test_gemm_matches_oracle(q4b, orc, ctx, n, k, m):
+    groups = k // 64
+    quants, meta = orc.synth_weight(3, 0, n, groups)
+    x = orc.synth_x(3, 0, m, k)
+    weight = ctx.upload(quants, meta, n, groups)
+    dx, dy = ctx.to_device(x), ctx.to_device(np.full((m, n), 7.0, dtype=np.float16))
+    ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    rows = np.unique(np.concatenate([np.arange(0, min(n, 20)), np.arange(n - 20, n),
+                                     np.random.default_rng(1).integers(0, n, 40)]))
+    ref = oracle_rows(orc, quants, meta, groups, x, rows)
+    assert_close(y[:, rows], ref, f"gemm {n}x{k} M={m}")
+    assert np.isfinite(y.astype(np.float32)).all()
+
+
+@pytest.mark.parametrize("m", [64, 200])
+def test_gemm_fused_gate_up(q4b, orc, ctx, m):
+    n, k = 640, 1024
+    groups = k // 64
+    gq, gm = orc.synth_weight(0, 4, n, groups)
+    uq, um = orc.synth_weight(0, 5, n, groups)
+    x = orc.synth_x(0, 0, m, k)
+    gate, up = ctx.upload(gq, gm, n, groups), ctx.upload(uq, um, n, groups)
+    dx, dy = ctx.to_device(x), ctx.alloc(m * n * 2)
+    ctx.gate_up_silu(gate, up, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    _, ref = orc.gate_up_silu(gq, gm, uq, um, groups, x, want32=False)
+    assert_close(y, ref, f"fused gemm M={m}")
+
+
+def test_gemm_float_x_residual_and_wide_output(q4b, orc, ctx):
+    n, k, m, ldy = 200, 512, 70, 256
+    groups = k // 64
+    quants, meta = orc.synth_weight(2, 0, n, groups)
+    weight = ctx.upload(quants, meta, n, groups)
+    x = orc.synth_x(2, 0, m, k).astype(np.float32)
+    residual = orc.synth_x(2, 9, m, n).astype(np.float32)
+    dx, dr = ctx.to_device(x), ctx.to_device(residual)
+    canvas = np.full((m, ldy), 5.0, dtype=np.float32)
+    dy = ctx.to_device(canvas)
+    ctx.matmul(weight, dx.ptr, q4b.F32, m, dy.ptr + 4 * 16, q4b.F32, ldy, dr.ptr, q4b.F32, n)
+    out = dy.download(np.float32, (m, ldy))
+    _, ref = orc.matmul(quants, meta, groups, x, residual=residual, want32=False)
+    assert_close(out[:, 16:216], ref, "fp32 x + residual")
+    assert (out[:, :16] == 5.0).all() and (out[:, 216:] == 5.0).all()
+
+
+@pytest.mark.parametrize("name,k,n", [("q", 5120, 6144), ("down", 17408, 5120)])
+def test_gemm_full_size_agrees_with_small_m_kernel(q4b, orc, ctx, name, k, n):
+    m = 2048
+    weight = ctx.synth_weight(0, 2, n, k // 64)
+    dx = ctx.synth_x(0, 0, m, k)
+    dy = ctx.alloc(m * n * 2)
+    ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    picks = [0, 1, 255, 256, 1000, 2047]
+    x_rows = dx.download(np.float16, (m, k))[picks]
+    dxs, dys = ctx.to_device(x_rows), ctx.alloc(len(picks) * n * 2)
+    ctx.matmul(weight, dxs.ptr, q4b.F16, len(picks), dys.ptr)   # small-M kernel
+    small = dys.download(np.float16, (len(picks), n))
+    assert relative_error(y[picks], small.astype(np.float64)) < 1e-3
+    # and a sample against the oracle itself
+    quants, meta = orc.synth_weight(0, 2, n, k // 64)
+    rows = np.array([0, 63, 64, 127, 128, n - 1])
+    ref = oracle_rows(orc, quants, meta, k // 64, x_rows, rows)
+    assert_close(small[:, rows], ref, f"{name} small-M")
+    assert_close(y[picks][:, rows], ref, f"{name} gemm")
