@@ -13,7 +13,10 @@
 // and everything one 64-row block needs for a range of groups is one contiguous
 // byte range (one bulk copy).  Inside a tile:
 //
-//   [  0,512)  32 lane pieces of 16 bytes.  Lane l = 4*gid + t owns rows
+//   [  0,512)  32 lane pieces of 16 bytes, lane l's piece at index piece_index(l)
+//              (a rotation inside each 64-byte gid group that keeps the
+//              row-per-thread readers of the tensor-core GEMM free of bank
+//              conflicts).  Lane l = 4*gid + t owns rows
 //              (gid, gid+8) and columns 16*t .. 16*t+15 of the tile.  Its four
 //              32-bit words i = 0..3 each carry the eight codes of one
 //              m16n8k16 A fragment, nibble p (bits 4p..4p+3):
@@ -58,6 +61,13 @@ struct WeightView {
 
 __host__ __device__ inline uint32_t ceil_div(uint32_t a, uint32_t b) {
     return (a + b - 1) / b;
+}
+
+// position (in 16-byte pieces) of lane l's piece inside a tile: pieces of one gid
+// stay in their 64-byte group, rotated by gid/2.  A warp reading piece t of 16
+// different rows then touches every bank group instead of two.
+__host__ __device__ inline uint32_t piece_index(uint32_t lane) {
+    return (lane & ~3u) | (((lane & 3u) + (lane >> 3)) & 3u);
 }
 
 // byte offset of tile (rt, g) in a stream with G groups per row

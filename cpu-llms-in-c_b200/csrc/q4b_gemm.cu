@@ -17,8 +17,10 @@
 // dequantised tile written to and re-read from shared memory next to the X tile
 // would exceed one SM's shared-memory bandwidth; through TMEM it costs none.
 // After the last group the same eight warps read D with tcgen05.ld, apply the
-// epilogue (optional residual, optional silu(gate)*up over two accumulators) and
-// store Y.  Every wait is bounded; on expiry the kernel records a code in the
+// epilogue (optional residual) and store Y.  Fused gate/up puts the 64 gate rows
+// and the 64 up rows of the same 64 output features into one 128-row A tile, so
+// the tensor cores still run full-width tiles; the epilogue pairs the two halves
+// through shared memory and stores silu(gate) * up.  Every wait is bounded; on expiry the kernel records a code in the
 // status word, releases its TMEM and returns.
 #include "q4b_kernels.h"
 
@@ -121,14 +123,14 @@ __device__ inline void tc_load_16(uint32_t address, uint32_t (&r)[16]) {
 }
 
 
-// BN  : activation rows per tile (columns of D)
-// NACC: accumulators per tile: 1, or 2 for fused gate/up (epilogue silu(gate) * up)
-template <int BN, int NACC>
+// BN   : activation rows per tile (columns of D)
+// FUSED: the A tile is 64 rows of `w` (gate) over 64 rows of `up`; epilogue silu(gate) * up
+template <int BN, bool FUSED>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
     constexpr uint32_t kXBytes = BN * 128;               // one group of X: BN rows x 64 halves
-    constexpr uint32_t kWBytes = NACC * 2 * kUnitBytes;  // 128 weight rows of each matrix, one group
-    constexpr uint32_t kDCols = NACC * BN;
+    constexpr uint32_t kWBytes = 2 * kUnitBytes;         // two 64-row blocks, one group
+    constexpr uint32_t kDCols = BN;
     constexpr uint32_t kTmemCols = kDCols + kTcSlots * 32 <= 256 ? 256 : 512;
     static_assert(kDCols + kTcSlots * 32 <= 512, "accumulators and A slots must fit the 512 TMEM columns");
     extern __shared__ uint8_t tc_smem_raw[];
@@ -138,6 +140,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     uint8_t *wbuf = base + kTcStages * kXBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wbuf + kTcStages * kWBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kTcStages + 2 * kTcSlots + 2);
+    float *exchange = reinterpret_cast<float *>(tmem_slot + 4);  // fused epilogue: [2 warpgroups][2][16][64]
     const uint32_t full0 = tc_smem_u32(bars), empty0 = full0 + 8 * kTcStages;
     const uint32_t a_full0 = empty0 + 8 * kTcStages, a_free0 = a_full0 + 8 * kTcSlots;
     const uint32_t d_full = a_free0 + 8 * kTcSlots, d_free = d_full + 8;
@@ -168,7 +171,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_d = *tmem_slot;          // D: columns [0, NACC*BN)
+    const uint32_t tmem_d = *tmem_slot;          // D: columns [0, BN)
     const uint32_t tmem_a = tmem_d + kDCols;     // A slots: 32 columns each
 
     bool ok = true;
@@ -188,13 +191,11 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     tc_mbar_expect_tx(bar, kWBytes + kXBytes);
                     const uint32_t wdst = tc_smem_u32(wbuf) + s * kWBytes;
 #pragma unroll
-                    for (int k = 0; k < NACC; ++k) {
-                        const uint8_t *stream = k == 0 ? p.w.tiles : p.up.tiles;
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const size_t offset = ((size_t)(nb * 2 + h) * G + g) * kUnitBytes;
-                            tc_bulk_copy(wdst + (k * 2 + h) * kUnitBytes, stream + offset, kUnitBytes, bar);
-                        }
+                    for (int h = 0; h < 2; ++h) {
+                        const uint8_t *stream = FUSED && h == 1 ? p.up.tiles : p.w.tiles;
+                        const uint32_t block = FUSED ? nb : nb * 2 + h;  // 64-row block of that stream
+                        const size_t offset = ((size_t)block * G + g) * kUnitBytes;
+                        tc_bulk_copy(wdst + h * kUnitBytes, stream + offset, kUnitBytes, bar);
                     }
                     tc_tensor_copy_2d(tc_smem_u32(xbuf) + s * kXBytes, &p.x_map, (int)(g * kGroup), (int)(mb * BN), bar);
                 }
@@ -222,19 +223,17 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t s = it % kTcStages;
                     if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                     const uint32_t xaddr = tc_smem_u32(xbuf) + s * kXBytes;
+                    const uint32_t a = unit % kTcSlots;
+                    if (!tc_wait(a_full0 + 8 * a, (unit / kTcSlots) & 1)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < NACC; ++k, ++unit) {
-                        const uint32_t a = unit % kTcSlots;
-                        if (!tc_wait(a_full0 + 8 * a, (unit / kTcSlots) & 1)) { ok = false; break; }
-                        tc_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint64_t desc = desc_base | (uint64_t)(((xaddr + kk * 32) >> 4) & 0x3fffu);
-                            tc_mma(tmem_d + k * BN, tmem_a + a * 32 + kk * 8, desc, idesc, (g > 0 || kk > 0) ? 1u : 0u);
-                        }
-                        tc_commit(a_free0 + 8 * a);  // the slot may be rewritten once these MMAs retire
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t desc = desc_base | (uint64_t)(((xaddr + kk * 32) >> 4) & 0x3fffu);
+                        tc_mma(tmem_d, tmem_a + a * 32 + kk * 8, desc, idesc, (g > 0 || kk > 0) ? 1u : 0u);
                     }
-                    tc_commit(empty0 + 8 * s);       // and the stage refilled
+                    ++unit;
+                    tc_commit(a_free0 + 8 * a);  // the slot may be rewritten once these MMAs retire
+                    tc_commit(empty0 + 8 * s);   // and the stage refilled
                 }
                 if (ok) tc_commit(d_full);
             }
@@ -256,20 +255,18 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t nb = tile / p.m_blocks, mb = tile % p.m_blocks;
             for (uint32_t g = 0; g < G && ok; ++g, ++it) {
                 const uint32_t s = it % kTcStages;
-#pragma unroll
-                for (int k = 0; k < NACC; ++k, ++unit) {
-                    const bool mine = NACC == 2 ? (uint32_t)k == wg : (g & 1u) == wg;
-                    if (!mine) continue;
+                for (int once = 0; once < 1; ++once, ++unit) {
+                    if ((unit & 1u) != wg) continue;  // the two warpgroups take alternate groups
                     const uint32_t a = unit % kTcSlots;
                     if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
-                    const uint8_t *tile_bytes = wbuf + s * kWBytes + k * 2 * kUnitBytes + tile_offset_bytes;
+                    const uint8_t *tile_bytes = wbuf + s * kWBytes + tile_offset_bytes;
                     const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
                     const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
                     const __half2 scale = __half2half2(__low2half(sb)), bias = __half2half2(__high2half(sb));
                     uint32_t regs[32];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
-                        const uint4 piece = *reinterpret_cast<const uint4 *>(tile_bytes + (gid * 4 + t) * 16);
+                        const uint4 piece = *reinterpret_cast<const uint4 *>(tile_bytes + piece_index(gid * 4 + t) * 16);
                         const uint32_t word[4] = {piece.x, piece.y, piece.z, piece.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -298,22 +295,36 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             // ---- epilogue: this warp's 32 rows x half of the columns ----
             if (!tc_wait(d_full, tile_iter & 1)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t n = nb * 128 + row;
+            const uint32_t n = FUSED ? nb * 64 + (row & 63) : nb * 128 + row;  // output feature of this thread
             const bool row_valid = n < p.w.rows;
+            float *swap = exchange + wg * (2 * 16 * 64);
+            uint32_t chunk = 0;
 #pragma unroll 1
-            for (uint32_t c = wg * (BN / 2); c < (wg + 1) * (BN / 2); c += 16) {
-                uint32_t d0[16], d1[16];
+            for (uint32_t c = wg * (BN / 2); c < (wg + 1) * (BN / 2); c += 16, ++chunk) {
+                uint32_t d0[16];
+                float other[16];
                 tc_load_16(tmem_d + c + lane_field, d0);
-                if (NACC == 2) tc_load_16(tmem_d + BN + c + lane_field, d1);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (FUSED) {
+                    // rows 64..127 hold `up` of the feature whose `gate` sits 64 rows above
+                    float *buffer = swap + (chunk & 1) * (16 * 64);
+                    if (row >= 64) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) buffer[j * 64 + (row - 64)] = __uint_as_float(d0[j]);
+                    }
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");
+                    if (row >= 64) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) other[j] = buffer[j * 64 + row];
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const uint32_t m = mb * BN + c + j;
                     if (!row_valid || m >= p.m_rows) continue;
                     float value = __uint_as_float(d0[j]);
-                    if (NACC == 2) {
+                    if (FUSED) {
                         // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
-                        value = (value / (1.0f + __expf(-value))) * __uint_as_float(d1[j]);
+                        value = (value / (1.0f + __expf(-value))) * other[j];
                     }
                     if (p.residual != nullptr) {
                         const size_t at = (size_t)m * p.ld_residual + n;
@@ -360,7 +371,7 @@ EncodeTiledFn encode_tiled() {
     return function;
 }
 
-template <int BN, int NACC>
+template <int BN, bool FUSED>
 cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr) return cudaErrorNotSupported;
@@ -375,9 +386,9 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     }
     p.m_blocks = ceil_div(args.m_rows, BN);
     const uint32_t tiles = p.n_blocks * p.m_blocks;
-    const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + NACC * 2 * kUnitBytes) +
-                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + 1024;
-    auto kernel = tc_gemm_kernel<BN, NACC>;
+    const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
+                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + (FUSED ? 2 * 2 * 16 * 64 * 4 : 0) + 1024;
+    auto kernel = tc_gemm_kernel<BN, FUSED>;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -404,12 +415,15 @@ cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t st
     p.ld_residual = args.ld_residual;
     p.m_rows = args.m_rows;
     p.groups = args.w.groups;
-    p.n_blocks = ceil_div(args.w.rows, 128);
+    p.n_blocks = ceil_div(args.w.rows, args.fused_silu ? 64 : 128);
     p.y_dtype = args.y_dtype;
     p.residual_dtype = args.residual_dtype;
-    if (args.fused_silu) return launch_tc_instance<128, 2>(p, args, sm_count, stream);
-    if (args.m_rows <= 128) return launch_tc_instance<128, 1>(p, args, sm_count, stream);
-    return launch_tc_instance<256, 1>(p, args, sm_count, stream);
+    if (args.fused_silu) {
+        return args.m_rows <= 128 ? launch_tc_instance<128, true>(p, args, sm_count, stream)
+                                  : launch_tc_instance<256, true>(p, args, sm_count, stream);
+    }
+    return args.m_rows <= 128 ? launch_tc_instance<128, false>(p, args, sm_count, stream)
+                              : launch_tc_instance<256, false>(p, args, sm_count, stream);
 }
 
 // fp32 activations -> fp16 (the tensor pipe multiplies fp16)

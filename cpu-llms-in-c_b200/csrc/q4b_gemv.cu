@@ -353,7 +353,7 @@ gemv_kernel(const GemvParams p) {
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const uint8_t *tile = unit + r * kTileBytes;
-                    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + lane * 16);
+                    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
                     const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
                     const uint32_t word[4] = {codes.x, codes.y, codes.z, codes.w};
                     float c[NT][4];

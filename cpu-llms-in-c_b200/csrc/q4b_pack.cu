@@ -42,7 +42,7 @@ repack_kernel(const uint8_t *__restrict__ quants, const void *__restrict__ meta,
         piece_hi = *reinterpret_cast<const uint64_t *>(quants + byte);
     }
     uint8_t *out = tiles + tile_offset(rt, g, groups);
-    reinterpret_cast<uint4 *>(out)[lane] = swizzle_lane(piece_lo, piece_hi);
+    reinterpret_cast<uint4 *>(out)[piece_index(lane)] = swizzle_lane(piece_lo, piece_hi);
     if (lane < 8) {
         uint16_t record[4] = {0, 0, 0, 0};
         uint32_t rows[2] = {rt * 16 + lane, rt * 16 + lane + 8};
@@ -95,7 +95,7 @@ unpack_kernel(WeightView w, uint8_t *__restrict__ codes, float *__restrict__ w32
     uint32_t g = (uint32_t)(tile % w.groups);
     uint32_t gid = lane >> 2, t = lane & 3u;
     const uint8_t *in = w.tiles + tile_offset(rt, g, w.groups);
-    uint4 words = reinterpret_cast<const uint4 *>(in)[lane];
+    uint4 words = reinterpret_cast<const uint4 *>(in)[piece_index(lane)];
     uint2 record = reinterpret_cast<const uint2 *>(in + kTileCodeBytes)[gid];
     const uint32_t word[4] = {words.x, words.y, words.z, words.w};
     size_t columns = (size_t)w.groups * kGroup;
