@@ -31,8 +31,9 @@ namespace q4b {
 namespace {
 
 constexpr int kTcStages = 4;     // ring stages (one quantisation group each)
-constexpr int kTcSlots = 4;      // A-operand slots in TMEM (32 columns each)
-constexpr int kTcThreads = 320;  // warp 0 producer, warp 1 MMA, warps 2..9 dequantise + epilogue
+constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
+constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
+constexpr int kTcThreads = 64 + kTcWarpgroups * 128;  // warp 0 producer, warp 1 MMA, then the warpgroups
 constexpr long long kTcWaitLimit = 4000000000ll;
 
 struct TcParams {
@@ -140,7 +141,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     uint8_t *wbuf = base + kTcStages * kXBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wbuf + kTcStages * kWBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kTcStages + 2 * kTcSlots + 2);
-    float *exchange = reinterpret_cast<float *>(tmem_slot + 4);  // fused epilogue: [2 warpgroups][2][16][64]
+    float *exchange = reinterpret_cast<float *>(tmem_slot + 4);  // fused epilogue: [warpgroups][2][16][64]
     const uint32_t full0 = tc_smem_u32(bars), empty0 = full0 + 8 * kTcStages;
     const uint32_t a_full0 = empty0 + 8 * kTcStages, a_free0 = a_full0 + 8 * kTcSlots;
     const uint32_t d_full = a_free0 + 8 * kTcSlots, d_free = d_full + 8;
@@ -159,7 +160,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             tc_mbar_init(a_free0 + 8 * a, 1);
         }
         tc_mbar_init(d_full, 1);
-        tc_mbar_init(d_free, 8);
+        tc_mbar_init(d_free, 4 * kTcWarpgroups);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -256,7 +257,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             for (uint32_t g = 0; g < G && ok; ++g, ++it) {
                 const uint32_t s = it % kTcStages;
                 for (int once = 0; once < 1; ++once, ++unit) {
-                    if ((unit & 1u) != wg) continue;  // the two warpgroups take alternate groups
+                    if (unit % kTcWarpgroups != wg) continue;  // the warpgroups take groups in turn
                     const uint32_t a = unit % kTcSlots;
                     if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                     const uint8_t *tile_bytes = wbuf + s * kWBytes + tile_offset_bytes;
@@ -298,9 +299,10 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t n = FUSED ? nb * 64 + (row & 63) : nb * 128 + row;  // output feature of this thread
             const bool row_valid = n < p.w.rows;
             float *swap = exchange + wg * (2 * 16 * 64);
+            constexpr uint32_t kColumnsPerGroup = BN / kTcWarpgroups;
             uint32_t chunk = 0;
 #pragma unroll 1
-            for (uint32_t c = wg * (BN / 2); c < (wg + 1) * (BN / 2); c += 16, ++chunk) {
+            for (uint32_t c = wg * kColumnsPerGroup; c < (wg + 1) * kColumnsPerGroup; c += 16, ++chunk) {
                 uint32_t d0[16];
                 float other[16];
                 tc_load_16(tmem_d + c + lane_field, d0);
@@ -387,7 +389,7 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     p.m_blocks = ceil_div(args.m_rows, BN);
     const uint32_t tiles = p.n_blocks * p.m_blocks;
     const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
-                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + (FUSED ? 2 * 2 * 16 * 64 * 4 : 0) + 1024;
+                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + (FUSED ? kTcWarpgroups * 2 * 16 * 64 * 4 : 0) + 1024;
     auto kernel = tc_gemm_kernel<BN, FUSED>;
     static bool configured = false;
     if (!configured) {
