@@ -281,7 +281,11 @@ def run_ours(args):
                 "peak_source": f"of {peaks['source']}", "frac_of_8TBs": achieved / 8000.0,
                 "us_per_launch": kernel_ms * 1e3, "traffic": model.ncu_traffic_bytes()}
 
-    extras = {"whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
+    prefill = []
+    if world == 1 and not args.no_prefill:
+        prefill = prefill_gemm(q4b, ctx, model, peaks)
+    extras = {"prefill_gemm": prefill,
+              "whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
               "whole_step_frac_of_8TBs": value / world / 8000.0,
               "tflops": layer_flops * LAYERS / (ms_per_step * 1e-3) / 1e12}
 
@@ -300,6 +304,37 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def prefill_gemm(q4b, ctx, model, peaks, layers=8):
+    """BASELINE configs[3]: the same layer set at M in {512, 2048, 8192} on the tcgen05 GEMM, rotating over
+    `layers` layers of distinct weights; TFLOP/s = 2*M*N*K (x2 fused) over device time (CUDA events)."""
+    results = []
+    layer_set = q4b.LAYER_27B
+    for m in (512, 2048, 8192):
+        xs = {k: ctx.synth_x(m, 0, m, k) for k in sorted({p.k for p in layer_set})}
+        ys = {p.name: ctx.alloc(m * p.n * 2) for p in layer_set}
+        x_ptrs = {k: b.ptr for k, b in xs.items()}
+        y_ptrs = {name: b.ptr for name, b in ys.items()}
+
+        def run():
+            for layer in model.layers[:layers]:
+                layer.forward(x_ptrs, y_ptrs, m)
+        run()
+        ctx.sync()
+        reps = 3 if m <= 2048 else 2
+        ctx.timer_start()
+        for _ in range(reps):
+            run()
+        ms = ctx.sync(timed=True) / (reps * layers)
+        tflops = q4b.layer_flops(layer_set, m) / (ms * 1e-3) / 1e12
+        results.append({"m_rows": m, "ms_per_layer": ms, "tflops": tflops,
+                        "frac_of_measured_bf16_burst": tflops / peaks["bf16_tflops"],
+                        "frac_of_measured_bf16_sustained": tflops / peaks["bf16_tflops_sustained"],
+                        "frac_of_nominal_2250": tflops / 2250.0})
+        for b in list(xs.values()) + list(ys.values()):
+            b.free()
+    return results
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -308,6 +343,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--m", type=int, default=1, help="activation rows (1 decode, 4 verify)")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
+    parser.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

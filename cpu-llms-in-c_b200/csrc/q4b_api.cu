@@ -288,24 +288,25 @@ int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_mess
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "activation convert", status);
         x = context->x16;
     }
+    TcGemmArgs gemm = {};
     for (int s = 0; s < args.segments; ++s) {
-        TcGemmArgs gemm = {};
-        gemm.w = args.w[s];
-        gemm.up = args.up;
-        gemm.fused_silu = args.fused_silu;
-        gemm.x = x;
-        gemm.m_rows = args.m_rows;
-        gemm.y = args.y[s];
-        gemm.y_dtype = args.y_dtype;
-        gemm.ldy = args.ldy[s];
-        gemm.residual = s == 0 ? args.residual : nullptr;
-        gemm.residual_dtype = args.residual_dtype;
-        gemm.ld_residual = args.ld_residual;
-        gemm.status = context->status_device;
-        cudaError_t status = launch_tc_gemm(gemm, context->sm_count, context->stream);
-        if (!context->capturing) ++context->launches;
-        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "tensor-core gemm launch", status);
+        gemm.w[s] = args.w[s];
+        gemm.y[s] = args.y[s];
+        gemm.ldy[s] = args.ldy[s];
     }
+    gemm.segments = args.segments;
+    gemm.up = args.up;
+    gemm.fused_silu = args.fused_silu;
+    gemm.x = x;
+    gemm.m_rows = args.m_rows;
+    gemm.y_dtype = args.y_dtype;
+    gemm.residual = args.residual;
+    gemm.residual_dtype = args.residual_dtype;
+    gemm.ld_residual = args.ld_residual;
+    gemm.status = context->status_device;
+    cudaError_t status = launch_tc_gemm(gemm, context->sm_count, context->stream);
+    if (!context->capturing) ++context->launches;
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "tensor-core gemm launch", status);
     return Q4B_OK;
 }
 

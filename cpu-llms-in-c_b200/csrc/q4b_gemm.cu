@@ -38,12 +38,15 @@ constexpr long long kTcWaitLimit = 4000000000ll;
 
 struct TcParams {
     CUtensorMap x_map;  // X [M][K] fp16, box 64 x BN, 128-byte swizzle
-    WeightView w;
-    WeightView up;      // second matrix when two accumulators are fused
-    void *y;
-    const void *residual;
+    WeightView w[kMaxSegments];  // matrices that share X (one launch), e.g. q, k, v
+    WeightView up;               // second matrix of fused gate/up (single segment)
+    void *y[kMaxSegments];
+    uint32_t ldy[kMaxSegments];
+    uint32_t block_begin[kMaxSegments + 1];  // prefix sums of row blocks over the segments
+    int segments;
+    const void *residual;        // segment 0 only
     uint32_t *status;
-    uint32_t ldy, ld_residual;
+    uint32_t ld_residual;
     uint32_t m_rows, groups, n_blocks, m_blocks;
     int y_dtype, residual_dtype;
 };
@@ -181,7 +184,14 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const uint32_t nb = tile / p.m_blocks, mb = tile % p.m_blocks;
+                const uint32_t nb_all = tile / p.m_blocks, mb = tile % p.m_blocks;
+                int segment = 0;
+#pragma unroll
+                for (int q = 1; q < kMaxSegments; ++q) {
+                    if (q < p.segments && nb_all >= p.block_begin[q]) segment = q;
+                }
+                const uint32_t nb = nb_all - p.block_begin[segment];
+                const uint8_t *tiles = p.w[segment].tiles;
                 for (uint32_t g = 0; g < G; ++g, ++it) {
                     const uint32_t s = it % kTcStages;
                     if (it >= kTcStages && !tc_wait(empty0 + 8 * s, ((it / kTcStages) - 1) & 1)) {
@@ -193,7 +203,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t wdst = tc_smem_u32(wbuf) + s * kWBytes;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const uint8_t *stream = FUSED && h == 1 ? p.up.tiles : p.w.tiles;
+                        const uint8_t *stream = FUSED && h == 1 ? p.up.tiles : tiles;
                         const uint32_t block = FUSED ? nb : nb * 2 + h;  // 64-row block of that stream
                         const size_t offset = ((size_t)block * G + g) * kUnitBytes;
                         tc_bulk_copy(wdst + h * kUnitBytes, stream + offset, kUnitBytes, bar);
@@ -253,7 +263,13 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         const __half2 to_code_add = __half2half2(__ushort_as_half(hi ? 0xd400 : 0xe400));  // -64 or -1024
         uint32_t it = 0, unit = 0, tile_iter = 0;
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
-            const uint32_t nb = tile / p.m_blocks, mb = tile % p.m_blocks;
+            const uint32_t nb_all = tile / p.m_blocks, mb = tile % p.m_blocks;
+            int segment = 0;
+#pragma unroll
+            for (int q = 1; q < kMaxSegments; ++q) {
+                if (q < p.segments && nb_all >= p.block_begin[q]) segment = q;
+            }
+            const uint32_t nb = nb_all - p.block_begin[segment];
             for (uint32_t g = 0; g < G && ok; ++g, ++it) {
                 const uint32_t s = it % kTcStages;
                 for (int once = 0; once < 1; ++once, ++unit) {
@@ -297,7 +313,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             if (!tc_wait(d_full, tile_iter & 1)) { ok = false; break; }
             tc_fence_after();
             const uint32_t n = FUSED ? nb * 64 + (row & 63) : nb * 128 + row;  // output feature of this thread
-            const bool row_valid = n < p.w.rows;
+            const bool row_valid = n < p.w[segment].rows;
+            void *y_out = p.y[segment];
+            const uint32_t ldy = p.ldy[segment];
             float *swap = exchange + wg * (2 * 16 * 64);
             constexpr uint32_t kColumnsPerGroup = BN / kTcWarpgroups;
             uint32_t chunk = 0;
@@ -328,16 +346,16 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
                         value = (value / (1.0f + __expf(-value))) * other[j];
                     }
-                    if (p.residual != nullptr) {
+                    if (p.residual != nullptr && segment == 0) {
                         const size_t at = (size_t)m * p.ld_residual + n;
                         value += p.residual_dtype == kF32 ? reinterpret_cast<const float *>(p.residual)[at]
                                                           : __half2float(reinterpret_cast<const __half *>(p.residual)[at]);
                     }
-                    const size_t at = (size_t)m * p.ldy + n;
+                    const size_t at = (size_t)m * ldy + n;
                     if (p.y_dtype == kF32) {
-                        reinterpret_cast<float *>(p.y)[at] = value;
+                        reinterpret_cast<float *>(y_out)[at] = value;
                     } else {
-                        reinterpret_cast<__half *>(p.y)[at] = __float2half_rn(value);
+                        reinterpret_cast<__half *>(y_out)[at] = __float2half_rn(value);
                     }
                 }
             }
@@ -377,8 +395,8 @@ template <int BN, bool FUSED>
 cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr) return cudaErrorNotSupported;
-    const cuuint64_t dims[2] = {(cuuint64_t)args.w.groups * kGroup, (cuuint64_t)args.m_rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)args.w.groups * kGroup * sizeof(__half)};
+    const cuuint64_t dims[2] = {(cuuint64_t)args.w[0].groups * kGroup, (cuuint64_t)args.m_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)args.w[0].groups * kGroup * sizeof(__half)};
     const cuuint32_t box[2] = {(cuuint32_t)kGroup, (cuuint32_t)BN};
     const cuuint32_t element_strides[2] = {1, 1};
     if (encode(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(args.x), dims, strides, box,
@@ -405,19 +423,28 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
 }  // namespace
 
 cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
-    if (args.m_rows == 0 || args.w.rows == 0) return cudaSuccess;
+    if (args.m_rows == 0 || args.segments < 1 || args.segments > kMaxSegments) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(args.x) & 15u) != 0) return cudaErrorInvalidValue;
+    if (args.fused_silu && args.segments != 1) return cudaErrorInvalidValue;
     TcParams p = {};
-    p.w = args.w;
+    uint32_t blocks = 0;
+    for (int s = 0; s < args.segments; ++s) {
+        p.w[s] = args.w[s];
+        p.y[s] = args.y[s];
+        p.ldy[s] = args.ldy[s];
+        p.block_begin[s] = blocks;
+        blocks += ceil_div(args.w[s].rows, args.fused_silu ? 64 : 128);
+    }
+    for (int s = args.segments; s <= kMaxSegments; ++s) p.block_begin[s] = blocks;
+    p.segments = args.segments;
     p.up = args.up;
-    p.y = args.y;
     p.residual = args.residual;
     p.status = args.status;
-    p.ldy = args.ldy;
     p.ld_residual = args.ld_residual;
     p.m_rows = args.m_rows;
-    p.groups = args.w.groups;
-    p.n_blocks = ceil_div(args.w.rows, args.fused_silu ? 64 : 128);
+    p.groups = args.w[0].groups;
+    p.n_blocks = blocks;
+    if (blocks == 0) return cudaSuccess;
     p.y_dtype = args.y_dtype;
     p.residual_dtype = args.residual_dtype;
     if (args.fused_silu) {

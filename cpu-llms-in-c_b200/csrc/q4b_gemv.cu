@@ -70,7 +70,7 @@ struct GemvParams {
     uint32_t m_rows;
     uint32_t groups;
     uint32_t stages;
-    uint32_t x_groups;     // groups of x staged per row (min(range, G))
+    uint32_t units_per_cta, units_extra;  // U / ctas and U % ctas
     uint32_t local_blocks; // row blocks a CTA's range can touch
     uint32_t total_units;
     int y_dtype, residual_dtype;
@@ -117,20 +117,51 @@ __device__ inline void consumer_barrier(uint32_t threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
+// the CTA whose range holds unit `unit` when the first `extra` CTAs own share+1 units and the rest share
+__device__ inline uint32_t cta_of_unit(uint32_t unit, uint32_t share, uint32_t extra) {
+    const uint32_t boundary = extra * (share + 1);
+    return unit < boundary ? unit / (share + 1) : extra + (unit - boundary) / share;
+}
+
 // D = A * B + C with C given (first == false) or zero (first == true)
 __device__ inline void mma_16816(float d[4], const uint32_t a[4], uint32_t b0, uint32_t b1, bool first) {
     if (first) {
-        asm volatile(
+        asm(
             "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
             "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
             : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
     } else {
-        asm volatile(
+        asm(
             "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
             "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+
+// 16 consecutive activations of row m as 8 half2 registers (zeros past M)
+template <bool X32>
+__device__ inline void load_x16(const void *x, size_t element, bool valid, uint32_t out[8]) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = 0u;
+        return;
+    }
+    if constexpr (X32) {
+        const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + element);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float4 v = __ldg(p + i);
+            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+            out[2 * i] = *reinterpret_cast<uint32_t *>(&lo);
+            out[2 * i + 1] = *reinterpret_cast<uint32_t *>(&hi);
+        }
+    } else {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(x) + element);
+        uint4 a = __ldg(p), b = __ldg(p + 1);
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
     }
 }
 
@@ -139,20 +170,19 @@ __device__ inline void mma_16816(float d[4], const uint32_t a[4], uint32_t b0, u
 // SUBN : feed the codes to the tensor pipe as fp16 subnormals (no unpack math)
 // X32  : x arrives as fp32 and is rounded to fp16 while it is staged
 //
-// Warps 0..7 consume, warp 8 produces.  A ring stage holds up to 8 "sub-units"
-// (2304 bytes: the four tiles of one 64-row block x one group of one matrix) that
-// all belong to the same row block: 8 consecutive groups, or 4 groups of gate
-// followed by the same 4 groups of up.  Consumer warp w takes sub-unit w: four
-// independent tiles per stage, accumulated in registers across stages.
+// Warps 0..7 consume, warp 8 produces.  A ring stage holds up to 8 consecutive
+// groups of one 64-row block (8 x 2304 bytes, one bulk copy; fused gate/up adds the
+// same groups of the second matrix as a second copy).  Consumer warp w takes group
+// w of the stage: four independent tiles (eight when fused, sharing one read of
+// x), accumulated in registers across stages.
 template <int NT, bool FUSED, bool SUBN, bool X32>
-__global__ void __launch_bounds__(288, NT > 1 ? 2 : 3)
+__global__ void __launch_bounds__(288, (FUSED && NT > 1) ? 1 : 2)
 gemv_kernel(const GemvParams p) {
     constexpr int NW = FUSED ? 2 : 1;
     constexpr int W = 8;                             // consumer warps
-    constexpr uint32_t S = W / NW;                   // groups per full stage
-    constexpr uint32_t MC = 8 * NT;                  // output columns held per warp
+    constexpr uint32_t S = W;                        // groups per full stage
     constexpr uint32_t PER_CTA = NW * NT * 4 * 128;  // partial sums of one 64-row block
-    constexpr uint32_t kStageBytes = W * kUnitBytes;
+    constexpr uint32_t kStageBytes = NW * W * kUnitBytes;  // larger copies stream faster
     constexpr uint32_t kConsumers = W * 32;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     // dependents may start at once: all they do before their own wait is prefetch weights
@@ -162,20 +192,19 @@ gemv_kernel(const GemvParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, t = lane & 3;
     const uint32_t G = p.groups, U = p.total_units, ctas = gridDim.x, cta = blockIdx.x;
-    const uint32_t u0 = (uint32_t)((uint64_t)U * cta / ctas);
-    const uint32_t u1 = (uint32_t)((uint64_t)U * (cta + 1) / ctas);
-    const uint32_t range = u1 - u0;
+    // CTA c owns units [u0, u1): the first U % ctas CTAs take one unit more
+    const uint32_t share = p.units_per_cta, extra = p.units_extra;
+    const uint32_t u0 = cta * share + min(cta, extra);
+    const uint32_t range = share + (cta < extra ? 1u : 0u);
+    const uint32_t u1 = u0 + range;
+    (void)U;
+    (void)ctas;
     const uint32_t stages = p.stages;
     const uint32_t grb0 = u0 / G, g_first = u0 % G;
-    const bool windowed = p.x_groups < G;  // x is staged per unit of the range, not per group
-    const uint32_t x_count = windowed ? range : G;
-    const uint32_t x_stride = p.x_groups * kGroup + 8;  // halves; +16 bytes de-phases the rows
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[kMaxStages], empty[kMaxStages]
     uint8_t *ring = smem_raw + 128;
-    __half *xs = reinterpret_cast<__half *>(ring + (size_t)stages * kStageBytes);  // [M][x_stride]
-    float *sx = reinterpret_cast<float *>(xs + (size_t)p.m_rows * x_stride);      // [x_groups][MC]
-    float *red = sx + (size_t)p.x_groups * MC;                                     // [L][PER_CTA]
+    float *red = reinterpret_cast<float *>(ring + (size_t)stages * kStageBytes);   // [L][PER_CTA]
     uint32_t *flags = reinterpret_cast<uint32_t *>(red + (size_t)p.local_blocks * PER_CTA);  // [L]
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
     const uint32_t ring0 = smem_u32(ring);
@@ -188,6 +217,7 @@ gemv_kernel(const GemvParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    for (uint32_t i = threadIdx.x; i < p.local_blocks * PER_CTA; i += blockDim.x) red[i] = 0.0f;
     __syncthreads();
 
     bool ok = true;
@@ -239,75 +269,38 @@ gemv_kernel(const GemvParams p) {
     if (warp < W) {
         const size_t K = (size_t)G * kGroup;
         const uint32_t m_rows = p.m_rows;
-        const uint32_t k_mine = FUSED ? (uint32_t)warp / S : 0u;  // matrix of this warp's sub-unit
-        const uint32_t j_mine = FUSED ? (uint32_t)warp % S : (uint32_t)warp;
-        // ---- stage x (fp16) for the groups this CTA meets; clear the block sums ----
-        for (uint32_t i = threadIdx.x; i < m_rows * x_count * 8; i += kConsumers) {
-            const uint32_t m = i / (x_count * 8), rest = i % (x_count * 8), li = rest >> 3, c8 = rest & 7u;
-            uint32_t g = windowed ? g_first + li : li;
-            if (g >= G) g %= G;
-            const size_t element = (size_t)m * K + (size_t)g * kGroup + 8 * c8;
-            uint4 value;
-            if constexpr (X32) {
-                const float4 *src = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + element);
-                float4 a = __ldg(src), b = __ldg(src + 1);
-                __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
-                __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
-                value = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                                   *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
-            } else {
-                value = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.x) + element));
-            }
-            *reinterpret_cast<uint4 *>(xs + (size_t)m * x_stride + li * kGroup + 8 * c8) = value;
-        }
-        for (uint32_t i = threadIdx.x; i < p.local_blocks * PER_CTA; i += kConsumers) red[i] = 0.0f;
-        consumer_barrier(kConsumers);
+        const uint32_t j_mine = (uint32_t)warp;  // this warp's group inside a stage
         Q4B_STAMP(3);
-        // ---- group sums of the staged x; columns past M stay zero ----
-        for (uint32_t i = threadIdx.x; i < x_count * MC; i += kConsumers) {
-            const uint32_t li = i / MC, m = i % MC;
-            float total = 0.0f;
-            if (m < m_rows) {
-                const uint4 *row = reinterpret_cast<const uint4 *>(xs + (size_t)m * x_stride + li * kGroup);
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    uint4 v = row[c];
-                    const uint32_t reg[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&reg[q]));
-                        total += f.x + f.y;
-                    }
-                }
-            }
-            sx[i] = total;
-        }
-        consumer_barrier(kConsumers);
         Q4B_STAMP(4);
 
-        float acc[4][NT][4];
+        float acc[NW][4][NT][4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
+        for (int k = 0; k < NW; ++k)
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
+            for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[r][n][j] = 0.0f;
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[k][r][n][j] = 0.0f;
         // Add every warp's sums of a finished row block into the CTA's block sums,
         // one warp at a time in warp order, so the result does not depend on timing.
         auto flush = [&](uint32_t lrb) {
-            float *target = red + (size_t)lrb * PER_CTA + k_mine * (NT * 512);
+            float *target = red + (size_t)lrb * PER_CTA;
             for (int turn = 0; turn < W; ++turn) {
                 if (warp == turn) {
 #pragma unroll
-                    for (int n = 0; n < NT; ++n)
+                    for (int k = 0; k < NW; ++k)
 #pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            float4 *at = reinterpret_cast<float4 *>(target) + (n * 4 + r) * 32 + lane;
-                            float4 v = *at;
-                            v.x += acc[r][n][0]; v.y += acc[r][n][1]; v.z += acc[r][n][2]; v.w += acc[r][n][3];
-                            *at = v;
-                            acc[r][n][0] = acc[r][n][1] = acc[r][n][2] = acc[r][n][3] = 0.0f;
-                        }
+                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) {
+                                float4 *at = reinterpret_cast<float4 *>(target + k * (NT * 512)) + (n * 4 + r) * 32 + lane;
+                                float4 v = *at;
+                                v.x += acc[k][r][n][0]; v.y += acc[k][r][n][1];
+                                v.z += acc[k][r][n][2]; v.w += acc[k][r][n][3];
+                                *at = v;
+                                acc[k][r][n][0] = acc[k][r][n][1] = acc[k][r][n][2] = acc[k][r][n][3] = 0.0f;
+                            }
                 }
                 consumer_barrier(kConsumers);
             }
@@ -332,58 +325,70 @@ gemv_kernel(const GemvParams p) {
             Q4B_ADD(8, clock64() - wait_begin);
             Q4B_ADD(9, 1);
             if (j_mine < count) {
-                const uint32_t li = windowed ? ua - u0 + j_mine : g + j_mine;
+                // B fragments straight from global memory (x is small and stays in L1/L2):
+                // lane (gid, t) holds x[m = gid][64 g + 16 t .. +15] for each column tile
+                const uint32_t group = g + j_mine;
                 uint32_t xb[NT][8];
                 float2 sums[NT];
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
                     const uint32_t m = n * 8 + gid;
-                    if (m < m_rows) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(xs + (size_t)m * x_stride + li * kGroup + 16 * t);
-                        uint4 a = src[0], b = src[1];
-                        xb[n][0] = a.x; xb[n][1] = a.y; xb[n][2] = a.z; xb[n][3] = a.w;
-                        xb[n][4] = b.x; xb[n][5] = b.y; xb[n][6] = b.z; xb[n][7] = b.w;
-                    } else {
+                    load_x16<X32>(p.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, xb[n]);
+                    // group sums of x on the tensor pipe: a fragment of ones times the same B
+                    const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+                    float total[4];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) xb[n][i] = 0u;
-                    }
-                    sums[n] = *reinterpret_cast<const float2 *>(&sx[li * MC + n * 8 + 2 * t]);
+                    for (int i = 0; i < 4; ++i) mma_16816(total, ones, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
+                    sums[n] = make_float2(total[0], total[1]);
                 }
-                const uint8_t *unit = ring + (size_t)s * kStageBytes + (size_t)(k_mine * S + j_mine) * kUnitBytes;
+#pragma unroll
+                for (int k = 0; k < NW; ++k) {
+                const uint8_t *unit = ring + (size_t)s * kStageBytes + (size_t)(k * S + j_mine) * kUnitBytes;
+                // the four tiles of the sub-unit advance together, word by word, so that
+                // consecutive MMAs in the instruction stream are independent of each other
+                uint4 codes[4];
+                uint2 meta[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const uint8_t *tile = unit + r * kTileBytes;
-                    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
-                    const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
-                    const uint32_t word[4] = {codes.x, codes.y, codes.z, codes.w};
-                    float c[NT][4];
+                    codes[r] = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
+                    meta[r] = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
+                }
+                float c[4][NT][4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t word = i == 0 ? codes[r].x : i == 1 ? codes[r].y : i == 2 ? codes[r].z : codes[r].w;
                         uint32_t a[4];
                         if constexpr (SUBN) {
-                            word_to_codes_subnormal(word[i], a);
+                            word_to_codes_subnormal(word, a);
                         } else {
                             __half2 h[4];
-                            word_to_codes_f16(word[i], h);
+                            word_to_codes_f16(word, h);
 #pragma unroll
                             for (int q = 0; q < 4; ++q) a[q] = *reinterpret_cast<uint32_t *>(&h[q]);
                         }
 #pragma unroll
-                        for (int n = 0; n < NT; ++n) mma_16816(c[n], a, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
+                        for (int n = 0; n < NT; ++n) mma_16816(c[r][n], a, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
                     }
-                    float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
-                    float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta[r].x));
+                    float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta[r].y));
                     if constexpr (SUBN) {
                         lo.x *= 16777216.0f;  // codes arrived as q * 2^-24
                         hi.x *= 1048576.0f;   // and 16 q * 2^-24
                     }
 #pragma unroll
                     for (int n = 0; n < NT; ++n) {
-                        acc[r][n][0] = fmaf(lo.x, c[n][0], fmaf(lo.y, sums[n].x, acc[r][n][0]));
-                        acc[r][n][1] = fmaf(lo.x, c[n][1], fmaf(lo.y, sums[n].y, acc[r][n][1]));
-                        acc[r][n][2] = fmaf(hi.x, c[n][2], fmaf(hi.y, sums[n].x, acc[r][n][2]));
-                        acc[r][n][3] = fmaf(hi.x, c[n][3], fmaf(hi.y, sums[n].y, acc[r][n][3]));
+                        acc[k][r][n][0] = fmaf(lo.x, c[r][n][0], fmaf(lo.y, sums[n].x, acc[k][r][n][0]));
+                        acc[k][r][n][1] = fmaf(lo.x, c[r][n][1], fmaf(lo.y, sums[n].y, acc[k][r][n][1]));
+                        acc[k][r][n][2] = fmaf(hi.x, c[r][n][2], fmaf(hi.y, sums[n].x, acc[k][r][n][2]));
+                        acc[k][r][n][3] = fmaf(hi.x, c[r][n][3], fmaf(hi.y, sums[n].y, acc[k][r][n][3]));
                     }
+                }
                 }
             }
             __syncwarp();
@@ -406,26 +411,27 @@ gemv_kernel(const GemvParams p) {
     for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
         const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
         if (contributed == G) continue;
-        const uint32_t first_cta = (uint32_t)((((uint64_t)grb * G + 1) * ctas + U - 1) / U) - 1;
+        const uint32_t first_cta = cta_of_unit(grb * G, share, extra);
         const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
         float *slot = p.scratch + ((size_t)grb * p.slots + (cta - first_cta)) * PER_CTA;
         for (uint32_t o = threadIdx.x; o < PER_CTA; o += blockDim.x) slot[o] = mine[o];
     }
     __syncthreads();
     // (2) one thread publishes them and learns which blocks this CTA completes
-    if (threadIdx.x == 0) {
-        __threadfence();
-        for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
-            const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
-            uint32_t finish = 1;
-            if (contributed != G) {
-                const uint32_t before = atomicAdd(p.counters + grb, contributed);
-                finish = before + contributed == G ? 2u : 0u;
-                if (finish) p.counters[grb] = 0;  // ready for the next launch
+    if (threadIdx.x <= grb_last - grb0) {  // one thread per row block, their round trips overlap
+        const uint32_t grb = grb0 + threadIdx.x;
+        const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
+        uint32_t finish = 1;
+        if (contributed != G) {
+            __threadfence();
+            const uint32_t before = atomicAdd(p.counters + grb, contributed);
+            finish = before + contributed == G ? 2u : 0u;
+            if (finish) {
+                p.counters[grb] = 0;  // ready for the next launch
+                __threadfence();
             }
-            flags[grb - grb0] = finish;
         }
-        __threadfence();
+        flags[grb - grb0] = finish;
     }
     __syncthreads();
     // (3) outputs of the blocks that are complete here
@@ -433,8 +439,8 @@ gemv_kernel(const GemvParams p) {
         const uint32_t finish = flags[grb - grb0];
         if (finish == 0) continue;
         const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
-        const uint32_t first_cta = (uint32_t)((((uint64_t)grb * G + 1) * ctas + U - 1) / U) - 1;
-        const uint32_t last_cta = (uint32_t)((((uint64_t)(grb + 1) * G) * ctas + U - 1) / U) - 1;
+        const uint32_t first_cta = cta_of_unit(grb * G, share, extra);
+        const uint32_t last_cta = cta_of_unit((grb + 1) * G - 1, share, extra);
         const uint32_t contributors = last_cta - first_cta + 1;
         const float *slots = p.scratch + ((size_t)grb * p.slots) * PER_CTA;
         int segment = 0;
@@ -557,6 +563,7 @@ cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *sc
 }
 
 // variant encoding (0 = heuristics): bits 0-3 CTAs per SM, 8-11 ring stages,
+// bit 12 equal unit ranges even when an even split of the row blocks exists,
 // bit 13 exact-fp16 codes instead of subnormals, bit 14 no programmatic
 // dependent launch
 cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan) {
@@ -570,13 +577,24 @@ cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan 
     const uint32_t units = (uint32_t)units64;
 
     int per_sm = variant & 0xf, stages = (variant >> 8) & 0xf;
-    if (per_sm == 0) per_sm = 1;
-    if (stages == 0) stages = 3;
+    if (per_sm == 0) per_sm = 2;
+    if (stages == 0) stages = NW == 2 ? 2 : 4;
     if (stages > kMaxStages) stages = kMaxStages;
-    uint32_t ctas = (uint32_t)sm_count * per_sm;
-    const uint32_t stage_groups = 8 / NW;
+    const uint32_t slots_on_chip = (uint32_t)sm_count * per_sm;
+    uint32_t ctas = slots_on_chip;
+    const uint32_t stage_groups = 8;
     const uint32_t by_work = units / stage_groups > 0 ? units / stage_groups : 1;  // a stage or more per CTA
     if (ctas > by_work) ctas = by_work;
+    // Prefer an even split: every CTA inside one row block, every block cut into
+    // the same number of parts (one part = no cross-CTA sum at all).  All CTAs
+    // are resident at once and stream equal shares, so they finish together.
+    if (blocks <= slots_on_chip && ((variant >> 12) & 1) == 0) {
+        uint32_t parts = 0;
+        for (uint32_t k = 1; k <= G; ++k) {
+            if (G % k == 0 && blocks * k <= slots_on_chip && (G / k >= 4 || k == 1)) parts = k;
+        }
+        if (parts > 0) ctas = blocks * parts;
+    }
     const uint32_t max_range = ceil_div(units, ctas);
     const uint32_t needed = ceil_div(max_range, stage_groups) + 1;
     if ((uint32_t)stages > needed) stages = needed < 2 ? 2 : needed;
@@ -587,15 +605,12 @@ cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan 
     plan->stage_units = stage_groups;
     plan->total_units = units;
     plan->blocks = blocks;
-    plan->x_groups = max_range < G ? max_range : G;
     plan->local_blocks = (max_range - 1) / G + 2;
     plan->slots = ceil_div(G, units / ctas > 0 ? units / ctas : 1) + 1;
     const size_t per_cta_floats = (size_t)NW * NT * 4 * 128;
     plan->scratch_bytes = (size_t)blocks * plan->slots * per_cta_floats * 4;
     plan->counter_bytes = (size_t)blocks * 4;
-    plan->smem_bytes = 128 + (size_t)stages * 8 * kUnitBytes +
-                       (size_t)args.m_rows * (plan->x_groups * kGroup + 8) * 2 +
-                       (size_t)plan->x_groups * 8 * NT * 4 +
+    plan->smem_bytes = 128 + (size_t)stages * NW * 8 * kUnitBytes +
                        (size_t)plan->local_blocks * per_cta_floats * 4 + (size_t)plan->local_blocks * 4 + 16;
     if (plan->smem_bytes > 220 * 1024) return cudaErrorInvalidValue;
     return cudaSuccess;
@@ -624,7 +639,8 @@ cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant,
     p.m_rows = args.m_rows;
     p.groups = args.w[0].groups;
     p.stages = plan.stages;
-    p.x_groups = plan.x_groups;
+    p.units_per_cta = plan.total_units / plan.ctas;
+    p.units_extra = plan.total_units % plan.ctas;
     p.local_blocks = plan.local_blocks;
     p.total_units = plan.total_units;
     p.y_dtype = args.y_dtype;

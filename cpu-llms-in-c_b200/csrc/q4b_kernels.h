@@ -47,7 +47,7 @@ struct GemvArgs {
 // launch geometry and the scratch a launch needs, derived from the shapes alone
 struct GemvPlan {
     uint32_t ctas, threads, stages, stage_units, total_units, blocks;
-    uint32_t x_groups, local_blocks, slots;
+    uint32_t local_blocks, slots;
     size_t smem_bytes, scratch_bytes, counter_bytes;
 };
 // variant: 0 = default; other values select alternatives for A/B measurements
@@ -60,14 +60,15 @@ cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *sc
 
 // ---- q4b_gemm.cu: tcgen05 prefill GEMM ----
 struct TcGemmArgs {
-    WeightView w;
-    WeightView up;        // valid when fused_silu
+    WeightView w[kMaxSegments];  // matrices that share x (same K), one launch
+    void *y[kMaxSegments];       // [M][ldy]
+    uint32_t ldy[kMaxSegments];
+    int segments;
+    WeightView up;        // valid when fused_silu (single segment)
     int fused_silu;
     const void *x;        // [M][K] fp16, 16-byte aligned
     uint32_t m_rows;
-    void *y;              // [M][ldy]
     int y_dtype;
-    uint32_t ldy;
     const void *residual; // [M][ld_residual] or null
     int residual_dtype;
     uint32_t ld_residual;

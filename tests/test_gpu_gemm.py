@@ -100,3 +100,22 @@ def test_gemm_full_size_agrees_with_small_m_kernel(q4b, orc, ctx, name, k, n):
     ref = oracle_rows(orc, quants, meta, k // 64, x_rows, rows)
     assert_close(small[:, rows], ref, f"{name} small-M")
     assert_close(y[picks][:, rows], ref, f"{name} gemm")
+
+
+def test_gemm_grouped_launch(q4b, orc, ctx):
+    # q, k, v share x and one launch (the reference fuses them into one matrix)
+    k, m = 1024, 150
+    shapes = [640, 128, 200]
+    x = orc.synth_x(0, 0, m, k)
+    dx = ctx.to_device(x)
+    weights, refs = [], []
+    for index, n in enumerate(shapes):
+        quants, meta = orc.synth_weight(0, index, n, k // 64)
+        weights.append(ctx.upload(quants, meta, n, k // 64))
+        refs.append(orc.matmul(quants, meta, k // 64, x, want32=False)[1])
+    outs = [ctx.alloc(m * n * 2) for n in shapes]
+    before = ctx.launches
+    ctx.matmul_group(weights, dx.ptr, q4b.F16, m, [o.ptr for o in outs])
+    assert ctx.launches - before == 1
+    for n, out, ref in zip(shapes, outs, refs):
+        assert_close(out.download(np.float16, (m, n)), ref, f"group member {n}")
