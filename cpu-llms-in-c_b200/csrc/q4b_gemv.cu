@@ -70,7 +70,8 @@ struct GemvParams {
     uint32_t m_rows;
     uint32_t groups;
     uint32_t stages;
-    uint32_t units_per_cta, units_extra;  // U / ctas and U % ctas
+    uint32_t units_per_cta, units_extra;  // U / ctas and U % ctas (equal-range mode)
+    uint32_t parts;                       // > 0: every row block is cut into `parts` CTAs
     uint32_t local_blocks; // row blocks a CTA's range can touch
     uint32_t total_units;
     int y_dtype, residual_dtype;
@@ -193,9 +194,17 @@ gemv_kernel(const GemvParams p) {
     const int gid = lane >> 2, t = lane & 3;
     const uint32_t G = p.groups, U = p.total_units, ctas = gridDim.x, cta = blockIdx.x;
     // CTA c owns units [u0, u1): the first U % ctas CTAs take one unit more
-    const uint32_t share = p.units_per_cta, extra = p.units_extra;
-    const uint32_t u0 = cta * share + min(cta, extra);
-    const uint32_t range = share + (cta < extra ? 1u : 0u);
+    const uint32_t share = p.units_per_cta, extra = p.units_extra, parts = p.parts;
+    uint32_t u0, range;
+    if (parts > 0) {  // CTA = (row block, part): groups [G*j/parts, G*(j+1)/parts) of that block
+        const uint32_t block = cta / parts, j = cta % parts;
+        const uint32_t from = G * j / parts, to = G * (j + 1) / parts;
+        u0 = block * G + from;
+        range = to - from;
+    } else {
+        u0 = cta * share + min(cta, extra);
+        range = share + (cta < extra ? 1u : 0u);
+    }
     const uint32_t u1 = u0 + range;
     (void)U;
     (void)ctas;
@@ -215,10 +224,12 @@ gemv_kernel(const GemvParams p) {
             mbar_init(empty0 + 8 * s, W);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    Q4B_STAMP(10);
     for (uint32_t i = threadIdx.x; i < p.local_blocks * PER_CTA; i += blockDim.x) red[i] = 0.0f;
+    Q4B_STAMP(11);
     __syncthreads();
+    Q4B_STAMP(12);
 
     bool ok = true;
     if (warp == W && lane == 0) {
@@ -398,7 +409,30 @@ gemv_kernel(const GemvParams p) {
             if (g == G) { g = 0; ++grb; }
         }
         Q4B_STAMP(5);
-        if (ok && range > 0) flush(cur_grb - grb0);
+        if (ok && range > 0) {
+            // Last row block of the range: the ring is drained, so every warp parks its
+            // sums in its own slice of it at once and the block sums are formed in one
+            // pass, still in warp order.
+            consumer_barrier(kConsumers);
+            float *parked = reinterpret_cast<float *>(ring);  // [W][PER_CTA]
+#pragma unroll
+            for (int k = 0; k < NW; ++k)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        reinterpret_cast<float4 *>(parked + (size_t)warp * PER_CTA + k * (NT * 512))[(n * 4 + r) * 32 + lane] =
+                            make_float4(acc[k][r][n][0], acc[k][r][n][1], acc[k][r][n][2], acc[k][r][n][3]);
+                    }
+            consumer_barrier(kConsumers);
+            float *target = red + (size_t)(cur_grb - grb0) * PER_CTA;
+            for (uint32_t o = threadIdx.x; o < PER_CTA; o += kConsumers) {
+                float total = target[o];
+#pragma unroll
+                for (int wv = 0; wv < W; ++wv) total += parked[(size_t)wv * PER_CTA + o];
+                target[o] = total;
+            }
+        }
         if (!ok && lane == 0) atomicExch(p.status, 0x52u);
     }
     __syncthreads();
@@ -411,7 +445,7 @@ gemv_kernel(const GemvParams p) {
     for (uint32_t grb = grb0; grb <= grb_last; ++grb) {
         const uint32_t contributed = min(u1, (grb + 1) * G) - max(u0, grb * G);
         if (contributed == G) continue;
-        const uint32_t first_cta = cta_of_unit(grb * G, share, extra);
+        const uint32_t first_cta = parts > 0 ? grb * parts : cta_of_unit(grb * G, share, extra);
         const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
         float *slot = p.scratch + ((size_t)grb * p.slots + (cta - first_cta)) * PER_CTA;
         for (uint32_t o = threadIdx.x; o < PER_CTA; o += blockDim.x) slot[o] = mine[o];
@@ -439,8 +473,8 @@ gemv_kernel(const GemvParams p) {
         const uint32_t finish = flags[grb - grb0];
         if (finish == 0) continue;
         const float *mine = red + (size_t)(grb - grb0) * PER_CTA;
-        const uint32_t first_cta = cta_of_unit(grb * G, share, extra);
-        const uint32_t last_cta = cta_of_unit((grb + 1) * G - 1, share, extra);
+        const uint32_t first_cta = parts > 0 ? grb * parts : cta_of_unit(grb * G, share, extra);
+        const uint32_t last_cta = parts > 0 ? first_cta + parts - 1 : cta_of_unit((grb + 1) * G - 1, share, extra);
         const uint32_t contributors = last_cta - first_cta + 1;
         const float *slots = p.scratch + ((size_t)grb * p.slots) * PER_CTA;
         int segment = 0;
@@ -588,14 +622,15 @@ cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan 
     // Prefer an even split: every CTA inside one row block, every block cut into
     // the same number of parts (one part = no cross-CTA sum at all).  All CTAs
     // are resident at once and stream equal shares, so they finish together.
+    uint32_t parts = 0;
     if (blocks <= slots_on_chip && ((variant >> 12) & 1) == 0) {
-        uint32_t parts = 0;
         for (uint32_t k = 1; k <= G; ++k) {
-            if (G % k == 0 && blocks * k <= slots_on_chip && (G / k >= 4 || k == 1)) parts = k;
+            if (blocks * k <= slots_on_chip && (G / k >= 4 || k == 1)) parts = k;
         }
         if (parts > 0) ctas = blocks * parts;
     }
-    const uint32_t max_range = ceil_div(units, ctas);
+    plan->parts = parts;
+    const uint32_t max_range = parts > 0 ? ceil_div(G, parts) : ceil_div(units, ctas);
     const uint32_t needed = ceil_div(max_range, stage_groups) + 1;
     if ((uint32_t)stages > needed) stages = needed < 2 ? 2 : needed;
 
@@ -606,7 +641,7 @@ cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan 
     plan->total_units = units;
     plan->blocks = blocks;
     plan->local_blocks = (max_range - 1) / G + 2;
-    plan->slots = ceil_div(G, units / ctas > 0 ? units / ctas : 1) + 1;
+    plan->slots = parts > 0 ? parts : ceil_div(G, units / ctas > 0 ? units / ctas : 1) + 1;
     const size_t per_cta_floats = (size_t)NW * NT * 4 * 128;
     plan->scratch_bytes = (size_t)blocks * plan->slots * per_cta_floats * 4;
     plan->counter_bytes = (size_t)blocks * 4;
@@ -641,6 +676,7 @@ cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant,
     p.stages = plan.stages;
     p.units_per_cta = plan.total_units / plan.ctas;
     p.units_extra = plan.total_units % plan.ctas;
+    p.parts = plan.parts;
     p.local_blocks = plan.local_blocks;
     p.total_units = plan.total_units;
     p.y_dtype = args.y_dtype;

@@ -47,7 +47,7 @@ struct GemvArgs {
 // launch geometry and the scratch a launch needs, derived from the shapes alone
 struct GemvPlan {
     uint32_t ctas, threads, stages, stage_units, total_units, blocks;
-    uint32_t local_blocks, slots;
+    uint32_t local_blocks, slots, parts;
     size_t smem_bytes, scratch_bytes, counter_bytes;
 };
 // variant: 0 = default; other values select alternatives for A/B measurements
