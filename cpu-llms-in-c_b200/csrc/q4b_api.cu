@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <vector>
 
 using namespace q4b;
 
@@ -37,6 +38,19 @@ struct q4b_weight {
     uint32_t rows_total;  // rows of the source matrix
     uint32_t row_begin;   // first source row held
     int device;
+};
+
+struct q4b_sequence {
+    std::vector<DecodeJob> jobs;
+    uint32_t m_rows, world, rank, epoch;
+    int device;
+    bool finalized;
+    DecodeJob *device_jobs;
+    uint32_t *done;
+    uint32_t *peer_done[kMaxPeers];
+    float *scratch;
+    uint32_t *counters;
+    SequenceLaunch launch;
 };
 
 struct q4b_graph {
@@ -828,6 +842,215 @@ int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm
     if (status != cudaSuccess) return device_failure(error_message, error_capacity, "probe", status);
     *gigabytes_per_second = (double)bytes * iterations / (ms * 1e-3) / 1e9;
     return Q4B_OK;
+}
+
+/* ---------------------------------------------------------------- sequences */
+int q4b_sequence_create(q4b_context *context, uint32_t m_rows, uint32_t world, uint32_t rank,
+                        q4b_sequence **sequence, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (sequence == nullptr || m_rows == 0 || m_rows > 16 || world == 0 || world > (uint32_t)kMaxPeers || rank >= world) {
+        set_error(error_message, error_capacity, "a sequence takes 1..16 activation rows and 1..%d ranks", kMaxPeers);
+        return Q4B_BAD_ARGUMENT;
+    }
+    q4b_sequence *result = new (std::nothrow) q4b_sequence();
+    if (result == nullptr) return Q4B_DEVICE_FAILURE;
+    result->m_rows = m_rows;
+    result->world = world;
+    result->rank = rank;
+    result->device = context->device;
+    *sequence = result;
+    return Q4B_OK;
+}
+
+static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights, int count, const q4b_weight *up,
+                        const void *x, void *const *y, const uint32_t *ldy, int y_dtype, char *error_message,
+                        size_t error_capacity) {
+    if (sequence == nullptr || sequence->finalized || weights == nullptr || y == nullptr || ldy == nullptr ||
+        x == nullptr || count < 1 || count > kMaxSegments || !valid_activation_dtype(y_dtype) || !aligned16(x)) {
+        set_error(error_message, error_capacity, "invalid job (1..%d matrices, 16-byte aligned fp16 x, fp16/fp32 y)",
+                  kMaxSegments);
+        return Q4B_BAD_ARGUMENT;
+    }
+    DecodeJob job = {};
+    for (int s = 0; s < count; ++s) {
+        if (weights[s] == nullptr || y[s] == nullptr || weights[s]->device != sequence->device ||
+            weights[s]->view.groups != weights[0]->view.groups || ldy[s] < weights[s]->view.rows) {
+            set_error(error_message, error_capacity, "matrices of a job must live on the context's device, share K and fit ldy");
+            return Q4B_BAD_ARGUMENT;
+        }
+        job.tiles[s] = weights[s]->view.tiles;
+        job.rows[s] = weights[s]->view.rows;
+        job.ldy[s] = ldy[s];
+        job.y[s][sequence->rank] = y[s];
+    }
+    if (up != nullptr) {
+        if (count != 1 || up->view.rows != weights[0]->view.rows || up->view.groups != weights[0]->view.groups) {
+            set_error(error_message, error_capacity, "gate and up must have the same shape");
+            return Q4B_BAD_ARGUMENT;
+        }
+        job.up_tiles = up->view.tiles;
+        job.fused = 1;
+    }
+    job.x = x;
+    job.groups = weights[0]->view.groups;
+    job.segments = (uint32_t)count;
+    job.y_dtype = (uint32_t)y_dtype;
+    sequence->jobs.push_back(job);
+    return Q4B_OK;
+}
+
+int q4b_sequence_add_matmul(q4b_sequence *sequence, const q4b_weight *const *weights, int count, const void *x,
+                            void *const *y, const uint32_t *ldy, int y_dtype, char *error_message,
+                            size_t error_capacity) {
+    return sequence_add(sequence, weights, count, nullptr, x, y, ldy, y_dtype, error_message, error_capacity);
+}
+
+int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, const q4b_weight *up, const void *x,
+                             void *y, uint32_t ldy, int y_dtype, char *error_message, size_t error_capacity) {
+    if (up == nullptr) {
+        set_error(error_message, error_capacity, "up is NULL");
+        return Q4B_BAD_ARGUMENT;
+    }
+    return sequence_add(sequence, &gate, 1, up, x, &y, &ldy, y_dtype, error_message, error_capacity);
+}
+
+int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t segment, uint32_t peer_rank,
+                                 void *peer_y) {
+    if (sequence == nullptr || sequence->finalized || job >= sequence->jobs.size() || segment >= kMaxSegments ||
+        peer_rank >= sequence->world) {
+        return Q4B_BAD_ARGUMENT;
+    }
+    sequence->jobs[job].y[segment][peer_rank] = peer_y;
+    return Q4B_OK;
+}
+
+int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (sequence == nullptr || sequence->finalized || sequence->jobs.empty() || context->capturing) {
+        set_error(error_message, error_capacity, "nothing to finalize");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const char *stages_text = getenv("Q4B_SEQUENCE_STAGES");
+    uint32_t stages = stages_text != nullptr ? (uint32_t)strtoul(stages_text, nullptr, 0) : 2u;
+    uint32_t ctas = 0, max_local = 2;
+    size_t smem_bytes = 0, scratch_bytes = 0, counter_bytes = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        Q4B_CUDA(sequence_geometry(sequence->m_rows, context->sm_count, stages, max_local, &ctas, &smem_bytes),
+                 "sequence geometry");
+        uint32_t needed_local = 1;
+        scratch_bytes = counter_bytes = 0;
+        for (DecodeJob &job : sequence->jobs) {
+            size_t s = 0, c = 0;
+            plan_decode_job(&job, sequence->m_rows, ctas, &s, &c);
+            if (s > scratch_bytes) scratch_bytes = s;
+            if (c > counter_bytes) counter_bytes = c;
+            if (job.local_blocks > needed_local) needed_local = job.local_blocks;
+        }
+        if (needed_local <= max_local) break;
+        max_local = needed_local;
+    }
+    const size_t job_bytes = sequence->jobs.size() * sizeof(DecodeJob);
+    cudaError_t status = cudaMalloc(&sequence->device_jobs, job_bytes);
+    if (status == cudaSuccess) status = cudaMalloc(&sequence->done, sequence->jobs.size() * sizeof(uint32_t));
+    if (status == cudaSuccess) status = cudaMalloc(&sequence->scratch, scratch_bytes + 256);
+    if (status == cudaSuccess) status = cudaMalloc(&sequence->counters, counter_bytes + 256);
+    if (status == cudaSuccess) status = cudaMemcpy(sequence->device_jobs, sequence->jobs.data(), job_bytes, cudaMemcpyHostToDevice);
+    if (status == cudaSuccess) status = cudaMemset(sequence->done, 0, sequence->jobs.size() * sizeof(uint32_t));
+    if (status == cudaSuccess) status = cudaMemset(sequence->counters, 0, counter_bytes + 256);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "sequence buffers", status);
+    sequence->peer_done[sequence->rank] = sequence->done;
+    SequenceLaunch &launch = sequence->launch;
+    launch.jobs = sequence->device_jobs;
+    launch.job_count = (uint32_t)sequence->jobs.size();
+    launch.m_rows = sequence->m_rows;
+    launch.stages = stages;
+    launch.ctas = ctas;
+    launch.max_local_blocks = max_local;
+    launch.world = sequence->world;
+    launch.rank = sequence->rank;
+    launch.done = sequence->done;
+    launch.scratch = sequence->scratch;
+    launch.counters = sequence->counters;
+    launch.status = context->status_device;
+    launch.smem_bytes = smem_bytes;
+    sequence->finalized = true;
+    return Q4B_OK;
+}
+
+void *q4b_sequence_done_counters(q4b_sequence *sequence) {
+    return sequence != nullptr && sequence->finalized ? sequence->done : nullptr;
+}
+
+int q4b_sequence_set_peer_counters(q4b_sequence *sequence, uint32_t peer_rank, void *peer_counters) {
+    if (sequence == nullptr || !sequence->finalized || peer_rank >= sequence->world || peer_counters == nullptr) {
+        return Q4B_BAD_ARGUMENT;
+    }
+    sequence->peer_done[peer_rank] = static_cast<uint32_t *>(peer_counters);
+    return Q4B_OK;
+}
+
+int q4b_sequence_launch(q4b_context *context, q4b_sequence *sequence, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (sequence == nullptr || !sequence->finalized) {
+        set_error(error_message, error_capacity, "the sequence is not finalized");
+        return Q4B_BAD_ARGUMENT;
+    }
+    for (uint32_t r = 0; r < sequence->world; ++r) {
+        if (sequence->peer_done[r] == nullptr) {
+            set_error(error_message, error_capacity, "rank %u's completion counters are not set", r);
+            return Q4B_BAD_ARGUMENT;
+        }
+        sequence->launch.peer_done[r] = sequence->peer_done[r];
+    }
+    sequence->launch.epoch = ++sequence->epoch;
+    Q4B_CUDA(launch_sequence(sequence->launch, context->stream), "sequence launch");
+    if (!context->capturing) ++context->launches;
+    return Q4B_OK;
+}
+
+void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence) {
+    if (sequence == nullptr) return;
+    if (context != nullptr) {
+        cudaSetDevice(context->device);
+        cudaStreamSynchronize(context->stream);
+    }
+    cudaFree(sequence->device_jobs);
+    cudaFree(sequence->done);
+    cudaFree(sequence->scratch);
+    cudaFree(sequence->counters);
+    delete sequence;
+}
+
+/* ----------------------------------------------------- memory shared by ranks */
+int q4b_ipc_export(q4b_context *context, void *device_pointer, void *handle_64_bytes, char *error_message,
+                   size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (device_pointer == nullptr || handle_64_bytes == nullptr) return Q4B_BAD_ARGUMENT;
+    cudaIpcMemHandle_t handle;
+    Q4B_CUDA(cudaIpcGetMemHandle(&handle, device_pointer), "cudaIpcGetMemHandle");
+    memcpy(handle_64_bytes, &handle, sizeof(handle));
+    return Q4B_OK;
+}
+
+int q4b_ipc_open(q4b_context *context, const void *handle_64_bytes, void **peer_pointer, char *error_message,
+                 size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (handle_64_bytes == nullptr || peer_pointer == nullptr) return Q4B_BAD_ARGUMENT;
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle_64_bytes, sizeof(handle));
+    Q4B_CUDA(cudaIpcOpenMemHandle(peer_pointer, handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    return Q4B_OK;
+}
+
+int q4b_ipc_close(q4b_context *context, void *peer_pointer) {
+    if (context != nullptr) cudaSetDevice(context->device);
+    return cudaIpcCloseMemHandle(peer_pointer) == cudaSuccess ? Q4B_OK : Q4B_DEVICE_FAILURE;
 }
 
 int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity) {

@@ -58,6 +58,39 @@ uint32_t gemv_max_m();
 cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
                                 size_t *counter_bytes);
 
+// ---- q4b_decode.cu: job sequences in one persistent launch ----
+constexpr int kMaxPeers = 8;
+// One projection (a group of matrices sharing x, or a fused gate/up pair) as the
+// sequence kernel reads it from device memory.
+struct DecodeJob {
+    const uint8_t *tiles[kMaxSegments];
+    const uint8_t *up_tiles;
+    void *y[kMaxSegments][kMaxPeers];  // where segment s goes on rank r (own rank included), column offset applied
+    const void *x;                     // [M][K] fp16
+    uint32_t rows[kMaxSegments];
+    uint32_t ldy[kMaxSegments];
+    uint32_t block_begin[kMaxSegments + 1];
+    uint32_t groups, segments, fused, y_dtype;
+    uint32_t total_units, units_per_cta, units_extra, parts, active_ctas, slots, local_blocks, reserved;
+};
+struct SequenceLaunch {
+    const DecodeJob *jobs;     // device
+    uint32_t job_count, m_rows, stages, ctas, max_local_blocks;
+    uint32_t world, rank, epoch;
+    uint32_t *done;            // device, [job_count], zeroed once; counts up across launches
+    uint32_t *peer_done[kMaxPeers];
+    float *scratch;
+    uint32_t *counters;
+    uint32_t *status;
+    size_t smem_bytes;
+};
+// fills the partition fields of `job` for a grid of `ctas`; returns scratch needs
+void plan_decode_job(DecodeJob *job, uint32_t m_rows, uint32_t ctas, size_t *scratch_bytes, size_t *counter_bytes);
+// grid size and shared memory of the sequence kernel on the current device
+cudaError_t sequence_geometry(uint32_t m_rows, int sm_count, uint32_t stages, uint32_t max_local_blocks,
+                              uint32_t *ctas, size_t *smem_bytes);
+cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream);
+
 // ---- q4b_gemm.cu: tcgen05 prefill GEMM ----
 struct TcGemmArgs {
     WeightView w[kMaxSegments];  // matrices that share x (same K), one launch

@@ -90,6 +90,19 @@ def library() -> ctypes.CDLL:
         "q4b_matmul_host": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
                                          ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_sequence_create": (_int, [_vp, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_sequence_add_matmul": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, ctypes.POINTER(_vp),
+                                           ctypes.POINTER(_u32), _int] + err),
+        "q4b_sequence_add_gate_up": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _int] + err),
+        "q4b_sequence_set_peer_output": (_int, [_vp, _u32, _u32, _u32, _vp]),
+        "q4b_sequence_finalize": (_int, [_vp, _vp] + err),
+        "q4b_sequence_done_counters": (_vp, [_vp]),
+        "q4b_sequence_set_peer_counters": (_int, [_vp, _u32, _vp]),
+        "q4b_sequence_launch": (_int, [_vp, _vp] + err),
+        "q4b_sequence_free": (None, [_vp, _vp]),
+        "q4b_ipc_export": (_int, [_vp, _vp, _vp] + err),
+        "q4b_ipc_open": (_int, [_vp, _vp, ctypes.POINTER(_vp)] + err),
+        "q4b_ipc_close": (_int, [_vp, _vp]),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
@@ -201,6 +214,66 @@ class Q4Graph:
     def free(self):
         if self.handle:
             library().q4b_graph_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Q4Sequence:
+    """A chain of projections executed by one persistent launch (q4b_sequence)."""
+
+    def __init__(self, context: "Q4Context", m_rows: int, world: int = 1, rank: int = 0):
+        self.context, self.m_rows, self.world, self.rank = context, m_rows, world, rank
+        handle = _vp()
+        context._check(library().q4b_sequence_create(context.handle, m_rows, world, rank, ctypes.byref(handle),
+                                                     context._err, _ERR))
+        self.handle = handle.value
+        self.jobs = 0
+
+    def add_matmul(self, weights, x_ptr: int, y_ptrs, ldys=None, y_dtype: int = F16) -> int:
+        count = len(weights)
+        handles = (_vp * count)(*[w.handle for w in weights])
+        outputs = (_vp * count)(*y_ptrs)
+        strides = (_u32 * count)(*(ldys if ldys is not None else [w.rows for w in weights]))
+        self.context._check(library().q4b_sequence_add_matmul(self.handle, handles, count, x_ptr, outputs, strides,
+                                                              y_dtype, self.context._err, _ERR))
+        self.jobs += 1
+        return self.jobs - 1
+
+    def add_gate_up(self, gate, up, x_ptr: int, y_ptr: int, ldy=None, y_dtype: int = F16) -> int:
+        self.context._check(library().q4b_sequence_add_gate_up(self.handle, gate.handle, up.handle, x_ptr, y_ptr,
+                                                               gate.rows if ldy is None else ldy, y_dtype,
+                                                               self.context._err, _ERR))
+        self.jobs += 1
+        return self.jobs - 1
+
+    def set_peer_output(self, job: int, segment: int, peer_rank: int, peer_ptr: int):
+        if library().q4b_sequence_set_peer_output(self.handle, job, segment, peer_rank, peer_ptr) != 0:
+            raise Q4Error(1, "invalid peer output")
+
+    def finalize(self):
+        self.context._check(library().q4b_sequence_finalize(self.context.handle, self.handle,
+                                                            self.context._err, _ERR))
+
+    @property
+    def done_counters(self) -> int:
+        return library().q4b_sequence_done_counters(self.handle)
+
+    def set_peer_counters(self, peer_rank: int, pointer: int):
+        if library().q4b_sequence_set_peer_counters(self.handle, peer_rank, pointer) != 0:
+            raise Q4Error(1, "invalid peer counters")
+
+    def launch(self):
+        self.context._check(library().q4b_sequence_launch(self.context.handle, self.handle,
+                                                          self.context._err, _ERR))
+
+    def free(self):
+        if self.handle:
+            library().q4b_sequence_free(self.context.handle, self.handle)
             self.handle = None
 
     def __del__(self):
@@ -347,6 +420,21 @@ class Q4Context:
                                                     _np_dtype_code(x), m_rows, y.ctypes.data, y_dtype,
                                                     ctypes.byref(ms), self._err, _ERR))
         return y, ms.value
+
+    # -- memory shared with peer processes -----------------------------------
+    def ipc_export(self, device_ptr: int) -> bytes:
+        handle = ctypes.create_string_buffer(64)
+        self._check(library().q4b_ipc_export(self.handle, device_ptr, handle, self._err, _ERR))
+        return handle.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        pointer = _vp()
+        buffer = ctypes.create_string_buffer(handle, 64)
+        self._check(library().q4b_ipc_open(self.handle, buffer, ctypes.byref(pointer), self._err, _ERR))
+        return pointer.value
+
+    def ipc_close(self, pointer: int):
+        library().q4b_ipc_close(self.handle, pointer)
 
     def probe_read(self, mode: int = 0, nbytes: int = 2 << 30, ctas_per_sm: int = 2, stages: int = 4,
                    stage_bytes: int = 18432, iterations: int = 5) -> float:

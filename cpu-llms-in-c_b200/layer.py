@@ -29,12 +29,6 @@ def slice_of(n: int, rank: int, world: int) -> tuple[int, int]:
     return begin, end - begin
 
 
-def x_stream(k: int) -> int:
-    """Generator stream of the activation with K columns (0 for any K: streams
-    are per (seed, stream) and x of different K never share a launch)."""
-    return 0
-
-
 class Q4Layer:
     """Weights of one layer on one rank plus the launch sequence."""
 
@@ -86,6 +80,22 @@ class Q4Layer:
                 ctx.gate_up_silu(gate, up, x, F16, m_rows, y_ptrs[first.name], F16, stride(first))
             else:
                 ctx.matmul(self.weights[first.name][0], x, F16, m_rows, y_ptrs[first.name], F16, stride(first))
+
+    def add_to(self, sequence, x_ptrs: dict[int, int], y_ptrs: dict[str, int], ldy: dict[str, int] | None = None):
+        """Append the layer's projections to a decode sequence, in launch order.
+        Returns [(job index, [projection per segment])]."""
+        jobs = []
+        for kind, members in self.launch_plan():
+            first = members[0]
+            stride = lambda p: (ldy[p.name] if ldy else self.slices[p.name][1])
+            if kind == "fused":
+                gate, up = self.weights[first.name]
+                job = sequence.add_gate_up(gate, up, x_ptrs[first.k], y_ptrs[first.name], stride(first))
+            else:
+                job = sequence.add_matmul([self.weights[p.name][0] for p in members], x_ptrs[first.k],
+                                          [y_ptrs[p.name] for p in members], [stride(p) for p in members])
+            jobs.append((job, members))
+        return jobs
 
     def launches_per_forward(self) -> int:
         return len(self.launch_plan())

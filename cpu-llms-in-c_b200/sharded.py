@@ -19,18 +19,22 @@ import ctypes
 
 import numpy as np
 
-from .host import F16, Q4Context, library
+from .host import F16, Q4Context, Q4Sequence, library
 from .layer import Q4Layer, slice_of
 
 
 class ShardedLayerStack:
     def __init__(self, ctx: Q4Context, layer_set, n_layers: int, m_rows: int, rank: int = 0, world: int = 1,
-                 dist=None, gather: str = "nccl"):
+                 dist=None, gather: str = "push", mode: str = "graph"):
         self.ctx, self.layer_set, self.n_layers, self.m = ctx, tuple(layer_set), n_layers, m_rows
         self.rank, self.world, self.dist, self.gather = rank, world, dist, gather
         self.layers = [Q4Layer(ctx, layer_set, seed, rank, world) for seed in range(n_layers)]
         self.ks = sorted({p.k for p in self.layer_set})
         self.graph = None
+        self.sequence = None
+        # "sequence": the whole pass is one persistent launch (M <= 16); "graph": one launch per projection
+        # group, replayed from a recorded graph
+        self.mode = mode if m_rows <= 16 else "graph"
 
         # activations: per layer, one [M, K] fp16 block per distinct K
         self.x_offsets, offset = {}, 0
@@ -119,6 +123,17 @@ class ShardedLayerStack:
         if self.world > 1:
             self._queue_sharded_nccl()
             return
+        if self.mode == "sequence":
+            if self.sequence is None:
+                self.sequence = Q4Sequence(self.ctx, self.m)
+                for index, layer in enumerate(self.layers):
+                    base = self.y_base + index * self.y_layer_bytes
+                    layer.add_to(self.sequence, self._x_ptrs(index),
+                                 {p.name: base + self.y_offsets[p.name] for p in self.layer_set},
+                                 {p.name: p.n for p in self.layer_set})
+                self.sequence.finalize()
+            self.sequence.launch()
+            return
         if self.graph is None:
             self._queue_single_gpu()  # plain launches once (also sets kernel attributes)
             self.ctx.sync()
@@ -170,5 +185,7 @@ class ShardedLayerStack:
             layer.free()
         if self.graph is not None:
             self.graph.free()
+        if self.sequence is not None:
+            self.sequence.free()
         library().q4b_free_host(self.ctx.handle, self.x_host)
         library().q4b_free_host(self.ctx.handle, self.y_host)

@@ -30,6 +30,7 @@ extern "C" {
 typedef struct q4b_context q4b_context;
 typedef struct q4b_weight q4b_weight;
 typedef struct q4b_graph q4b_graph;
+typedef struct q4b_sequence q4b_sequence;
 
 enum { Q4B_OK = 0, Q4B_BAD_ARGUMENT = 1, Q4B_DEVICE_FAILURE = 2, Q4B_LOAD_FAILURE = 3 };
 enum { Q4B_F16 = 0, Q4B_F32 = 1, Q4B_BF16 = 2, Q4B_NONE = -1 };
@@ -175,6 +176,55 @@ int q4b_gate_up_silu_host(q4b_context *context, const q4b_weight *gate, const q4
  * last q4b_timer_start. */
 int q4b_timer_start(q4b_context *context, char *error_message, size_t error_capacity);
 int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_t error_capacity);
+
+/* ---- decode sequences: one token's chain of projections in ONE launch.
+ * The reference encodes a whole token into one command buffer
+ * (qwen38_m3_model_forward_submit, qwen38_m3_decode.m:1614-1690: per layer
+ * encode_delta / encode_attention / encode_mlp back to back).  A sequence is the
+ * same idea for the Q4 matmuls: jobs are added in execution order, each either a
+ * group of 1..4 matrices that share x (q4b_matmul_group) or a fused gate/up pair
+ * (q4b_gate_up_silu); job j may read what job j-1 wrote.  All pointers are
+ * DEVICE pointers, x is fp16, 1 <= m_rows <= 16.  q4b_sequence_finalize plans
+ * the work split and allocates the sequence's own scratch (synchronous, never
+ * while recording); q4b_sequence_launch queues one cooperative kernel on the
+ * context's stream and may be recorded into a graph.
+ *
+ * Column-parallel ranks (one process per GPU): create with (world, rank), give
+ * every job the slice this rank owns, and with q4b_sequence_set_peer_output name
+ * where that slice goes in each peer's copy of y (a pointer obtained with
+ * q4b_ipc_open, column offset applied).  After finalize exchange
+ * q4b_sequence_done_counters between the ranks (q4b_ipc_export / q4b_ipc_open)
+ * and install them with q4b_sequence_set_peer_counters.  The kernel then stores
+ * every output on every rank and a job starts only when all ranks have published
+ * the previous one: the all-gather is part of the launch.  All ranks must launch
+ * the same sequence the same number of times. */
+int q4b_sequence_create(q4b_context *context, uint32_t m_rows, uint32_t world, uint32_t rank,
+                        q4b_sequence **sequence, char *error_message, size_t error_capacity);
+int q4b_sequence_add_matmul(q4b_sequence *sequence, const q4b_weight *const *weights, int count,
+                            const void *x, void *const *y, const uint32_t *ldy, int y_dtype,
+                            char *error_message, size_t error_capacity);
+int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, const q4b_weight *up,
+                             const void *x, void *y, uint32_t ldy, int y_dtype,
+                             char *error_message, size_t error_capacity);
+int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t segment,
+                                 uint32_t peer_rank, void *peer_y);
+int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence,
+                          char *error_message, size_t error_capacity);
+void *q4b_sequence_done_counters(q4b_sequence *sequence);
+int q4b_sequence_set_peer_counters(q4b_sequence *sequence, uint32_t peer_rank, void *peer_counters);
+int q4b_sequence_launch(q4b_context *context, q4b_sequence *sequence,
+                        char *error_message, size_t error_capacity);
+void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence);
+
+/* ---- device memory shared between the ranks of one node (thin wrappers of the
+ * CUDA IPC calls; the reference is single-device and has no counterpart).  A
+ * 64-byte handle made by the owner is opened by a peer process, which may then
+ * store into that memory over NVLink. */
+int q4b_ipc_export(q4b_context *context, void *device_pointer, void *handle_64_bytes,
+                   char *error_message, size_t error_capacity);
+int q4b_ipc_open(q4b_context *context, const void *handle_64_bytes, void **peer_pointer,
+                 char *error_message, size_t error_capacity);
+int q4b_ipc_close(q4b_context *context, void *peer_pointer);
 
 /* ---- read-bandwidth probe: the role of the reference's device-memory probe
  * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):

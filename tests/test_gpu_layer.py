@@ -27,16 +27,17 @@ def oracle_layer(orc, layer_set, seed, m):
     return out
 
 
-@pytest.mark.parametrize("m", [1, 4])
-def test_small_layer_stack_matches_oracle(q4b, orc, m):
+@pytest.mark.parametrize("mode", ["sequence", "graph"])
+@pytest.mark.parametrize("m", [1, 4, 9])
+def test_small_layer_stack_matches_oracle(q4b, orc, m, mode):
     sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
     with q4b.Q4Context(0) as ctx:
-        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_SMALL, 3, m)
+        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_SMALL, 3, m, mode=mode)
         before = ctx.launches
-        stack.step()   # plain launches + recording
-        stack.step()   # replay
+        stack.step()   # graph mode: plain launches + recording
+        stack.step()   # graph mode: replay; sequence mode: second launch of the same sequence
         ctx.sync()
-        assert ctx.launches - before >= 3 * 4 * 2
+        assert ctx.launches - before >= (2 if mode == "sequence" else 3 * 4 * 2)
         for index in (0, 2):
             got = stack.outputs(index)
             want = oracle_layer(orc, q4b.LAYER_SMALL, index, m)
@@ -50,10 +51,11 @@ def test_small_layer_stack_matches_oracle(q4b, orc, m):
         stack.free()
 
 
-def test_27b_layer_matches_oracle_at_decode(q4b, orc):
+@pytest.mark.parametrize("mode", ["sequence", "graph"])
+def test_27b_layer_matches_oracle_at_decode(q4b, orc, mode):
     sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
     with q4b.Q4Context(0) as ctx:
-        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, 1, 1)
+        stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, 1, 1, mode=mode)
         stack.step()
         got = stack.outputs(0)
         want = oracle_layer(orc, q4b.LAYER_27B, 0, 1)
