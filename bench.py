@@ -183,7 +183,8 @@ def workload_config(args, world):
     return {"workload": f"27B-shape Q4 layer set (q,k,v,o,gate+up SiLU,down) x {LAYERS} layers, M={args.m}, "
                         f"seed=layer index (BASELINE configs[2]/[4])",
             "m_rows": args.m, "layers": LAYERS, "group": 64,
-            "parallelism": "single GPU" if world == 1 else f"column-parallel N/{world} + all-gather",
+            "parallelism": ("single GPU" if world == 1 else
+                            f"column-parallel N/{world} + all-gather ({args.gather})"),
             "l2": "inputs_exceed_l2 (12.27 GB of distinct weights per step)"}
 
 
@@ -209,7 +210,8 @@ def run_ours(args):
     from importlib import import_module
     sharded = import_module("cpu-llms-in-c_b200.sharded")
     ctx = q4b.Q4Context(local_rank)
-    model = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, LAYERS, args.m, rank, world, dist)
+    model = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, LAYERS, args.m, rank, world, dist, gather=args.gather,
+                                      mode=args.mode)
     layer_bytes, layer_flops = layer_work(q4b, args.m)
     step_bytes = layer_bytes * LAYERS
 
@@ -344,6 +346,10 @@ def main():
     parser.add_argument("--m", type=int, default=1, help="activation rows (1 decode, 4 verify)")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM section")
+    parser.add_argument("--gather", default="push", choices=["push", "nccl"],
+                        help="N > 1: slices stored into every rank's y by the kernel, or NCCL all-gather per projection")
+    parser.add_argument("--mode", default="graph", choices=["graph", "sequence"],
+                        help="N = 1: one launch per projection group replayed from a graph, or one persistent launch")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

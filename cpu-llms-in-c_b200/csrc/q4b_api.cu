@@ -925,6 +925,14 @@ int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t 
     return Q4B_OK;
 }
 
+int q4b_sequence_set_job_blocks(q4b_sequence *sequence, uint32_t job, uint32_t blocks_on_all_ranks) {
+    if (sequence == nullptr || sequence->finalized || job >= sequence->jobs.size() || blocks_on_all_ranks == 0) {
+        return Q4B_BAD_ARGUMENT;
+    }
+    sequence->jobs[job].expected_blocks = blocks_on_all_ranks;
+    return Q4B_OK;
+}
+
 int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
@@ -947,6 +955,14 @@ int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence, char *er
             if (s > scratch_bytes) scratch_bytes = s;
             if (c > counter_bytes) counter_bytes = c;
             if (job.local_blocks > needed_local) needed_local = job.local_blocks;
+            if (attempt == 0) {
+                const uint32_t own = job.block_begin[kMaxSegments];
+                if (job.expected_blocks == 0) job.expected_blocks = own * sequence->world;
+                if (job.expected_blocks < own) {
+                    set_error(error_message, error_capacity, "a job's block count over all ranks is below this rank's own");
+                    return Q4B_BAD_ARGUMENT;
+                }
+            }
         }
         if (needed_local <= max_local) break;
         max_local = needed_local;

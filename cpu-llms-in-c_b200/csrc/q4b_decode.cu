@@ -242,11 +242,15 @@ decode_sequence_kernel(const SeqParams p) {
         const long long t_dep = SQ_CLOCK();
         if (j > 0 && range > 0 && threadIdx.x == 0) {
             // every row block of the previous job, on every rank, announces itself once
-            const uint32_t expected = p.jobs[j - 1].block_begin[kMaxSegments] * p.world * p.epoch;
+            const uint32_t expected = p.jobs[j - 1].expected_blocks * p.epoch;
             const long long start = clock64();
             uint32_t seen = 0;
             for (;;) {
-                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.done + (j - 1)) : "memory");
+                if (p.world > 1) {  // peers add to the counter over NVLink
+                    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.done + (j - 1)) : "memory");
+                } else {
+                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.done + (j - 1)) : "memory");
+                }
                 if ((int32_t)(seen - expected) >= 0) break;
                 if (clock64() - start > kSeqWaitLimit) { flags[0] = 0xdeadu; break; }
                 __nanosleep(32);

@@ -71,7 +71,8 @@ struct DecodeJob {
     uint32_t ldy[kMaxSegments];
     uint32_t block_begin[kMaxSegments + 1];
     uint32_t groups, segments, fused, y_dtype;
-    uint32_t total_units, units_per_cta, units_extra, parts, active_ctas, slots, local_blocks, reserved;
+    uint32_t total_units, units_per_cta, units_extra, parts, active_ctas, slots, local_blocks;
+    uint32_t expected_blocks;  // row blocks all ranks publish for this job per launch (0: blocks * world)
 };
 struct SequenceLaunch {
     const DecodeJob *jobs;     // device

@@ -95,6 +95,7 @@ def library() -> ctypes.CDLL:
                                            ctypes.POINTER(_u32), _int] + err),
         "q4b_sequence_add_gate_up": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _int] + err),
         "q4b_sequence_set_peer_output": (_int, [_vp, _u32, _u32, _u32, _vp]),
+        "q4b_sequence_set_job_blocks": (_int, [_vp, _u32, _u32]),
         "q4b_sequence_finalize": (_int, [_vp, _vp] + err),
         "q4b_sequence_done_counters": (_vp, [_vp]),
         "q4b_sequence_set_peer_counters": (_int, [_vp, _u32, _vp]),
@@ -254,6 +255,10 @@ class Q4Sequence:
     def set_peer_output(self, job: int, segment: int, peer_rank: int, peer_ptr: int):
         if library().q4b_sequence_set_peer_output(self.handle, job, segment, peer_rank, peer_ptr) != 0:
             raise Q4Error(1, "invalid peer output")
+
+    def set_job_blocks(self, job: int, blocks_on_all_ranks: int):
+        if library().q4b_sequence_set_job_blocks(self.handle, job, blocks_on_all_ranks) != 0:
+            raise Q4Error(1, "invalid job block count")
 
     def finalize(self):
         self.context._check(library().q4b_sequence_finalize(self.context.handle, self.handle,

@@ -5,13 +5,14 @@ each rank owns its slice's tile stream, computes Y[:, n0:n1] from the full x and
 the slices are gathered so that every rank ends with the whole [M, N].
 
 Two gather paths:
+  * "push"  : (M <= 16) the whole pass is one decode sequence (q4b_decode.cu);
+              every epilogue stores its slice straight into every rank's copy of
+              y over NVLink and a job starts only when all ranks have published
+              the previous one -- no collective call per projection;
   * "nccl"  : torch.distributed all_gather_into_tensor per gather point, queued
-              on the context's stream (the baseline and the correctness check);
-  * "push"  : the kernels' epilogues store their slice straight into every
-              peer's output buffer over NVLink (see q4b_comm.cu), one bounded
-              arrival wait per layer.
-With world == 1 neither runs and the whole step is replayed from one recorded
-launch sequence.  torch is imported only when world > 1 (process group, NCCL).
+              on the context's stream (the baseline and the cross-check).
+With world == 1 neither runs.  torch is imported only when world > 1 (process
+group for the handle exchange, NCCL for the baseline).
 """
 from __future__ import annotations
 
@@ -57,9 +58,12 @@ class ShardedLayerStack:
         self.h2d_bytes_per_step = self.x_layer_bytes * n_layers
         self.d2h_bytes_per_step = self.y_layer_bytes * n_layers
         self._torch = None
-        if world > 1:
+        if world > 1 and gather == "push" and m_rows <= 16:
+            self._setup_push()
+        elif world > 1:
             import torch
             self._torch = torch
+            self.gather = "nccl"
             self.stream = torch.cuda.ExternalStream(ctx.stream)
             self.y_torch = torch.zeros(self.y_layer_bytes * n_layers // 2, dtype=torch.float16, device="cuda")
             self.y_base = self.y_torch.data_ptr()
@@ -81,6 +85,41 @@ class ShardedLayerStack:
         ctx._check(lib.q4b_copy_to_host(ctx.handle, self.x_host, self.x_all.ptr, self.x_layer_bytes * n_layers,
                                         ctx._err, 512))
         ctx.sync()
+
+    def _setup_push(self):
+        """Full y on every rank, shared through IPC handles; one sequence with peer outputs."""
+        ctx, dist = self.ctx, self.dist
+        self.y_all = ctx.alloc(self.y_layer_bytes * self.n_layers)
+        self.y_base = self.y_all.ptr
+        handles = [None] * self.world
+        dist.all_gather_object(handles, ctx.ipc_export(self.y_all.ptr))
+        self.peer_y = [self.y_base if r == self.rank else ctx.ipc_open(handles[r]) for r in range(self.world)]
+        sequence = Q4Sequence(ctx, self.m, self.world, self.rank)
+        for index, layer in enumerate(self.layers):
+            offsets = {p.name: index * self.y_layer_bytes + self.y_offsets[p.name] + layer.slices[p.name][0] * 2
+                       for p in self.layer_set}
+            jobs = layer.add_to(sequence, self._x_ptrs(index), {n: self.y_base + o for n, o in offsets.items()},
+                                {p.name: p.n for p in self.layer_set})
+            for job, members in jobs:
+                sequence.set_job_blocks(job, sum(-(-slice_of(p.n, r, self.world)[1] // 64)
+                                                 for p in members for r in range(self.world)))
+                for segment, p in enumerate(members):
+                    for r in range(self.world):
+                        if r != self.rank:
+                            sequence.set_peer_output(job, segment, r, self.peer_y[r] + offsets[p.name])
+        sequence.finalize()
+        counters = [None] * self.world
+        dist.all_gather_object(counters, ctx.ipc_export(sequence.done_counters))
+        self.peer_counters = []
+        for r in range(self.world):
+            if r != self.rank:
+                pointer = ctx.ipc_open(counters[r])
+                self.peer_counters.append(pointer)
+                sequence.set_peer_counters(r, pointer)
+        self.sequence = sequence
+        self.mode = "sequence"
+        ctx.sync()
+        dist.barrier()  # every rank's counters are zero and mapped before anyone launches
 
     def _pinned(self, nbytes: int) -> int:
         pointer = ctypes.c_void_p()
@@ -120,7 +159,7 @@ class ShardedLayerStack:
 
     def step(self):
         """One pass over all layers, queued on the context stream."""
-        if self.world > 1:
+        if self.world > 1 and self.gather == "nccl":
             self._queue_sharded_nccl()
             return
         if self.mode == "sequence":
@@ -159,7 +198,8 @@ class ShardedLayerStack:
         for index, layer in enumerate(self.layers):
             gate, up = layer.weights[fused.name]
             out = (self.local_base + index * self.local_layer_bytes + self.local_offsets[fused.name]
-                   if self.world > 1 else self.y_base + index * self.y_layer_bytes + self.y_offsets[fused.name])
+                   if self.world > 1 and self.gather == "nccl"
+                   else self.y_base + index * self.y_layer_bytes + self.y_offsets[fused.name])
             self.ctx.gate_up_silu(gate, up, self._x_ptrs(index)[fused.k], F16, self.m, out, F16)
 
     def outputs(self, index: int) -> dict[str, np.ndarray]:
@@ -181,6 +221,11 @@ class ShardedLayerStack:
         return None
 
     def free(self):
+        if self.world > 1 and self.gather == "push":
+            self.ctx.sync()
+            self.dist.barrier()  # nobody stores into a peer that is about to unmap
+            for pointer in [p for r, p in enumerate(self.peer_y) if r != self.rank] + self.peer_counters:
+                self.ctx.ipc_close(pointer)
         for layer in self.layers:
             layer.free()
         if self.graph is not None:

@@ -208,6 +208,11 @@ int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, con
                              char *error_message, size_t error_capacity);
 int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t segment,
                                  uint32_t peer_rank, void *peer_y);
+/* Ranks whose slices differ in size: the number of 64-row blocks (summed over the
+ * job's matrices, each rounded up) that ALL ranks together compute for `job`;
+ * the next job starts when that many have been published.  Default: this rank's
+ * own count times world (equal slices). */
+int q4b_sequence_set_job_blocks(q4b_sequence *sequence, uint32_t job, uint32_t blocks_on_all_ranks);
 int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence,
                           char *error_message, size_t error_capacity);
 void *q4b_sequence_done_counters(q4b_sequence *sequence);

@@ -1,0 +1,56 @@
+"""One rank of the column-parallel parity check (launched by torch.distributed.run).
+
+Every rank holds its N-slice of every projection, runs the small layer stack
+twice and must end with the WHOLE [M, N] of every projection equal to the
+oracle's, both through the fused push gather and through the NCCL baseline."""
+import importlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    from q4_cases import assert_close
+    from test_gpu_layer import oracle_layer
+    from oracle import q4_oracle as orc
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    q4b = importlib.import_module("cpu-llms-in-c_b200")
+    sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
+    layer_set = q4b.LAYER_SMALL if len(sys.argv) < 2 or sys.argv[1] == "small" else q4b.LAYER_27B
+    layers = 3 if layer_set is q4b.LAYER_SMALL else 1
+    ctx = q4b.Q4Context(local)
+    for gather in ("push", "nccl"):
+        for m in (1, 4):
+            stack = sharded.ShardedLayerStack(ctx, layer_set, layers, m, rank, world, dist, gather=gather)
+            assert stack.gather == gather
+            for _ in range(3):
+                stack.step()
+            ctx.sync()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for index in range(layers):
+                got = stack.outputs(index)
+                want = oracle_layer(orc, layer_set, index, m)
+                for name in want:
+                    assert_close(got[name], want[name], f"rank {rank} {gather} layer {index} {name} M={m}")
+            dist.barrier()
+            stack.free()
+    ctx.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("multi-gpu parity ok", world, "ranks")
+
+
+if __name__ == "__main__":
+    main()
