@@ -3,6 +3,7 @@
     python cpu-llms-in-c_b200/profile_case.py gemv gate_up 1     # decode kernel, fused gate/up, M = 1
     python cpu-llms-in-c_b200/profile_case.py gemv down 4        # decode kernel, down projection, M = 4
     python cpu-llms-in-c_b200/profile_case.py gemm gate_up 2048  # tcgen05 kernel, fused gate/up, M = 2048
+    python cpu-llms-in-c_b200/profile_case.py sequence 2 1       # decode sequence: 2 whole 27B layers, M = 1
 
 The 27B shapes over a few sets of distinct weights (about 0.4 GB on the device,
 more than L2, so DRAM counters mean something), two passes, a handful of
@@ -18,9 +19,24 @@ SHAPES = {"q": (5120, 6144, False), "o": (6144, 5120, False), "gate_up": (5120, 
           "down": (17408, 5120, False)}
 
 
+def sequence(q4b, layers, m):
+    """The whole layer set as one persistent launch per pass, three passes."""
+    sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
+    ctx = q4b.Q4Context(0)
+    stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, layers, m, mode="sequence")
+    for _ in range(3):
+        stack.step()
+    ctx.sync()
+    print(f"sequence of {layers} layers, M={m}: 3 launches")
+    stack.free()
+    ctx.close()
+
+
 def main(argv):
     q4b = importlib.import_module("cpu-llms-in-c_b200")
     kind = argv[1] if len(argv) > 1 else "gemv"
+    if kind == "sequence":
+        return sequence(q4b, int(argv[2]) if len(argv) > 2 else 2, int(argv[3]) if len(argv) > 3 else 1)
     which = argv[2] if len(argv) > 2 else "gate_up"
     m = int(argv[3]) if len(argv) > 3 else (1 if kind == "gemv" else 2048)
     if kind == "gemv" and m > 16 or kind == "gemm" and m <= 16:
