@@ -231,6 +231,48 @@ int q4b_ipc_open(q4b_context *context, const void *handle_64_bytes, void **peer_
                  char *error_message, size_t error_capacity);
 int q4b_ipc_close(q4b_context *context, void *peer_pointer);
 
+/* ---- layer-image files: replaces map_file, validate_delta_header,
+ * validate_attention_header, load_delta_layer and load_attention_layer
+ * (qwen38_m3_decode.m:374-625) for the Q4 matrices of a layer.  File layouts:
+ * qwen38_m3_image.h:26-94 (magic "Q38M3Q4\0", version 3) and
+ * qwen38_m3_attention_image.h:21-72 (magic "Q38M3ATT", version 1).
+ *
+ * q4b_image_open maps the file read-only and validates it as the reference does:
+ * at least one page, magic, version, one-page header, group size 64, the layer
+ * index asked for (DeltaNet images never at layers 3 mod 4, attention images only
+ * there or at the MTP layer 64), every segment page-aligned (mapped_buffer,
+ * :398-407), the file ending with the output metadata; and, beyond the
+ * reference, every segment inside the file and large enough for its matrix.
+ * check_27b_shapes adds the fixed shapes the reference runtime insists on
+ * (:412-421, :433-443).  allowed_sha256 (may be NULL) is the list of source
+ * digests the caller accepts, the role of pinned_sha.  Failures return
+ * Q4B_LOAD_FAILURE with a message.  No GPU is needed to open an image. */
+typedef struct q4b_image q4b_image;
+enum { Q4B_IMAGE_DELTA = 0, Q4B_IMAGE_ATTENTION = 1 };
+enum { Q4B_MATRIX_GATE = 0, Q4B_MATRIX_UP = 1, Q4B_MATRIX_DOWN = 2, Q4B_MATRIX_INPUT = 3, Q4B_MATRIX_OUTPUT = 4 };
+typedef struct {
+    uint32_t kind, version, layer_index, hidden_size, intermediate_size, group_size;
+    uint32_t rows[5], groups[5];          /* by Q4B_MATRIX_*: output rows and K/64 */
+    uint32_t constants_f32_count;
+    uint32_t reference_counts[3];         /* how many of the eight values below the packer filled */
+    float gate_up_reference_first_8[8];   /* silu(gate x) * up x, rows 0..7 (qwen38_m3_pack.c:448-505) */
+    float mlp_reference_first_8[8];       /* whole MLP + residual, rows 0..7 */
+    float layer_reference_first_8[8];
+    char source_sha256[65], mlp_source_sha256[65];
+} q4b_image_info;
+int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_27b_shapes,
+                   const char *const *allowed_sha256, int allowed_count, q4b_image **image,
+                   char *error_message, size_t error_capacity);
+int q4b_image_describe(const q4b_image *image, q4b_image_info *info);
+/* the fp32 constants block (norm weights and the like), a host pointer into the mapping */
+const float *q4b_image_constants(const q4b_image *image, uint32_t *count);
+/* host pointers to the two segments of one matrix, as the packer wrote them */
+int q4b_image_segments(const q4b_image *image, int matrix, const void **quants, const void **metadata);
+/* rows [row_begin, row_begin+row_count) of one matrix, repacked and uploaded (q4b_weight_upload) */
+int q4b_image_weight(q4b_context *context, const q4b_image *image, int matrix, uint32_t row_begin,
+                     uint32_t row_count, q4b_weight **weight, char *error_message, size_t error_capacity);
+void q4b_image_close(q4b_image *image);
+
 /* ---- read-bandwidth probe: the role of the reference's device-memory probe
  * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):
  * reads `bytes` of device memory `iterations` times and reports GB/s from CUDA

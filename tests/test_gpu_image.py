@@ -1,0 +1,87 @@
+"""Layer images on the GPU: every matrix of an image arrives in HBM bit-exact
+(whole and as the row slice a rank owns), and the image checks itself the way the
+reference's packer intends: fused gate/up on the packer's sin/cos activation
+reproduces the eight reference rows stored in the header
+(qwen38_m3_pack.c:187-239, header field source_reference_first_8)."""
+import importlib
+
+import numpy as np
+import pytest
+
+from q4_cases import assert_close, bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(q4b):
+    context = q4b.Q4Context(0)
+    yield context
+    context.close()
+
+
+@pytest.fixture(scope="module")
+def image(q4b):
+    return importlib.import_module("cpu-llms-in-c_b200.image")
+
+
+def build(orc, image, path, kind, layer, hidden, intermediate, input_rows, output_groups, seed):
+    shapes = [(intermediate, hidden // 64), (intermediate, hidden // 64), (hidden, intermediate // 64),
+              (input_rows, hidden // 64), (hidden, output_groups)]
+    matrices = {m: orc.synth_weight(seed, m, rows, groups) for m, (rows, groups) in enumerate(shapes)}
+    x = orc.activation_sincos(hidden).reshape(1, hidden)
+    (gq, gm), (uq, um) = matrices[image.GATE], matrices[image.UP]
+    reference, _ = orc.gate_up_silu(gq[:8], gm[:8], uq[:8], um[:8], hidden // 64, x, want64=False)
+    image.write_layer_image(path, kind, layer, hidden, intermediate, matrices,
+                            np.linspace(0, 1, 64, dtype=np.float32), gate_up_reference=reference[0])
+    return matrices, x
+
+
+@pytest.mark.parametrize("kind_name,layer", [("DELTA", 2), ("ATTENTION", 3)])
+def test_image_matrices_arrive_bit_exact(q4b, orc, ctx, image, tmp_path, kind_name, layer):
+    kind = getattr(image, kind_name)
+    path = str(tmp_path / "layer.img")
+    matrices, _ = build(orc, image, path, kind, layer, 1024, 3072, 2112, 32, seed=layer)
+    opened = image.Q4Image(path, kind, layer)
+    for m, (quants, meta) in matrices.items():
+        rows, groups = opened.shape(m)
+        weight = opened.weight(ctx, m)
+        codes, w32, w16 = weight.unpack()
+        assert (codes == orc.unpack_codes(quants, rows, groups)).all()
+        assert bits_equal(w32, orc.dequant_w32(quants, meta, rows, groups))
+        assert bits_equal(w16, orc.dequant_w16(quants, meta, rows, groups))
+        weight.free()
+        # the slice of the second of three ranks
+        begin, count = (rows // 48) * 16, (rows // 48) * 16
+        part = opened.weight(ctx, m, begin, count)
+        _, w32, _ = part.unpack(codes=False, w16=False)
+        assert bits_equal(w32, orc.dequant_w32(quants, meta, rows, groups)[begin:begin + count])
+        part.free()
+    opened.close()
+
+
+def test_image_reproduces_its_embedded_reference(q4b, orc, ctx, image, tmp_path):
+    path = str(tmp_path / "layer.img")
+    hidden, intermediate = 5120, 1024  # the packer's hidden size; a short intermediate keeps the file small
+    matrices, x = build(orc, image, path, image.DELTA, 0, hidden, intermediate, 256, 4, seed=9)
+    opened = image.Q4Image(path, image.DELTA, 0)
+    assert list(opened.info.reference_counts)[:1] == [8]
+    gate, up = opened.weight(ctx, image.GATE), opened.weight(ctx, image.UP)
+    dx = ctx.to_device(x)
+    dy = ctx.alloc(intermediate * 4)
+    ctx.gate_up_silu(gate, up, dx.ptr, q4b.F16, 1, dy.ptr, q4b.F32)
+    got = dy.download(np.float32, (1, intermediate))
+    stored = np.array(list(opened.info.gate_up_reference_first_8), dtype=np.float32).reshape(1, 8)
+    assert_close(got[:, :8], stored, "first eight rows against the header's reference")
+    # and the down projection of the same image against the oracle
+    (dq, dm) = matrices[image.DOWN]
+    down = opened.weight(ctx, image.DOWN)
+    h = orc.synth_x(9, 0, 4, intermediate)
+    dh = ctx.to_device(h)
+    dz = ctx.alloc(4 * hidden * 2)
+    ctx.matmul(down, dh.ptr, q4b.F16, 4, dz.ptr, q4b.F16)
+    _, want = orc.matmul(dq, dm, intermediate // 64, h, want32=False)
+    assert_close(dz.download(np.float16, (4, hidden)), want, "down projection from the image")
+    for weight in (gate, up, down):
+        weight.free()
+    opened.close()

@@ -1,0 +1,117 @@
+"""Layer-image files on CPU: the restated header layouts against the offsets the
+reference's own headers give, and the loader's validation rules
+(qwen38_m3_decode.m:374-446) on synthetic images -- good ones and broken ones."""
+import importlib
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "image_header_offsets.json")
+
+
+@pytest.fixture(scope="module")
+def image(q4b):
+    return importlib.import_module("cpu-llms-in-c_b200.image")
+
+
+def small_matrices(orc, hidden=256, intermediate=512, input_rows=320, output_groups=6, seed=11):
+    """gate/up [intermediate, hidden], down [hidden, intermediate], input [input_rows, hidden],
+    output [hidden, 64 * output_groups]"""
+    shapes = [(intermediate, hidden // 64), (intermediate, hidden // 64), (hidden, intermediate // 64),
+              (input_rows, hidden // 64), (hidden, output_groups)]
+    return {m: orc.synth_weight(seed, m, rows, groups) for m, (rows, groups) in enumerate(shapes)}
+
+
+def test_restated_layouts_match_the_reference_headers(image):
+    golden = json.load(open(GOLDEN))
+    for kind, key in ((image.DELTA, "delta"), (image.ATTENTION, "attention")):
+        assert golden[key]["sizeof"][0] == image.PAGE
+        assert golden[key]["magic"] == [0, 8]
+        for name, (offset, fmt) in image.FIELDS[kind].items():
+            assert golden[key][name] == [offset, struct.calcsize(fmt)], (key, name)
+
+
+def test_good_images_open_and_describe_themselves(image, orc, tmp_path):
+    matrices = small_matrices(orc)
+    constants = np.arange(37, dtype=np.float32) * 0.5
+    for kind, layer in ((image.DELTA, 5), (image.ATTENTION, 7), (image.ATTENTION, 64)):
+        path = str(tmp_path / f"layer{kind}_{layer}.img")
+        image.write_layer_image(path, kind, layer, 256, 512, matrices, constants, source_sha256="ab" * 32,
+                                gate_up_reference=range(8), mlp_reference=[0.25] * 8)
+        opened = image.Q4Image(path, kind, layer)
+        info = opened.info
+        assert (info.kind, info.layer_index, info.hidden_size, info.intermediate_size) == (kind, layer, 256, 512)
+        assert [opened.shape(m) for m in range(5)] == [(512, 4), (512, 4), (256, 8), (320, 4), (256, 6)]
+        assert np.array_equal(opened.constants(), constants)
+        assert info.source_sha256 == b"ab" * 32
+        if kind == image.DELTA:
+            assert list(info.gate_up_reference_first_8) == [float(v) for v in range(8)]
+            assert list(info.mlp_reference_first_8) == [0.25] * 8
+            assert list(info.reference_counts) == [8, 8, 0]
+        opened.close()
+        # the digests the caller accepts (the role of pinned_sha)
+        image.Q4Image(path, kind, layer, allowed_sha256=["cd" * 32, "ab" * 32]).close()
+        with pytest.raises(image.Q4Error) as refused:
+            image.Q4Image(path, kind, layer, allowed_sha256=["cd" * 32])
+        assert refused.value.status == 3 and "digest" in refused.value.message
+
+
+def test_broken_images_are_refused(image, orc, tmp_path):
+    matrices = small_matrices(orc)
+    path = str(tmp_path / "good.img")
+    image.write_layer_image(path, image.DELTA, 5, 256, 512, matrices, np.zeros(8, np.float32))
+    good = open(path, "rb").read()
+    fields = image.FIELDS[image.DELTA]
+
+    def refused(data: bytes, needle: str, layer=5, kind=image.DELTA, strict=False):
+        broken = str(tmp_path / "broken.img")
+        with open(broken, "wb") as handle:
+            handle.write(data)
+        with pytest.raises(image.Q4Error) as info:
+            image.Q4Image(broken, kind, layer, check_27b_shapes=strict)
+        assert info.value.status == 3, info.value.message
+        assert needle in info.value.message, info.value.message
+
+    def patched(name, value):
+        data = bytearray(good)
+        struct.pack_into(fields[name][1], data, fields[name][0], value)
+        return bytes(data)
+
+    refused(good[:100], "cannot open")                                   # shorter than one page
+    refused(b"X" + good[1:], "magic")
+    refused(patched("version", 2), "version")
+    refused(patched("header_bytes", 8192), "one page")
+    refused(patched("group_size", 128), "group size")
+    refused(good, "layer index", layer=6)
+    refused(patched("layer_index", 7), "attention layers", layer=7)      # DeltaNet image at an attention layer
+    refused(good, "magic", kind=image.ATTENTION, layer=7)
+    refused(patched("gate_metadata_offset", struct.unpack_from("<Q", good, fields["gate_metadata_offset"][0])[0] + 16),
+            "page-aligned")
+    refused(good[:-4096], "outside the file")
+    refused(good + b"\0" * 4096, "does not end")
+    refused(patched("up_quants_offset", 1 << 40), "outside the file")
+    refused(patched("rows", 1024), "smaller than its matrix")
+    refused(patched("constants_f32_count", 1 << 24), "constants")
+    refused(good, "27B", strict=True)
+    with pytest.raises(image.Q4Error) as missing:
+        image.Q4Image(str(tmp_path / "absent.img"), image.DELTA, 5)
+    assert missing.value.status == 3
+
+
+def test_segments_are_the_bytes_the_writer_put_there(image, orc, tmp_path):
+    import ctypes
+    matrices = small_matrices(orc)
+    path = str(tmp_path / "layer.img")
+    image.write_layer_image(path, image.DELTA, 1, 256, 512, matrices)
+    opened = image.Q4Image(path, image.DELTA, 1)
+    lib = importlib.import_module("cpu-llms-in-c_b200").library()
+    for m, (quants, meta) in matrices.items():
+        q, md = ctypes.c_void_p(), ctypes.c_void_p()
+        assert lib.q4b_image_segments(opened.handle, m, ctypes.byref(q), ctypes.byref(md)) == 0
+        got_q = np.ctypeslib.as_array(ctypes.cast(q, ctypes.POINTER(ctypes.c_uint8)), shape=(quants.size,))
+        got_m = np.ctypeslib.as_array(ctypes.cast(md, ctypes.POINTER(ctypes.c_uint16)), shape=(meta.size,))
+        assert np.array_equal(got_q, quants.reshape(-1)) and np.array_equal(got_m, meta.reshape(-1))
+    opened.close()
