@@ -123,6 +123,19 @@ def synth_weight(seed: int, projection: int, rows: int, groups: int):
             meta.reshape(rows, groups, 2))
 
 
+def synth_weight_rows(seed: int, projection: int, groups: int, rows):
+    """The given rows of the seeded matrix `synth_weight` would produce, without
+    generating the rest (the generator is counter-based).  Returns (quants uint8
+    [len(rows), groups*32], meta uint16 [len(rows), groups, 2])."""
+    rows = [int(r) for r in rows]
+    quants = np.empty((len(rows), groups * 8), dtype=np.uint32)
+    meta = np.empty((len(rows), groups * 2), dtype=np.uint16)
+    for i, row in enumerate(rows):
+        lib().q4o_synth_codes(seed, stream_of(projection, 0), _ptr(quants[i], _u32p), row * groups * 8, groups * 8)
+        lib().q4o_synth_meta(seed, stream_of(projection, 1), _ptr(meta[i], _u16p), row * groups, groups)
+    return quants.view(np.uint8).reshape(len(rows), groups * 32), meta.reshape(len(rows), groups, 2)
+
+
 def bf16_exact_meta(seed: int, projection: int, rows: int, groups: int):
     """Seeded metadata whose values are exact in BOTH bf16 and fp16.
 
