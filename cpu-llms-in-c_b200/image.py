@@ -196,3 +196,85 @@ class Q4Image:
         if self.handle:
             library().q4b_image_close(self.handle)
             self.handle = None
+
+
+class Q4LayerMatmuls:
+    """The Q4 matmuls of one layer on one rank (q4b_layer_*): the host-side mirror
+    of the reference's encode_mlp / in-projection / out-projection dispatch."""
+
+    def __init__(self, ctx: Q4Context, handle):
+        self.ctx, self.handle = ctx, handle
+
+    @staticmethod
+    def _prototypes():
+        lib = library()
+        err = [ctypes.c_char_p, ctypes.c_size_t]
+        u32, i32 = ctypes.c_uint32, ctypes.c_int
+        lib.q4b_layer_load.argtypes = [_vp, _vp, u32, u32, ctypes.POINTER(_vp)] + err
+        lib.q4b_layer_wrap.argtypes = [ctypes.POINTER(_vp), ctypes.POINTER(u32), ctypes.POINTER(u32), u32, u32,
+                                       ctypes.POINTER(_vp)]
+        lib.q4b_layer_free.argtypes = [_vp, _vp]
+        lib.q4b_layer_free.restype = None
+        lib.q4b_layer_slice.argtypes = [u32, u32, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]
+        lib.q4b_layer_slice.restype = None
+        lib.q4b_layer_encode_input.argtypes = [_vp, _vp, _vp, u32, _vp, i32] + err
+        lib.q4b_layer_encode_output.argtypes = [_vp, _vp, _vp, i32, u32, _vp, i32, _vp, i32] + err
+        lib.q4b_layer_encode_gate_up.argtypes = [_vp, _vp, _vp, u32, _vp, i32] + err
+        lib.q4b_layer_encode_down.argtypes = [_vp, _vp, _vp, i32, u32, _vp, i32, _vp, i32] + err
+        lib.q4b_layer_encode_mlp.argtypes = [_vp, _vp, _vp, u32, _vp, i32, _vp, i32, _vp, i32] + err
+        return lib
+
+    @classmethod
+    def load(cls, ctx: Q4Context, image: Q4Image, rank: int = 0, world: int = 1) -> "Q4LayerMatmuls":
+        lib = cls._prototypes()
+        handle = _vp()
+        ctx._check(lib.q4b_layer_load(ctx.handle, image.handle, rank, world, ctypes.byref(handle), ctx._err, 512))
+        return cls(ctx, handle)
+
+    @classmethod
+    def wrap(cls, ctx: Q4Context, matrices, rows_total, row_begin, rank: int = 0, world: int = 1) -> "Q4LayerMatmuls":
+        lib = cls._prototypes()
+        handles = (_vp * 5)(*[None if m is None else m.handle for m in matrices])
+        totals = (ctypes.c_uint32 * 5)(*rows_total)
+        begins = (ctypes.c_uint32 * 5)(*row_begin)
+        handle = _vp()
+        if lib.q4b_layer_wrap(handles, totals, begins, rank, world, ctypes.byref(handle)) != 0:
+            raise Q4Error(1, "invalid layer description")
+        return cls(ctx, handle)
+
+    @classmethod
+    def slice_of(cls, rows: int, rank: int, world: int) -> tuple[int, int]:
+        lib = cls._prototypes()
+        begin, count = ctypes.c_uint32(), ctypes.c_uint32()
+        lib.q4b_layer_slice(rows, rank, world, ctypes.byref(begin), ctypes.byref(count))
+        return begin.value, count.value
+
+    def encode_input(self, normalized: int, batch: int, projected: int, dtype: int):
+        self.ctx._check(library().q4b_layer_encode_input(self.ctx.handle, self.handle, normalized, batch, projected,
+                                                         dtype, self.ctx._err, 512))
+
+    def encode_output(self, mixer: int, mixer_dtype: int, batch: int, residual, residual_dtype: int, hidden: int,
+                      hidden_dtype: int):
+        self.ctx._check(library().q4b_layer_encode_output(self.ctx.handle, self.handle, mixer, mixer_dtype, batch,
+                                                          residual, residual_dtype, hidden, hidden_dtype,
+                                                          self.ctx._err, 512))
+
+    def encode_gate_up(self, post_normalized: int, batch: int, intermediate: int, dtype: int):
+        self.ctx._check(library().q4b_layer_encode_gate_up(self.ctx.handle, self.handle, post_normalized, batch,
+                                                           intermediate, dtype, self.ctx._err, 512))
+
+    def encode_down(self, intermediate: int, dtype: int, batch: int, residual, residual_dtype: int, out: int,
+                    out_dtype: int):
+        self.ctx._check(library().q4b_layer_encode_down(self.ctx.handle, self.handle, intermediate, dtype, batch,
+                                                        residual, residual_dtype, out, out_dtype, self.ctx._err, 512))
+
+    def encode_mlp(self, post_normalized: int, batch: int, intermediate: int, dtype: int, residual,
+                   residual_dtype: int, out: int, out_dtype: int):
+        self.ctx._check(library().q4b_layer_encode_mlp(self.ctx.handle, self.handle, post_normalized, batch,
+                                                       intermediate, dtype, residual, residual_dtype, out, out_dtype,
+                                                       self.ctx._err, 512))
+
+    def free(self):
+        if self.handle:
+            library().q4b_layer_free(self.ctx.handle, self.handle)
+            self.handle = None

@@ -113,8 +113,8 @@ int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *c
  * x is [M][K] row-major fp16 or fp32, y is [M][ldy] fp16 or fp32 (ldy >= rows
  * of the shard lets a shard write its column slice of a wider matrix),
  * residual is [M][ld_residual] fp16 or fp32 or NULL.  DEVICE pointers, 16-byte
- * aligned; asynchronous.  The kernel is chosen by M: GEMV for M <= 32, the
- * tcgen05 GEMM above. */
+ * aligned; asynchronous.  The kernel is chosen by M: the decode kernel for
+ * M <= 16, the tcgen05 GEMM above. */
 int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
                uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, const void *residual,
                int residual_dtype, uint32_t ld_residual,
@@ -272,6 +272,48 @@ int q4b_image_segments(const q4b_image *image, int matrix, const void **quants, 
 int q4b_image_weight(q4b_context *context, const q4b_image *image, int matrix, uint32_t row_begin,
                      uint32_t row_count, q4b_weight **weight, char *error_message, size_t error_capacity);
 void q4b_image_close(q4b_image *image);
+
+/* ---- one decoder layer's Q4 matmuls, as the reference's encoders issue them
+ * (qwen38_m3_decode.m): the in-projection at the head of encode_delta (:668-674)
+ * and encode_attention (:747-753), the out-projection with residual at their
+ * tails (:716-723, :788-795), encode_mlp (:639-660): fused gate/up + SiLU, then
+ * down with the residual added; and their batched forms encode_prefill_gemm_f16
+ * (:885-928), encode_prefill_gemm_residual (:930-1001), encode_prefill_mlp
+ * (:1016-1038) -- one entry point each, the kernel is chosen by `batch`.
+ *
+ * A layer holds, of every matrix, the rows this rank owns (column-parallel over
+ * `world` ranks; q4b_layer_slice gives the rule: contiguous, 16-row granular).
+ * All activations are DEVICE pointers, [batch, width] row-major with the FULL
+ * width of the matrix's output: a call writes columns [begin, begin+count) and
+ * leaves the rest to the other ranks (gather is the caller's; with world = 1 the
+ * slice is everything).  Inputs: fp16, except where a dtype is passed (the
+ * reference feeds fp32 to the second projections, qwen38_layer.metal:193-255).
+ * q4b_layer_encode_mlp runs both halves and therefore needs world = 1. */
+typedef struct q4b_layer q4b_layer;
+void q4b_layer_slice(uint32_t rows, uint32_t rank, uint32_t world, uint32_t *row_begin, uint32_t *row_count);
+int q4b_layer_load(q4b_context *context, const q4b_image *image, uint32_t rank, uint32_t world,
+                   q4b_layer **layer, char *error_message, size_t error_capacity);
+/* a layer over matrices the caller already holds (Q4B_MATRIX_* order, entries may be NULL);
+ * rows_total = rows of the whole matrix, row_begin = first row the given shard holds */
+int q4b_layer_wrap(const q4b_weight *const *matrices, const uint32_t *rows_total, const uint32_t *row_begin,
+                   uint32_t rank, uint32_t world, q4b_layer **layer);
+void q4b_layer_free(q4b_context *context, q4b_layer *layer);
+int q4b_layer_encode_input(q4b_context *context, const q4b_layer *layer, const void *normalized_f16,
+                           uint32_t batch, void *projected, int projected_dtype,
+                           char *error_message, size_t error_capacity);
+int q4b_layer_encode_output(q4b_context *context, const q4b_layer *layer, const void *mixer_output,
+                            int mixer_dtype, uint32_t batch, const void *residual, int residual_dtype,
+                            void *hidden, int hidden_dtype, char *error_message, size_t error_capacity);
+int q4b_layer_encode_gate_up(q4b_context *context, const q4b_layer *layer, const void *post_normalized_f16,
+                             uint32_t batch, void *intermediate, int intermediate_dtype,
+                             char *error_message, size_t error_capacity);
+int q4b_layer_encode_down(q4b_context *context, const q4b_layer *layer, const void *intermediate,
+                          int intermediate_dtype, uint32_t batch, const void *residual, int residual_dtype,
+                          void *layer_output, int output_dtype, char *error_message, size_t error_capacity);
+int q4b_layer_encode_mlp(q4b_context *context, const q4b_layer *layer, const void *post_normalized_f16,
+                         uint32_t batch, void *intermediate, int intermediate_dtype, const void *residual,
+                         int residual_dtype, void *layer_output, int output_dtype,
+                         char *error_message, size_t error_capacity);
 
 /* ---- read-bandwidth probe: the role of the reference's device-memory probe
  * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):

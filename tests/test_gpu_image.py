@@ -85,3 +85,53 @@ def test_image_reproduces_its_embedded_reference(q4b, orc, ctx, image, tmp_path)
     for weight in (gate, up, down):
         weight.free()
     opened.close()
+
+
+def oracle_mlp(orc, matrices, image, hidden, intermediate, x, residual):
+    """silu(gate x) * (up x) in fp32, then down on that fp32 vector plus residual, as the
+    reference's decode MLP does (qwen38_q4_gate_up_silu, qwen38_q4_mlp_down_residual_f32)."""
+    (gq, gm), (uq, um), (dq, dm) = matrices[image.GATE], matrices[image.UP], matrices[image.DOWN]
+    mid32, _ = orc.gate_up_silu(gq, gm, uq, um, hidden // 64, x, want64=False)
+    _, out = orc.matmul(dq, dm, intermediate // 64, mid32, residual=residual, want32=False)
+    return mid32, out
+
+
+@pytest.mark.parametrize("batch", [1, 4, 40])
+def test_layer_encoders_from_an_image(q4b, orc, ctx, image, tmp_path, batch):
+    hidden, intermediate, input_rows, output_groups = 1024, 3072, 2112, 32
+    path = str(tmp_path / "layer.img")
+    matrices, _ = build(orc, image, path, image.DELTA, 4, hidden, intermediate, input_rows, output_groups, seed=4)
+    opened = image.Q4Image(path, image.DELTA, 4)
+    x = orc.synth_x(4, 0, batch, hidden)
+    residual = orc.synth_x(4, 7, batch, hidden).astype(np.float32)
+    mixer = orc.synth_x(4, 8, batch, output_groups * 64).astype(np.float32)
+    mid_ref, out_ref = oracle_mlp(orc, matrices, image, hidden, intermediate, x, residual)
+    _, in_ref = orc.matmul(*matrices[image.INPUT], hidden // 64, x, want32=False)
+    _, o_ref = orc.matmul(*matrices[image.OUTPUT], output_groups, mixer, residual=residual, want32=False)
+
+    dx, dres, dmix = ctx.to_device(x), ctx.to_device(residual), ctx.to_device(mixer)
+    for world in (1, 2, 3):
+        dmid = ctx.to_device(np.zeros((batch, intermediate), np.float32))
+        dout = ctx.to_device(np.zeros((batch, hidden), np.float32))
+        din = ctx.to_device(np.zeros((batch, input_rows), np.float16))
+        dhid = ctx.to_device(np.zeros((batch, hidden), np.float32))
+        layers = [image.Q4LayerMatmuls.load(ctx, opened, rank, world) for rank in range(world)]
+        if world == 1:
+            layers[0].encode_mlp(dx.ptr, batch, dmid.ptr, q4b.F32, dres.ptr, q4b.F32, dout.ptr, q4b.F32)
+        else:
+            with pytest.raises(q4b.Q4Error):
+                layers[0].encode_mlp(dx.ptr, batch, dmid.ptr, q4b.F32, dres.ptr, q4b.F32, dout.ptr, q4b.F32)
+            for layer in layers:      # every rank's slice of the intermediate lands in the same buffer: the gather
+                layer.encode_gate_up(dx.ptr, batch, dmid.ptr, q4b.F32)
+            for layer in layers:
+                layer.encode_down(dmid.ptr, q4b.F32, batch, dres.ptr, q4b.F32, dout.ptr, q4b.F32)
+        for layer in layers:
+            layer.encode_input(dx.ptr, batch, din.ptr, q4b.F16)
+            layer.encode_output(dmix.ptr, q4b.F32, batch, dres.ptr, q4b.F32, dhid.ptr, q4b.F32)
+        assert_close(dmid.download(np.float32, (batch, intermediate)), mid_ref.astype(np.float64), f"gate/up world {world}")
+        assert_close(dout.download(np.float32, (batch, hidden)), out_ref, f"mlp world {world}")
+        assert_close(din.download(np.float16, (batch, input_rows)), in_ref, f"in-projection world {world}")
+        assert_close(dhid.download(np.float32, (batch, hidden)), o_ref, f"out-projection world {world}")
+        for layer in layers:
+            layer.free()
+    opened.close()

@@ -115,3 +115,16 @@ def test_segments_are_the_bytes_the_writer_put_there(image, orc, tmp_path):
         got_m = np.ctypeslib.as_array(ctypes.cast(md, ctypes.POINTER(ctypes.c_uint16)), shape=(meta.size,))
         assert np.array_equal(got_q, quants.reshape(-1)) and np.array_equal(got_m, meta.reshape(-1))
     opened.close()
+
+
+def test_row_slices_of_the_c_layer_match_the_python_rule(image, q4b):
+    layer = importlib.import_module("cpu-llms-in-c_b200.layer")
+    for rows in (16, 100, 1024, 5120, 6144, 16480, 17408, 248320):
+        for world in (1, 2, 3, 4, 8):
+            covered = 0
+            for rank in range(world):
+                got = image.Q4LayerMatmuls.slice_of(rows, rank, world)
+                assert got == layer.slice_of(rows, rank, world)
+                assert got[0] == covered
+                covered += got[1]
+            assert covered == rows
