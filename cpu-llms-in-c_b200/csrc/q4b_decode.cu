@@ -23,6 +23,8 @@
 // kernel: no collective call per projection.
 #include "q4b_kernels.h"
 
+#include <cstdlib>
+
 #include <cooperative_groups.h>
 
 #ifdef Q4B_TRACE
@@ -161,6 +163,7 @@ decode_sequence_kernel(const SeqParams p) {
     uint8_t *ring = sq_smem + 128;
     float *red = reinterpret_cast<float *>(ring + (size_t)stages * kStageBytes);   // [L][kPerBlock]
     uint32_t *flags = reinterpret_cast<uint32_t *>(red + (size_t)p.max_local_blocks * kPerBlock);
+    float *part = reinterpret_cast<float *>(flags + ((p.max_local_blocks + 3u) & ~3u));  // [W][512], M <= 4 only
     const uint32_t full0 = sq_smem_u32(bars), empty0 = sq_smem_u32(bars + kSeqMaxStages);
     const uint32_t ring0 = sq_smem_u32(ring);
 
@@ -298,12 +301,56 @@ decode_sequence_kernel(const SeqParams p) {
             }
         };
 
+        // The same for M <= 4 in two barriers: only columns 0..3 of the 8-wide tiles carry activations,
+        // so every warp parks those (2 planes x 64 rows x 4 columns) in its own slice and the CTA's
+        // threads add the eight slices in warp order.
+        auto flush_small = [&](uint32_t lrb) {
+            float *mine = part + (size_t)warp * 512;
+            if (t < 2) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t row = r * 16 + gid;
+                        *reinterpret_cast<float2 *>(mine + (k * 64 + row) * 4 + 2 * t) =
+                            make_float2(acc[k][r][0][0], acc[k][r][0][1]);
+                        *reinterpret_cast<float2 *>(mine + (k * 64 + row + 8) * 4 + 2 * t) =
+                            make_float2(acc[k][r][0][2], acc[k][r][0][3]);
+                    }
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[k][r][0][0] = acc[k][r][0][1] = acc[k][r][0][2] = acc[k][r][0][3] = 0.0f;
+            sq_consumer_barrier();
+            float *target = red + (size_t)lrb * kPerBlock;
+            for (uint32_t o = threadIdx.x; o < 512; o += 256) {
+                const uint32_t k = o >> 8, row = (o >> 2) & 63u, col = o & 3u;
+                float total = 0.0f;
+#pragma unroll
+                for (int w = 0; w < W; ++w) total += part[(size_t)w * 512 + o];
+                // fragment layout of the block sums: tile r = row / 16, lane = 4 (row % 8) + col / 2,
+                // element 2 (row / 8 % 2) + col % 2
+                const uint32_t index = k * (NT * 512) + (row >> 4) * 128 + ((row & 7u) * 4 + (col >> 1)) * 4 +
+                                       ((row >> 3) & 1u) * 2 + (col & 1u);
+                target[index] += total;
+            }
+            sq_consumer_barrier();
+        };
+        auto flush = [&](uint32_t lrb) {
+            if (NT == 1 && m_rows <= 4) {
+                flush_small(lrb);
+            } else {
+                flush_in_turns(lrb);
+            }
+        };
+
         uint32_t ua = u0, g = g_first, cur_grb = grb0, grb = grb0;
         while (ua < u1) {
             const uint32_t s = it % stages;
             const uint32_t count = min(min(per_stage, G - g), u1 - ua);
             if (grb != cur_grb) {
-                flush_in_turns(cur_grb - grb0);
+                flush(cur_grb - grb0);
                 cur_grb = grb;
             }
             if (!sq_wait(full0 + 8 * s, (it / stages) & 1)) {
@@ -397,7 +444,7 @@ decode_sequence_kernel(const SeqParams p) {
         if (range == 0) continue;
         SQ_ADD(1, t_loop);
         const long long t_flush = SQ_CLOCK();
-        flush_in_turns(cur_grb - grb0);  // ends with a consumer barrier
+        flush(cur_grb - grb0);  // ends with a consumer barrier
         SQ_ADD(2, t_flush);
         const long long t_finish = SQ_CLOCK();
         // ---- finish every row block this CTA touched ----
@@ -420,13 +467,13 @@ decode_sequence_kernel(const SeqParams p) {
             const uint32_t contributed = min(u1, (b + 1) * G) - max(u0, b * G);
             uint32_t finish = 1;
             if (contributed != G) {
-                __threadfence();
-                const uint32_t before = atomicAdd(p.counters + b, contributed);
+                // release: the CTA's parked sums (ordered before this by the barrier) are visible to whoever reads
+                // the count; acquire: the last arriver sees everybody else's
+                uint32_t before;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                             : "=r"(before) : "l"(p.counters + b), "r"(contributed) : "memory");
                 finish = before + contributed == G ? 2u : 0u;
-                if (finish) {
-                    p.counters[b] = 0;  // ready for the next job
-                    __threadfence();
-                }
+                if (finish) p.counters[b] = 0;  // ready for the next job (ordered by the publishing release below)
             }
             flags[threadIdx.x] = finish;
         }
@@ -453,9 +500,19 @@ decode_sequence_kernel(const SeqParams p) {
                     value = mine[o];
                     if (fused) second = mine[NT * 512 + o];
                 } else {  // the slots in CTA order: the same sum whichever CTA arrives last
-                    for (uint32_t c = 0; c < contributors; ++c) {
-                        value += __ldcg(slots + (size_t)c * kPerBlock + o);
-                        if (fused) second += __ldcg(slots + (size_t)c * kPerBlock + NT * 512 + o);
+                    for (uint32_t c0 = 0; c0 < contributors; c0 += 4) {  // four loads in flight at a time
+                        float a[4], b[4];
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q) {
+                            const bool live = c0 + q < contributors;
+                            a[q] = live ? __ldcg(slots + (size_t)(c0 + q) * kPerBlock + o) : 0.0f;
+                            b[q] = live && fused ? __ldcg(slots + (size_t)(c0 + q) * kPerBlock + NT * 512 + o) : 0.0f;
+                        }
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q) {
+                            value += a[q];
+                            second += b[q];
+                        }
                     }
                 }
                 if (fused) {
@@ -488,7 +545,6 @@ decode_sequence_kernel(const SeqParams p) {
                     asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_done[r] + j), "r"(finished) : "memory");
                 SQ_ADD(5, t_publish);
             } else {
-                __threadfence();
                 asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.done + j), "r"(finished) : "memory");
             }
         }
@@ -518,8 +574,11 @@ void plan_decode_job(DecodeJob *job, uint32_t m_rows, uint32_t ctas, size_t *scr
     const uint32_t units = blocks * G;
     job->total_units = units;
     // every row block cut into the same number of parts when all parts fit the grid
+    // Every row block cut into the same number of K parts when all parts fit the grid: one CTA then touches
+    // one row block only.  (Equal unit ranges over the whole grid balance the bytes better but make every CTA
+    // share two or three row blocks; measured 80 against 68 us per 27B layer.)
     uint32_t parts = 0;
-    if (blocks <= ctas) {
+    if (blocks <= ctas && getenv("Q4B_SEQUENCE_EQUAL_RANGES") == nullptr) {
         for (uint32_t k = 1; k <= G; ++k) {
             if (blocks * k <= ctas && (G / k >= 4 || k == 1)) parts = k;
         }
@@ -554,7 +613,8 @@ cudaError_t sequence_geometry(uint32_t m_rows, int sm_count, uint32_t stages, ui
     const int NT = m_rows <= 8 ? 1 : 2;
     if (m_rows == 0 || m_rows > 16 || stages < 2 || stages > (uint32_t)kSeqMaxStages) return cudaErrorInvalidValue;
     const size_t bytes = 128 + (size_t)stages * 16 * kUnitBytes +
-                         (size_t)max_local_blocks * (2 * NT * 4 * 128) * sizeof(float) + max_local_blocks * 4 + 16;
+                         (size_t)max_local_blocks * (2 * NT * 4 * 128) * sizeof(float) +
+                         ((max_local_blocks + 3u) & ~3u) * 4 + (m_rows <= 4 ? 8 * 512 * sizeof(float) : 0) + 16;
     if (bytes > 220 * 1024) return cudaErrorInvalidValue;
     int per_sm = 0;
     cudaError_t status = NT == 1 ? sequence_attributes<1>(bytes, &per_sm) : sequence_attributes<2>(bytes, &per_sm);

@@ -317,6 +317,19 @@ gemv_kernel(const GemvParams p) {
             }
         };
 
+        // B fragments come straight from global memory (x is small and stays in L1/L2): lane (gid, t)
+        // holds x[m = gid][64 g + 16 t .. +15] for each column tile.  They are fetched one stage ahead,
+        // so that their latency hides behind the tiles of the stage before.
+        uint32_t x_ahead[NT][8];
+        auto fetch_x = [&](uint32_t group) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const uint32_t m = n * 8 + gid;
+                load_x16<X32>(p.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, x_ahead[n]);
+            }
+        };
+        if (range > 0 && j_mine < min(min(S, G - g_first), range)) fetch_x(g_first + j_mine);
+
         // ---- main loop: the same stage sequence the producer issues ----
         uint32_t ua = u0, g = g_first, cur_grb = grb0, grb = grb0;
         for (uint32_t it = 0; ua < u1; ++it) {
@@ -335,16 +348,20 @@ gemv_kernel(const GemvParams p) {
             }
             Q4B_ADD(8, clock64() - wait_begin);
             Q4B_ADD(9, 1);
+            // what the next stage holds, for the fetch ahead
+            const uint32_t ua_next = ua + count, g_next = g + count == G ? 0u : g + count;
+            const uint32_t count_next = ua_next < u1 ? min(min(S, G - g_next), u1 - ua_next) : 0u;
             if (j_mine < count) {
-                // B fragments straight from global memory (x is small and stays in L1/L2):
-                // lane (gid, t) holds x[m = gid][64 g + 16 t .. +15] for each column tile
-                const uint32_t group = g + j_mine;
                 uint32_t xb[NT][8];
                 float2 sums[NT];
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    const uint32_t m = n * 8 + gid;
-                    load_x16<X32>(p.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, xb[n]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) xb[n][i] = x_ahead[n][i];
+                }
+                if (j_mine < count_next) fetch_x(g_next + j_mine);
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
                     // group sums of x on the tensor pipe: a fragment of ones times the same B
                     const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
                     float total[4];
@@ -401,6 +418,9 @@ gemv_kernel(const GemvParams p) {
                     }
                 }
                 }
+            }
+            else if (j_mine < count_next) {
+                fetch_x(g_next + j_mine);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
