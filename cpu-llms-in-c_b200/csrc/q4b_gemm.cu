@@ -30,7 +30,12 @@ namespace q4b {
 
 namespace {
 
-constexpr int kTcStages = 4;     // ring stages (one quantisation group each)
+// ring stages (one quantisation group each): as many as the shared memory holds next to the fused epilogue's
+// exchange buffer -- the X tiles come from L2 and their latency has to be covered by tiles in flight
+template <int BN, bool FUSED>
+struct TcStages {
+    static constexpr int value = BN == 256 ? (FUSED ? 5 : 6) : 8;
+};
 constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
 constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
 constexpr int kTcThreads = 64 + kTcWarpgroups * 128;  // warp 0 producer, warp 1 MMA, then the warpgroups
@@ -48,6 +53,7 @@ struct TcParams {
     uint32_t *status;
     uint32_t ld_residual;
     uint32_t m_rows, groups, n_blocks, m_blocks;
+    uint32_t m_group;            // activation blocks walked together (see tc_tile_of)
     int y_dtype, residual_dtype;
 };
 
@@ -127,11 +133,25 @@ __device__ inline void tc_load_16(uint32_t address, uint32_t (&r)[16]) {
 }
 
 
+// Tile order: the activation blocks are walked in groups of `m_group`; inside a group every weight block
+// meets every activation block of the group before the next weight block starts.  CTAs that run together
+// then share a few weight blocks and a slice of X small enough to stay in L2, whatever M is.
+__device__ inline void tc_tile_of(uint32_t tile, uint32_t n_blocks, uint32_t m_blocks, uint32_t m_group,
+                                  uint32_t &nb_all, uint32_t &mb) {
+    const uint32_t per_group = n_blocks * m_group;
+    const uint32_t group = tile / per_group, rest = tile % per_group;
+    const uint32_t first = group * m_group;
+    const uint32_t width = min(m_group, m_blocks - first);   // the last group may be narrower
+    nb_all = rest / width;
+    mb = first + rest % width;
+}
+
 // BN   : activation rows per tile (columns of D)
 // FUSED: the A tile is 64 rows of `w` (gate) over 64 rows of `up`; epilogue silu(gate) * up
 template <int BN, bool FUSED>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
+    constexpr int kTcStages = TcStages<BN, FUSED>::value;
     constexpr uint32_t kXBytes = BN * 128;               // one group of X: BN rows x 64 halves
     constexpr uint32_t kWBytes = 2 * kUnitBytes;         // two 64-row blocks, one group
     constexpr uint32_t kDCols = BN;
@@ -184,7 +204,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const uint32_t nb_all = tile / p.m_blocks, mb = tile % p.m_blocks;
+                uint32_t nb_all, mb;
+                tc_tile_of(tile, p.n_blocks, p.m_blocks, p.m_group, nb_all, mb);
                 int segment = 0;
 #pragma unroll
                 for (int q = 1; q < kMaxSegments; ++q) {
@@ -263,7 +284,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         const __half2 to_code_add = __half2half2(__ushort_as_half(hi ? 0xd400 : 0xe400));  // -64 or -1024
         uint32_t it = 0, unit = 0, tile_iter = 0;
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
-            const uint32_t nb_all = tile / p.m_blocks, mb = tile % p.m_blocks;
+            uint32_t nb_all, mb;
+            tc_tile_of(tile, p.n_blocks, p.m_blocks, p.m_group, nb_all, mb);
             int segment = 0;
 #pragma unroll
             for (int q = 1; q < kMaxSegments; ++q) {
@@ -405,7 +427,13 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
         return cudaErrorInvalidValue;
     }
     p.m_blocks = ceil_div(args.m_rows, BN);
+    // about 32 MB of X per group of activation blocks
+    const size_t block_bytes = (size_t)BN * args.w[0].groups * kGroup * sizeof(__half);
+    p.m_group = (uint32_t)((size_t)(32u << 20) / block_bytes);
+    if (p.m_group < 1) p.m_group = 1;
+    if (p.m_group > p.m_blocks) p.m_group = p.m_blocks;
     const uint32_t tiles = p.n_blocks * p.m_blocks;
+    constexpr int kTcStages = TcStages<BN, FUSED>::value;
     const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
                               (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + (FUSED ? kTcWarpgroups * 2 * 16 * 64 * 4 : 0) + 1024;
     auto kernel = tc_gemm_kernel<BN, FUSED>;
