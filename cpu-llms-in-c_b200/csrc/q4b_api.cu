@@ -30,6 +30,9 @@ struct q4b_context {
     size_t counter_bytes;
     __half *x16;              // fp16 copy of fp32 activations for the tensor-core GEMM (grown on demand)
     size_t x16_bytes;
+    float *tc_workspace;      // partial tiles of the tensor-core GEMM when it splits tiles over CTAs
+    size_t tc_workspace_bytes;
+    uint32_t *tc_flags;
 };
 
 struct q4b_weight {
@@ -302,7 +305,19 @@ int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_mess
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "activation convert", status);
         x = context->x16;
     }
+    if (context->tc_workspace == nullptr && !context->capturing) {
+        // once per context: sm_count partial tiles of 128 x 256 floats and their flags
+        const size_t bytes = (size_t)context->sm_count * 128 * 256 * sizeof(float);
+        cudaError_t status = cudaMalloc(&context->tc_workspace, bytes);
+        if (status == cudaSuccess) status = cudaMalloc(&context->tc_flags, (size_t)context->sm_count * sizeof(uint32_t));
+        if (status == cudaSuccess) status = cudaMemset(context->tc_flags, 0, (size_t)context->sm_count * sizeof(uint32_t));
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemm workspace", status);
+        context->tc_workspace_bytes = bytes;
+    }
     TcGemmArgs gemm = {};
+    gemm.workspace = context->tc_workspace;
+    gemm.workspace_bytes = context->tc_workspace_bytes;
+    gemm.flags = context->tc_flags;
     for (int s = 0; s < args.segments; ++s) {
         gemm.w[s] = args.w[s];
         gemm.y[s] = args.y[s];
@@ -447,6 +462,8 @@ void q4b_context_close(q4b_context *context) {
     cudaFreeHost(context->status_host);
     cudaFree(context->scratch);
     cudaFree(context->counters);
+    cudaFree(context->tc_workspace);
+    cudaFree(context->tc_flags);
     cudaFree(context->x16);
     delete context;
 }

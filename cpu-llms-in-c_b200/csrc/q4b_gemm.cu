@@ -24,6 +24,7 @@
 // status word, releases its TMEM and returns.
 #include "q4b_kernels.h"
 
+#include <cstdlib>
 #include <cuda.h>
 
 namespace q4b {
@@ -54,6 +55,10 @@ struct TcParams {
     uint32_t ld_residual;
     uint32_t m_rows, groups, n_blocks, m_blocks;
     uint32_t m_group;            // activation blocks walked together (see tc_tile_of)
+    // stream-K (split != 0): the (tile, group) iterations are cut into equal contiguous ranges, one per CTA
+    uint32_t split, iters_per_cta, iters_extra;
+    float *workspace;            // [CTA][128][BN] fp32 partial tiles
+    uint32_t *flags;             // [CTA] 1 while that CTA's partial tile waits to be added, else 0
     int y_dtype, residual_dtype;
 };
 
@@ -146,6 +151,45 @@ __device__ inline void tc_tile_of(uint32_t tile, uint32_t n_blocks, uint32_t m_b
     mb = first + rest % width;
 }
 
+// The work of one CTA as all its roles walk it: a list of segments (tile, groups [g0, g1)).
+// Without splitting a segment is a whole tile and the tiles are dealt round-robin.  With splitting
+// (few tiles for many SMs) the tile-major sequence of (tile, group) iterations is cut into equal
+// contiguous ranges; a tile cut in two or more is summed by the CTA that holds its first groups, which
+// reaches them last in time -- the others left their partial tiles in the workspace long before.
+struct TcWalk {
+    uint32_t split, tile, tiles, step, i, i1, G;
+    __device__ inline void start(const TcParams &p, uint32_t tiles_total) {
+        split = p.split;
+        G = p.groups;
+        tiles = tiles_total;
+        tile = blockIdx.x;
+        step = gridDim.x;
+        i = blockIdx.x * p.iters_per_cta + min(blockIdx.x, p.iters_extra);
+        i1 = i + p.iters_per_cta + (blockIdx.x < p.iters_extra ? 1u : 0u);
+    }
+    __device__ inline bool next(uint32_t &t, uint32_t &g0, uint32_t &g1) {
+        if (split == 0) {
+            if (tile >= tiles) return false;
+            t = tile;
+            g0 = 0;
+            g1 = G;
+            tile += step;
+            return true;
+        }
+        if (i >= i1) return false;
+        t = i / G;
+        g0 = i % G;
+        g1 = min(G, g0 + (i1 - i));
+        i += g1 - g0;
+        return true;
+    }
+};
+__device__ inline uint32_t tc_cta_of_iteration(const TcParams &p, uint32_t iteration) {
+    const uint32_t boundary = p.iters_extra * (p.iters_per_cta + 1);
+    return iteration < boundary ? iteration / (p.iters_per_cta + 1)
+                                : p.iters_extra + (iteration - boundary) / p.iters_per_cta;
+}
+
 // BN   : activation rows per tile (columns of D)
 // FUSED: the A tile is 64 rows of `w` (gate) over 64 rows of `up`; epilogue silu(gate) * up
 template <int BN, bool FUSED>
@@ -202,8 +246,10 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     if (warp == 0) {
         // ---- producer: Q4 tiles by bulk copy, X tile by TMA tensor copy ----
         if (lane == 0) {
-            uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            uint32_t it = 0, tile, g0, g1;
+            TcWalk walk;
+            walk.start(p, tiles);
+            while (ok && walk.next(tile, g0, g1)) {
                 uint32_t nb_all, mb;
                 tc_tile_of(tile, p.n_blocks, p.m_blocks, p.m_group, nb_all, mb);
                 int segment = 0;
@@ -213,7 +259,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 }
                 const uint32_t nb = nb_all - p.block_begin[segment];
                 const uint8_t *tiles = p.w[segment].tiles;
-                for (uint32_t g = 0; g < G; ++g, ++it) {
+                for (uint32_t g = g0; g < g1; ++g, ++it) {
                     const uint32_t s = it % kTcStages;
                     if (it >= kTcStages && !tc_wait(empty0 + 8 * s, ((it / kTcStages) - 1) & 1)) {
                         ok = false;
@@ -247,11 +293,13 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t desc_base = ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
                                        ((uint64_t)2 << 61);
-            uint32_t it = 0, unit = 0, tile_iter = 0;
-            for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
+            uint32_t it = 0, unit = 0, tile_iter = 0, tile, g0, g1;
+            TcWalk walk;
+            walk.start(p, tiles);
+            for (; ok && walk.next(tile, g0, g1); ++tile_iter) {
                 if (tile_iter > 0 && !tc_wait(d_free, (tile_iter - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                for (uint32_t g = 0; g < G && ok; ++g, ++it) {
+                for (uint32_t g = g0; g < g1 && ok; ++g, ++it) {
                     const uint32_t s = it % kTcStages;
                     if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                     const uint32_t xaddr = tc_smem_u32(xbuf) + s * kXBytes;
@@ -261,7 +309,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint64_t desc = desc_base | (uint64_t)(((xaddr + kk * 32) >> 4) & 0x3fffu);
-                        tc_mma(tmem_d, tmem_a + a * 32 + kk * 8, desc, idesc, (g > 0 || kk > 0) ? 1u : 0u);
+                        tc_mma(tmem_d, tmem_a + a * 32 + kk * 8, desc, idesc, (g > g0 || kk > 0) ? 1u : 0u);
                     }
                     ++unit;
                     tc_commit(a_free0 + 8 * a);  // the slot may be rewritten once these MMAs retire
@@ -282,8 +330,10 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         const uint32_t mask = hi ? 0x00F000F0u : 0x000F000Fu;
         const __half2 to_code_mul = __half2half2(__ushort_as_half(hi ? 0x2c00 : 0x3c00));  // 1/16 or 1
         const __half2 to_code_add = __half2half2(__ushort_as_half(hi ? 0xd400 : 0xe400));  // -64 or -1024
-        uint32_t it = 0, unit = 0, tile_iter = 0;
-        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_iter) {
+        uint32_t it = 0, unit = 0, tile_iter = 0, tile, g0, g1;
+        TcWalk walk;
+        walk.start(p, tiles);
+        for (; ok && walk.next(tile, g0, g1); ++tile_iter) {
             uint32_t nb_all, mb;
             tc_tile_of(tile, p.n_blocks, p.m_blocks, p.m_group, nb_all, mb);
             int segment = 0;
@@ -292,12 +342,15 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 if (q < p.segments && nb_all >= p.block_begin[q]) segment = q;
             }
             const uint32_t nb = nb_all - p.block_begin[segment];
-            for (uint32_t g = 0; g < G && ok; ++g, ++it) {
+            for (uint32_t g = g0; g < g1 && ok; ++g, ++it) {
                 const uint32_t s = it % kTcStages;
+                // Every warpgroup observes every phase of every stage barrier, also for the groups it leaves to
+                // the others: a parity wait that skips a phase (a warpgroup returns to a stage only every third
+                // fill when the ring has six stages) would be satisfied by the phase before last.
+                if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                 for (int once = 0; once < 1; ++once, ++unit) {
                     if (unit % kTcWarpgroups != wg) continue;  // the warpgroups take groups in turn
                     const uint32_t a = unit % kTcSlots;
-                    if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                     const uint8_t *tile_bytes = wbuf + s * kWBytes + tile_offset_bytes;
                     const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
                     const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
@@ -340,6 +393,55 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t ldy = p.ldy[segment];
             float *swap = exchange + wg * (2 * 16 * 64);
             constexpr uint32_t kColumnsPerGroup = BN / kTcWarpgroups;
+            if (g0 > 0) {
+                // ---- a later part of a split tile: leave the partial sums for the CTA that holds the first groups ----
+                float *mine = p.workspace + ((size_t)blockIdx.x * 128 + row) * BN;
+#pragma unroll 1
+                for (uint32_t c = wg * kColumnsPerGroup; c < (wg + 1) * kColumnsPerGroup; c += 16) {
+                    uint32_t d0[16];
+                    tc_load_16(tmem_d + c + lane_field, d0);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        *reinterpret_cast<float4 *>(mine + c + j) =
+                            make_float4(__uint_as_float(d0[j]), __uint_as_float(d0[j + 1]), __uint_as_float(d0[j + 2]),
+                                        __uint_as_float(d0[j + 3]));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc_mbar_arrive(d_free);
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(kTcWarpgroups * 128) : "memory");
+                if (threadIdx.x == 64) {
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + blockIdx.x), "r"(1u) : "memory");
+                }
+                continue;
+            }
+            uint32_t partial_first = 0, partial_count = 0;
+            if (g1 < G) {
+                // ---- the first part of a split tile: every later part was finished long ago by its CTA ----
+                partial_first = blockIdx.x + 1;
+                partial_count = tc_cta_of_iteration(p, tile * G + G - 1) - blockIdx.x;
+                if (threadIdx.x == 64) {
+                    const long long start = clock64();
+                    for (uint32_t q = 0; q < partial_count; ++q) {
+                        uint32_t ready = 0;
+                        for (;;) {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ready) : "l"(p.flags + partial_first + q) : "memory");
+                            if (ready != 0) break;
+                            if (clock64() - start > kTcWaitLimit) {
+                                atomicExch(p.status, 0x74u);
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                        p.flags[partial_first + q] = 0;  // consumed: ready for the next launch
+                    }
+                    __threadfence();
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kTcWarpgroups * 128) : "memory");
+            }
             uint32_t chunk = 0;
 #pragma unroll 1
             for (uint32_t c = wg * kColumnsPerGroup; c < (wg + 1) * kColumnsPerGroup; c += 16, ++chunk) {
@@ -347,6 +449,17 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 float other[16];
                 tc_load_16(tmem_d + c + lane_field, d0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (uint32_t q = 0; q < partial_count; ++q) {  // partial tiles in CTA order
+                    const float *theirs = p.workspace + ((size_t)(partial_first + q) * 128 + row) * BN + c;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(theirs + j));
+                        d0[j] = __float_as_uint(__uint_as_float(d0[j]) + v.x);
+                        d0[j + 1] = __float_as_uint(__uint_as_float(d0[j + 1]) + v.y);
+                        d0[j + 2] = __float_as_uint(__uint_as_float(d0[j + 2]) + v.z);
+                        d0[j + 3] = __float_as_uint(__uint_as_float(d0[j + 3]) + v.w);
+                    }
+                }
                 if (FUSED) {
                     // rows 64..127 hold `up` of the feature whose `gate` sits 64 rows above
                     float *buffer = swap + (chunk & 1) * (16 * 64);
@@ -443,7 +556,26 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
         if (status != cudaSuccess) return status;
         configured = true;
     }
-    const unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
+    unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
+    // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last round
+    // (160 on 148).  Split the iterations evenly instead when that wins a tenth or more.
+    const uint32_t rounds = ceil_div(tiles, (uint32_t)sm_count);
+    const double whole_tile_efficiency = (double)tiles / ((double)rounds * sm_count);
+    const uint64_t iterations = (uint64_t)tiles * p.groups;
+    p.split = 0;
+    if (args.workspace != nullptr && getenv("Q4B_GEMM_WHOLE_TILES") == nullptr && whole_tile_efficiency < 0.9 && iterations >= (uint64_t)sm_count * 8 &&
+        (size_t)sm_count * 128 * BN * sizeof(float) <= args.workspace_bytes) {
+        p.split = 1;
+        grid = (unsigned)sm_count;
+        p.iters_per_cta = (uint32_t)(iterations / grid);
+        p.iters_extra = (uint32_t)(iterations % grid);
+        p.workspace = args.workspace;
+        p.flags = args.flags;
+        // CTAs wait on one another: all of them must be resident
+        void *arguments[] = {&p};
+        return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), dim3(grid), dim3(kTcThreads), arguments,
+                                           smem_bytes, stream);
+    }
     kernel<<<grid, kTcThreads, smem_bytes, stream>>>(p);
     return cudaGetLastError();
 }

@@ -107,6 +107,11 @@ struct TcGemmArgs {
     int residual_dtype;
     uint32_t ld_residual;
     uint32_t *status;
+    // optional, for splitting tiles over CTAs when there are few: sm_count x 128 x 256 floats and sm_count
+    // zero-initialised flags (left zero by every launch)
+    float *workspace;
+    size_t workspace_bytes;
+    uint32_t *flags;
 };
 cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream);
 cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream);

@@ -31,8 +31,10 @@ def oracle_rows(orc, quants, meta, groups, x, rows, residual=None):
     return np.concatenate(cols, axis=1)
 
 
+# the last four have few tiles for 148 SMs: their (tile, group) iterations are split evenly over the CTAs
 @pytest.mark.parametrize("n,k,m", [(256, 128, 64), (128, 64, 17), (384, 320, 300), (1024, 2048, 128),
-                                   (1000, 1024, 257), (2048, 5120, 512)])
+                                   (1000, 1024, 257), (2048, 5120, 512), (5120, 17408, 512), (640, 6144, 512),
+                                   (2560, 5120, 100), (1100, 4096, 700)])
 def test_gemm_matches_oracle(q4b, orc, ctx, n, k, m):
     groups = k // 64
     quants, meta = orc.synth_weight(3, 0, n, groups)
@@ -48,9 +50,8 @@ def test_gemm_matches_oracle(q4b, orc, ctx, n, k, m):
     assert np.isfinite(y.astype(np.float32)).all()
 
 
-@pytest.mark.parametrize("m", [64, 200])
-def test_gemm_fused_gate_up(q4b, orc, ctx, m):
-    n, k = 640, 1024
+@pytest.mark.parametrize("m,n,k", [(64, 640, 1024), (200, 640, 1024), (300, 3072, 5120), (512, 2176, 5120)])
+def test_gemm_fused_gate_up(q4b, orc, ctx, m, n, k):
     groups = k // 64
     gq, gm = orc.synth_weight(0, 4, n, groups)
     uq, um = orc.synth_weight(0, 5, n, groups)
