@@ -286,6 +286,8 @@ def run_ours(args):
     prefill = []
     if world == 1 and not args.no_prefill:
         prefill = prefill_gemm(q4b, ctx, model, peaks)
+    elif not args.no_prefill:
+        prefill = sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks)
     extras = {"prefill_gemm": prefill,
               "whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
               "whole_step_frac_of_8TBs": value / world / 8000.0,
@@ -335,6 +337,25 @@ def prefill_gemm(q4b, ctx, model, peaks, layers=8):
         for b in list(xs.values()) + list(ys.values()):
             b.free()
     return results
+
+
+def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, layers=8, m=512):
+    """BASELINE configs[4] at M = 512: every rank runs the tensor-core GEMM on its N-slices of the 27B layer
+    set and the slices are all-gathered (NCCL on the context's stream); device time, max over ranks."""
+    stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, layers, m, rank, world, dist, gather="nccl")
+    for _ in range(2):
+        stack.step()
+    barrier()
+    reps = 3
+    ctx.timer_start()
+    for _ in range(reps):
+        stack.step()
+    ms = max_over_ranks(ctx.sync(timed=True)) / (reps * layers)
+    barrier()
+    tflops = q4b.layer_flops(q4b.LAYER_27B, m) / (ms * 1e-3) / 1e12
+    stack.free()
+    return [{"m_rows": m, "ms_per_layer": ms, "tflops": tflops, "gather": "nccl all-gather per projection",
+             "frac_of_measured_bf16_burst_per_gpu": tflops / world / peaks["bf16_tflops"]}]
 
 
 def main():
