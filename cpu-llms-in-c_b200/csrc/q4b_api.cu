@@ -623,6 +623,22 @@ int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_p
     return Q4B_OK;
 }
 
+int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, const uint32_t *rows, uint32_t count,
+                         void *out, int out_dtype, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (embedding == nullptr || rows == nullptr || out == nullptr || !valid_activation_dtype(out_dtype) ||
+        embedding->device != context->device || !aligned16(out)) {
+        set_error(error_message, error_capacity, "embedding, row list or output missing, or not fp16/fp32 16-byte aligned");
+        return Q4B_BAD_ARGUMENT;
+    }
+    cudaError_t status = launch_lookup_rows(embedding->view, rows, count, embedding->row_begin, out, out_dtype,
+                                            context->stream);
+    if (!context->capturing) ++context->launches;
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "embedding lookup", status);
+    return Q4B_OK;
+}
+
 int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *codes, float *w32,
                       uint16_t *w16, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);

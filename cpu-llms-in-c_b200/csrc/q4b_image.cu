@@ -1,15 +1,17 @@
 // Layer-image files: open, validate, hand matrices to the loader.
 //
 // Replaces map_file / validate_delta_header / validate_attention_header /
-// load_delta_layer / load_attention_layer of the reference runtime
-// (models/qwen3.8-27b/targets/apple-m3-pro/qwen38_m3_decode.m:374-625) for the
-// part that concerns the Q4 matmul path: the ten Q4 segments of a layer (gate, up,
-// down, input projection, output projection; quants + metadata each) and the
+// validate_global_header / load_delta_layer / load_attention_layer / load_global of
+// the reference runtime (models/qwen3.8-27b/targets/apple-m3-pro/
+// qwen38_m3_decode.m:374-625) for the part that concerns the Q4 matmul path: the ten
+// Q4 segments of a layer (gate, up, down, input projection, output projection;
+// quants + metadata each), the embedding and lm_head of the global image, and the
 // embedded eight-row references the packer stored for self-checks.  The file
 // layouts are the reference's (qwen38_m3_image.h:26-94, version 3, magic
-// "Q38M3Q4\0"; qwen38_m3_attention_image.h:21-72, version 1, magic "Q38M3ATT");
-// they are restated here as field offsets, pinned by a test against the offsets the
-// reference's own headers give.
+// "Q38M3Q4\0"; qwen38_m3_attention_image.h:21-72, version 1, magic "Q38M3ATT";
+// qwen38_m3_global_image.h:14-38, version 1, magic "Q38M3GLB"); they are restated
+// here as field offsets, pinned by a test against the offsets the reference's own
+// headers give.
 //
 // On unified memory the reference wraps the mapping in no-copy buffers; on a B200
 // a matrix is uploaded and repacked into the tile stream (q4b_weight_upload), by
@@ -40,6 +42,7 @@ struct ShapeFields {  // byte offsets of the uint32 rows / groups-per-row of one
 struct Layout {
     unsigned char magic[8];
     uint32_t version;
+    uint32_t matrices;          // 5 for a layer image, 2 for the global image (embedding, lm_head)
     uint32_t layer_index, hidden_size, intermediate_size, group_size, constants_count;
     SegmentFields segment[5];   // gate, up, down, input, output
     ShapeFields shape[5];
@@ -52,7 +55,7 @@ struct Layout {
 
 // qwen38_m3_image.h:26-94
 const Layout kDelta = {
-    {'Q', '3', '8', 'M', '3', 'Q', '4', '\0'}, 3,
+    {'Q', '3', '8', 'M', '3', 'Q', '4', '\0'}, 3, 5,
     284, 16, 20, 24, 304,
     {{56, 64, 72, 80}, {88, 96, 104, 112}, {120, 128, 136, 144}, {384, 392, 400, 408}, {416, 424, 432, 440}},
     {{20, 0}, {20, 0}, {40, 44}, {288, 292}, {296, 300}},
@@ -63,12 +66,24 @@ const Layout kDelta = {
 };
 // qwen38_m3_attention_image.h:21-72
 const Layout kAttention = {
-    {'Q', '3', '8', 'M', '3', 'A', 'T', 'T'}, 1,
+    {'Q', '3', '8', 'M', '3', 'A', 'T', 'T'}, 1, 5,
     16, 20, 24, 28, 64,
     {{72, 80, 88, 96}, {104, 112, 120, 128}, {136, 144, 152, 160}, {216, 224, 232, 240}, {248, 256, 264, 272}},
     {{24, 0}, {24, 0}, {0, 0}, {48, 52}, {56, 60}},
     168, 176, 4,
     280, 0,
+    0, 0, 0,
+    0, 0, 0,
+};
+
+// qwen38_m3_global_image.h:14-38: embedding and lm_head, both [vocab, hidden]; the file ends with the constants
+const Layout kGlobal = {
+    {'Q', '3', '8', 'M', '3', 'G', 'L', 'B'}, 1, 2,
+    0, 20, 16, 24, 28,
+    {{40, 48, 56, 64}, {72, 80, 88, 96}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}},
+    {{16, 0}, {16, 0}, {0, 0}, {0, 0}, {0, 0}},
+    104, 112, 0xffffffffu,
+    120, 185,
     0, 0, 0,
     0, 0, 0,
 };
@@ -109,12 +124,13 @@ extern "C" {
 int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_27b_shapes,
                    const char *const *allowed_sha256, int allowed_count, q4b_image **image,
                    char *error_message, size_t error_capacity) {
-    if (path == nullptr || image == nullptr || (kind != Q4B_IMAGE_DELTA && kind != Q4B_IMAGE_ATTENTION)) {
+    if (path == nullptr || image == nullptr ||
+        (kind != Q4B_IMAGE_DELTA && kind != Q4B_IMAGE_ATTENTION && kind != Q4B_IMAGE_GLOBAL)) {
         set_message(error_message, error_capacity, "path, kind or result pointer missing");
         return Q4B_BAD_ARGUMENT;
     }
     *image = nullptr;
-    const Layout &layout = kind == Q4B_IMAGE_DELTA ? kDelta : kAttention;
+    const Layout &layout = kind == Q4B_IMAGE_DELTA ? kDelta : kind == Q4B_IMAGE_ATTENTION ? kAttention : kGlobal;
     // map_file (qwen38_m3_decode.m:374-396): a regular file of at least one page, mapped read-only
     const int file = open(path, O_RDONLY);
     struct stat status;
@@ -148,7 +164,7 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
     // validate_delta_header / validate_attention_header (:409-446)
     info.kind = (uint32_t)kind;
     info.version = read_u32(h, 8);
-    info.layer_index = read_u32(h, layout.layer_index);
+    info.layer_index = layout.layer_index != 0 ? read_u32(h, layout.layer_index) : 0;
     info.hidden_size = read_u32(h, layout.hidden_size);
     info.intermediate_size = read_u32(h, layout.intermediate_size);
     info.group_size = read_u32(h, layout.group_size);
@@ -157,15 +173,16 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
     else if (info.version != layout.version) problem = "wrong version";
     else if (read_u32(h, 12) != kPage) problem = "header is not one page";
     else if (info.group_size != 64) problem = "group size is not 64";
-    else if (info.layer_index != layer_index) problem = "layer index differs from the one asked for";
+    else if (layout.layer_index != 0 && info.layer_index != layer_index)
+        problem = "layer index differs from the one asked for";
     else if (kind == Q4B_IMAGE_DELTA && layer_index % 4 == 3) problem = "layers 3 mod 4 are attention layers";
     else if (kind == Q4B_IMAGE_ATTENTION && layer_index % 4 != 3 && layer_index != kMtpLayerIndex)
         problem = "only layers 3 mod 4 (and the MTP layer) are attention layers";
     else if (info.hidden_size == 0 || info.hidden_size % 64 != 0 || info.intermediate_size == 0 ||
-             info.intermediate_size % 64 != 0)
+             (kind != Q4B_IMAGE_GLOBAL && info.intermediate_size % 64 != 0))
         problem = "hidden or intermediate size is not a positive multiple of 64";
 
-    for (int m = 0; m < 5 && problem == nullptr; ++m) {
+    for (int m = 0; m < (int)layout.matrices && problem == nullptr; ++m) {
         // rows and groups: gate/up are [intermediate, hidden/64]; down of the attention image [hidden, intermediate/64]
         uint32_t rows = layout.shape[m].rows != 0 ? read_u32(h, layout.shape[m].rows) : info.hidden_size;
         uint32_t groups = layout.shape[m].groups != 0 ? read_u32(h, layout.shape[m].groups)
@@ -194,10 +211,18 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
         if (c_offset > length || c_bytes > length - c_offset || c_bytes < (uint64_t)info.constants_f32_count * 4)
             problem = "the constants lie outside the file";
         const uint32_t last = layout.last_segment;
-        const uint64_t end = read_u64(h, layout.segment[last].meta_offset) + read_u64(h, layout.segment[last].meta_bytes);
-        if (problem == nullptr && end != length) problem = "the file does not end with the output metadata";
+        const uint64_t end = last == 0xffffffffu ? c_offset + c_bytes
+                                                 : read_u64(h, layout.segment[last].meta_offset) +
+                                                       read_u64(h, layout.segment[last].meta_bytes);
+        if (problem == nullptr && end != length)
+            problem = last == 0xffffffffu ? "the file does not end with the constants"
+                                          : "the file does not end with the output metadata";
     }
-    if (problem == nullptr && check_27b_shapes) {
+    if (problem == nullptr && check_27b_shapes && kind == Q4B_IMAGE_GLOBAL) {
+        // validate_global_header (:447-460)
+        if (info.intermediate_size != 248320 || info.hidden_size != 5120 || info.constants_f32_count != 5120)
+            problem = "not the 27B vocabulary and hidden size";
+    } else if (problem == nullptr && check_27b_shapes) {
         // the shapes the reference runtime insists on (:412-421, :433-443)
         const bool delta = kind == Q4B_IMAGE_DELTA;
         const bool ok = info.hidden_size == 5120 && info.intermediate_size == 17408 &&
@@ -225,7 +250,8 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
     }
     if (problem != nullptr) {
         set_message(error_message, error_capacity, "invalid %s image at layer %u: %s",
-                    kind == Q4B_IMAGE_DELTA ? "DeltaNet" : "attention", layer_index, problem);
+                    kind == Q4B_IMAGE_DELTA ? "DeltaNet" : kind == Q4B_IMAGE_ATTENTION ? "attention" : "global",
+                    layer_index, problem);
         q4b_image_close(result);
         return Q4B_LOAD_FAILURE;
     }
@@ -254,7 +280,10 @@ const float *q4b_image_constants(const q4b_image *image, uint32_t *count) {
 }
 
 int q4b_image_segments(const q4b_image *image, int matrix, const void **quants, const void **metadata) {
-    if (image == nullptr || matrix < 0 || matrix >= 5 || quants == nullptr || metadata == nullptr) return Q4B_BAD_ARGUMENT;
+    if (image == nullptr || matrix < 0 || matrix >= (int)image->layout->matrices || quants == nullptr ||
+        metadata == nullptr) {
+        return Q4B_BAD_ARGUMENT;
+    }
     *quants = image->mapping + image->quants_offset[matrix];
     *metadata = image->mapping + image->meta_offset[matrix];
     return Q4B_OK;
@@ -262,7 +291,7 @@ int q4b_image_segments(const q4b_image *image, int matrix, const void **quants, 
 
 int q4b_image_weight(q4b_context *context, const q4b_image *image, int matrix, uint32_t row_begin,
                      uint32_t row_count, q4b_weight **weight, char *error_message, size_t error_capacity) {
-    if (image == nullptr || matrix < 0 || matrix >= 5) {
+    if (image == nullptr || matrix < 0 || matrix >= (int)image->layout->matrices) {
         set_message(error_message, error_capacity, "no image or no such matrix");
         return Q4B_BAD_ARGUMENT;
     }

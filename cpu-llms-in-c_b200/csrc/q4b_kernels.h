@@ -15,6 +15,10 @@ cudaError_t launch_repack(const uint8_t *quants, const void *meta, const void *b
 // tile stream -> codes u8 [rows][K], w32 [rows][K], w16 [rows][K] (any may be null)
 cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
                           cudaStream_t stream);
+// rows[i] (device, numbered in the whole matrix; row_base = first row this shard holds) dequantised into
+// out[i][K] fp16 or fp32; rows the shard does not hold give zeros
+cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t count, uint32_t row_base, void *out,
+                               int out_dtype, cudaStream_t stream);
 cudaError_t launch_synth_codes(uint64_t seed, uint64_t stream_id, uint32_t *words,
                                uint64_t word_begin, uint64_t word_count, cudaStream_t stream);
 cudaError_t launch_synth_meta(uint64_t seed, uint64_t stream_id, __half *meta,

@@ -165,6 +165,61 @@ cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
 }
 
 // ---------------------------------------------------------------------------
+// rows of a matrix, dequantised: the embedding lookup
+// (qwen38_q4_embedding_lookup, qwen38_global.metal:13-28: out[c] = half(float(scale) * float(q) + float(bias)))
+// ---------------------------------------------------------------------------
+// one thread per (requested row, group, quarter of the group): 16 columns
+__global__ void __launch_bounds__(256)
+lookup_rows_kernel(WeightView w, const uint32_t *__restrict__ rows, uint32_t count, uint32_t row_base,
+                   void *__restrict__ out, int out_dtype) {
+    const uint64_t thread = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t per_row = w.groups * 4;
+    const uint64_t which = thread / per_row;
+    if (which >= count) return;
+    const uint32_t rest = (uint32_t)(thread % per_row), g = rest >> 2, t = rest & 3u;
+    const uint32_t row = rows[which] - row_base;  // rows outside this shard wrap to huge values
+    const size_t columns = (size_t)w.groups * kGroup;
+    const size_t at = which * columns + (size_t)g * kGroup + 16 * t;
+    if (row >= w.rows) {  // not held here: zeros, so that the shards of a split vocabulary add up
+        if (out_dtype == kF32) {
+            for (int i = 0; i < 16; ++i) reinterpret_cast<float *>(out)[at + i] = 0.0f;
+        } else {
+            for (int i = 0; i < 16; ++i) reinterpret_cast<__half *>(out)[at + i] = __float2half_rn(0.0f);
+        }
+        return;
+    }
+    const uint32_t rt = row >> 4, within = row & 15u, gid = within & 7u, upper = within >> 3;
+    const uint8_t *in = w.tiles + tile_offset(rt, g, w.groups);
+    const uint4 words = reinterpret_cast<const uint4 *>(in)[piece_index(gid * 4 + t)];
+    const uint2 record = reinterpret_cast<const uint2 *>(in + kTileCodeBytes)[gid];
+    const __half2 meta = *reinterpret_cast<const __half2 *>(upper ? &record.y : &record.x);
+    const float scale = __low2float(meta), bias = __high2float(meta);
+    const uint32_t word[4] = {words.x, words.y, words.z, words.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            // column 4 i + c of this lane's 16 sits in nibble 4 (c % 2) + 2 (c / 2) of word i, rows gid + 8 one nibble up
+            const uint32_t nibble = 4u * (c & 1) + 2u * (c >> 1) + upper;
+            const float value = dequant_w32((word[i] >> (4u * nibble)) & 0xfu, scale, bias);
+            if (out_dtype == kF32) {
+                reinterpret_cast<float *>(out)[at + 4 * i + c] = value;
+            } else {
+                reinterpret_cast<__half *>(out)[at + 4 * i + c] = __float2half_rn(value);
+            }
+        }
+    }
+}
+
+cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t count, uint32_t row_base, void *out,
+                               int out_dtype, cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    const uint64_t threads = (uint64_t)count * w.groups * 4;
+    lookup_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(w, rows, count, row_base, out, out_dtype);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // seeded generator
 // ---------------------------------------------------------------------------
 __global__ void synth_codes_kernel(uint64_t key, uint32_t *words, uint64_t word_begin,

@@ -90,6 +90,7 @@ def library() -> ctypes.CDLL:
         "q4b_matmul_host": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
                                          ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_embedding_lookup": (_int, [_vp, _vp, _vp, _u32, _vp, _int] + err),
         "q4b_sequence_create": (_int, [_vp, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_sequence_add_matmul": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, ctypes.POINTER(_vp),
                                            ctypes.POINTER(_u32), _int] + err),
@@ -397,6 +398,10 @@ class Q4Context:
         strides = (_u32 * count)(*(ldys if ldys is not None else [w.rows for w in weights]))
         self._check(library().q4b_matmul_group(self.handle, handles, count, x_ptr, x_dtype, m_rows, outputs,
                                                y_dtype, strides, self._err, _ERR))
+
+    def embedding_lookup(self, embedding: Q4Weight, rows_ptr: int, count: int, out_ptr: int, out_dtype: int = F16):
+        self._check(library().q4b_embedding_lookup(self.handle, embedding.handle, rows_ptr, count, out_ptr, out_dtype,
+                                                   self._err, _ERR))
 
     def gate_up_silu(self, gate: Q4Weight, up: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int,
                      y_dtype: int = F16, ldy: int | None = None):

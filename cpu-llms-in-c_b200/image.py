@@ -19,7 +19,8 @@ import numpy as np
 from .host import Q4Context, Q4Error, Q4Weight, _vp, library
 
 PAGE = 4096
-DELTA, ATTENTION = 0, 1
+DELTA, ATTENTION, GLOBAL = 0, 1, 2
+EMBEDDING, LM_HEAD = 0, 1
 GATE, UP, DOWN, INPUT, OUTPUT = range(5)
 MATRIX_NAMES = ("gate", "up", "down", "input", "output")
 
@@ -60,9 +61,19 @@ _ATTENTION_FIELDS = {
     "attention_output_metadata_offset": (264, "<Q"), "attention_output_metadata_bytes": (272, "<Q"),
     "source_sha256": (280, "65s"),
 }
-FIELDS = {DELTA: _DELTA_FIELDS, ATTENTION: _ATTENTION_FIELDS}
-MAGIC = {DELTA: b"Q38M3Q4\0", ATTENTION: b"Q38M3ATT"}
-VERSION = {DELTA: 3, ATTENTION: 1}
+_GLOBAL_FIELDS = {
+    "version": (8, "<I"), "header_bytes": (12, "<I"), "vocab_size": (16, "<I"), "hidden_size": (20, "<I"),
+    "group_size": (24, "<I"), "constants_f32_count": (28, "<I"),
+    "embedding_quants_offset": (40, "<Q"), "embedding_quants_bytes": (48, "<Q"),
+    "embedding_metadata_offset": (56, "<Q"), "embedding_metadata_bytes": (64, "<Q"),
+    "lm_head_quants_offset": (72, "<Q"), "lm_head_quants_bytes": (80, "<Q"),
+    "lm_head_metadata_offset": (88, "<Q"), "lm_head_metadata_bytes": (96, "<Q"),
+    "constants_offset": (104, "<Q"), "constants_bytes": (112, "<Q"),
+    "embedding_source_sha256": (120, "65s"), "lm_head_source_sha256": (185, "65s"),
+}
+FIELDS = {DELTA: _DELTA_FIELDS, ATTENTION: _ATTENTION_FIELDS, GLOBAL: _GLOBAL_FIELDS}
+MAGIC = {DELTA: b"Q38M3Q4\0", ATTENTION: b"Q38M3ATT", GLOBAL: b"Q38M3GLB"}
+VERSION = {DELTA: 3, ATTENTION: 1, GLOBAL: 1}
 _SEGMENT_PREFIX = {DELTA: ("gate", "up", "down", "delta_input", "delta_output"),
                    ATTENTION: ("gate", "up", "down", "attention_input", "attention_output")}
 
@@ -127,6 +138,41 @@ def write_layer_image(path: str, kind: int, layer_index: int, hidden_size: int, 
             struct.pack_into(fmt, header, offset, *value)
         else:
             struct.pack_into(fmt, header, offset, value)
+    with open(path, "wb") as handle:
+        handle.write(header)
+        handle.write(body)
+    return values
+
+
+def write_global_image(path: str, hidden_size: int, embedding, lm_head, constants: np.ndarray | None = None,
+                       embedding_sha256: str = "0" * 64, lm_head_sha256: str = "0" * 64) -> dict:
+    """Write a global image (qwen38_m3_global_image.h): embedding and lm_head, each (quants uint8
+    [vocab, hidden/2], meta uint16 [vocab, hidden/64, 2]); the fp32 constants end the file."""
+    fields = FIELDS[GLOBAL]
+    constants = np.zeros(0, dtype=np.float32) if constants is None else np.ascontiguousarray(constants, np.float32)
+    header = bytearray(PAGE)
+    header[0:8] = MAGIC[GLOBAL]
+    values: dict = {"version": VERSION[GLOBAL], "header_bytes": PAGE, "vocab_size": int(embedding[0].shape[0]),
+                    "hidden_size": hidden_size, "group_size": 64, "constants_f32_count": int(constants.size),
+                    "embedding_source_sha256": embedding_sha256.encode(),
+                    "lm_head_source_sha256": lm_head_sha256.encode()}
+    body = bytearray()
+
+    def append(data: bytes) -> tuple[int, int]:
+        offset = PAGE + len(body)
+        padded = _padded(data)
+        body.extend(padded)
+        return offset, len(padded)
+
+    for prefix, (quants, meta) in (("embedding", embedding), ("lm_head", lm_head)):
+        values[f"{prefix}_quants_offset"], values[f"{prefix}_quants_bytes"] = append(
+            np.ascontiguousarray(quants, np.uint8).tobytes())
+        values[f"{prefix}_metadata_offset"], values[f"{prefix}_metadata_bytes"] = append(
+            np.ascontiguousarray(meta, np.uint16).tobytes())
+    values["constants_offset"], values["constants_bytes"] = append(constants.tobytes())
+    for name, value in values.items():
+        offset, fmt = fields[name]
+        struct.pack_into(fmt, header, offset, value)
     with open(path, "wb") as handle:
         handle.write(header)
         handle.write(body)

@@ -99,6 +99,14 @@ int q4b_synth_x(q4b_context *context, uint64_t seed, uint64_t stream_id, void *d
 void q4b_weight_free(q4b_context *context, q4b_weight *weight);
 int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_per_row,
                     uint64_t *device_bytes);
+/* Embedding lookup: replaces qwen38_q4_embedding_lookup (qwen38_global.metal:13-28).
+ * out[i][k] = scale * (float)q + bias of row rows[i] (rounded to fp16 when out_dtype
+ * is fp16, as the reference does), i < count.  rows (DEVICE memory) are numbered in
+ * the whole matrix; a shard (row slice) writes zeros for rows it does not hold, so
+ * the shards of a split vocabulary add up.  Asynchronous. */
+int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, const uint32_t *rows,
+                         uint32_t count, void *out, int out_dtype,
+                         char *error_message, size_t error_capacity);
 /* Dequantisation in isolation (the job of qwen38_q4_embedding_lookup,
  * qwen38_global.metal:13-28) over the whole shard, written to HOST buffers, any
  * of which may be NULL: codes uint8 [rows][K], w32 float [rows][K] =
@@ -248,8 +256,12 @@ int q4b_ipc_close(q4b_context *context, void *peer_pointer);
  * digests the caller accepts, the role of pinned_sha.  Failures return
  * Q4B_LOAD_FAILURE with a message.  No GPU is needed to open an image. */
 typedef struct q4b_image q4b_image;
-enum { Q4B_IMAGE_DELTA = 0, Q4B_IMAGE_ATTENTION = 1 };
+enum { Q4B_IMAGE_DELTA = 0, Q4B_IMAGE_ATTENTION = 1, Q4B_IMAGE_GLOBAL = 2 };
 enum { Q4B_MATRIX_GATE = 0, Q4B_MATRIX_UP = 1, Q4B_MATRIX_DOWN = 2, Q4B_MATRIX_INPUT = 3, Q4B_MATRIX_OUTPUT = 4 };
+/* the global image (qwen38_m3_global_image.h:14-38, magic "Q38M3GLB", version 1; load_global, :462-498) holds two
+ * [vocabulary, hidden] matrices; its info reports the vocabulary as intermediate_size, the embedding's source
+ * digest as source_sha256 and the lm_head's as mlp_source_sha256; layer_index is ignored */
+enum { Q4B_MATRIX_EMBEDDING = 0, Q4B_MATRIX_LM_HEAD = 1 };
 typedef struct {
     uint32_t kind, version, layer_index, hidden_size, intermediate_size, group_size;
     uint32_t rows[5], groups[5];          /* by Q4B_MATRIX_*: output rows and K/64 */

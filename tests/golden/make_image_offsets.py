@@ -17,6 +17,7 @@ import tempfile
 HEADERS = {
     "delta": ("qwen38_m3_image.h", "qwen38_m3_image_header"),
     "attention": ("qwen38_m3_attention_image.h", "qwen38_m3_attention_image_header"),
+    "global": ("qwen38_m3_global_image.h", "qwen38_m3_global_image_header"),
 }
 
 

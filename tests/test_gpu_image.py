@@ -135,3 +135,40 @@ def test_layer_encoders_from_an_image(q4b, orc, ctx, image, tmp_path, batch):
         for layer in layers:
             layer.free()
     opened.close()
+
+
+def test_embedding_lookup_from_a_global_image(q4b, orc, ctx, image, tmp_path):
+    vocab, hidden = 3001, 1024
+    embedding = orc.synth_weight(6, 0, vocab, hidden // 64)
+    lm_head = orc.synth_weight(6, 1, vocab, hidden // 64)
+    path = str(tmp_path / "global.img")
+    image.write_global_image(path, hidden, embedding, lm_head, np.ones(hidden, np.float32))
+    opened = image.Q4Image(path, image.GLOBAL, 0)
+    tokens = np.array([0, 1, 15, 16, 17, 2999, 3000, 1234, 1234, 64, 127, 128], dtype=np.uint32)
+    w32 = orc.dequant_w32(*embedding, vocab, hidden // 64)
+    d_tokens = ctx.to_device(tokens)
+    whole = opened.weight(ctx, image.EMBEDDING)
+    out16, out32 = ctx.alloc(tokens.size * hidden * 2), ctx.alloc(tokens.size * hidden * 4)
+    ctx.embedding_lookup(whole, d_tokens.ptr, tokens.size, out32.ptr, q4b.F32)
+    ctx.embedding_lookup(whole, d_tokens.ptr, tokens.size, out16.ptr, q4b.F16)
+    assert bits_equal(out32.download(np.float32, (tokens.size, hidden)), w32[tokens])
+    assert bits_equal(out16.download(np.float16, (tokens.size, hidden)), w32[tokens].astype(np.float16))
+    # a vocabulary split over three ranks: every shard answers for its rows and writes zeros elsewhere
+    total = np.zeros((tokens.size, hidden), dtype=np.float32)
+    for rank in range(3):
+        begin, count = image.Q4LayerMatmuls.slice_of(vocab, rank, 3)
+        shard = opened.weight(ctx, image.EMBEDDING, begin, count)
+        ctx.embedding_lookup(shard, d_tokens.ptr, tokens.size, out32.ptr, q4b.F32)
+        total += out32.download(np.float32, (tokens.size, hidden))
+        shard.free()
+    assert bits_equal(total, w32[tokens])
+    # and the lm_head of the same image as a matmul
+    head = opened.weight(ctx, image.LM_HEAD)
+    x = orc.synth_x(6, 0, 1, hidden)
+    dx, dy = ctx.to_device(x), ctx.alloc(vocab * 4)
+    ctx.matmul(head, dx.ptr, q4b.F16, 1, dy.ptr, q4b.F32)
+    _, want = orc.matmul(*lm_head, hidden // 64, x, want32=False)
+    assert_close(dy.download(np.float32, (1, vocab)), want, "lm_head from the global image")
+    for weight in (whole, head):
+        weight.free()
+    opened.close()

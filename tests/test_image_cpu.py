@@ -27,7 +27,7 @@ def small_matrices(orc, hidden=256, intermediate=512, input_rows=320, output_gro
 
 def test_restated_layouts_match_the_reference_headers(image):
     golden = json.load(open(GOLDEN))
-    for kind, key in ((image.DELTA, "delta"), (image.ATTENTION, "attention")):
+    for kind, key in ((image.DELTA, "delta"), (image.ATTENTION, "attention"), (image.GLOBAL, "global")):
         assert golden[key]["sizeof"][0] == image.PAGE
         assert golden[key]["magic"] == [0, 8]
         for name, (offset, fmt) in image.FIELDS[kind].items():
@@ -128,3 +128,32 @@ def test_row_slices_of_the_c_layer_match_the_python_rule(image, q4b):
                 assert got[0] == covered
                 covered += got[1]
             assert covered == rows
+
+
+def test_global_image_opens_and_is_validated(image, orc, tmp_path):
+    vocab, hidden = 1000, 256          # a vocabulary that is no multiple of 64
+    embedding = orc.synth_weight(5, 0, vocab, hidden // 64)
+    lm_head = orc.synth_weight(5, 1, vocab, hidden // 64)
+    constants = np.arange(hidden, dtype=np.float32)
+    path = str(tmp_path / "global.img")
+    image.write_global_image(path, hidden, embedding, lm_head, constants, "aa" * 32, "bb" * 32)
+    opened = image.Q4Image(path, image.GLOBAL, 0)
+    assert (opened.info.intermediate_size, opened.info.hidden_size) == (vocab, hidden)
+    assert opened.shape(image.EMBEDDING) == (vocab, 4) and opened.shape(image.LM_HEAD) == (vocab, 4)
+    assert opened.info.source_sha256 == b"aa" * 32 and opened.info.mlp_source_sha256 == b"bb" * 32
+    assert np.array_equal(opened.constants(), constants)
+    opened.close()
+    image.Q4Image(path, image.GLOBAL, 0, allowed_sha256=["aa" * 32, "bb" * 32]).close()
+    for bad_list in (["aa" * 32], ["bb" * 32]):
+        with pytest.raises(image.Q4Error):
+            image.Q4Image(path, image.GLOBAL, 0, allowed_sha256=bad_list)
+    with pytest.raises(image.Q4Error) as strict:
+        image.Q4Image(path, image.GLOBAL, 0, check_27b_shapes=True)
+    assert "27B" in strict.value.message
+    data = open(path, "rb").read()
+    broken = str(tmp_path / "broken.img")
+    with open(broken, "wb") as handle:
+        handle.write(data + b"\0" * 4096)
+    with pytest.raises(image.Q4Error) as tail:
+        image.Q4Image(broken, image.GLOBAL, 0)
+    assert "does not end with the constants" in tail.value.message
