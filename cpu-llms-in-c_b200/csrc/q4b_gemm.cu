@@ -558,12 +558,16 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     }
     unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
     // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last round
-    // (160 on 148).  Split the iterations evenly instead when that wins a tenth or more.
+    // (160 on 148).  Split the iterations evenly instead when that wins: a CTA then works through
+    // iterations / SMs groups plus about 48 groups' worth of leaving and adding a 128 x BN partial tile
+    // (measured: 5120 -> 6144 at M = 512, 96 tiles of 80 groups, is faster whole).
     const uint32_t rounds = ceil_div(tiles, (uint32_t)sm_count);
-    const double whole_tile_efficiency = (double)tiles / ((double)rounds * sm_count);
     const uint64_t iterations = (uint64_t)tiles * p.groups;
+    const double whole_cost = (double)rounds * p.groups;
+    const double split_cost = (double)iterations / sm_count + 48.0;
     p.split = 0;
-    if (args.workspace != nullptr && getenv("Q4B_GEMM_WHOLE_TILES") == nullptr && whole_tile_efficiency < 0.9 && iterations >= (uint64_t)sm_count * 8 &&
+    if (args.workspace != nullptr && getenv("Q4B_GEMM_WHOLE_TILES") == nullptr && split_cost < 0.92 * whole_cost &&
+        iterations >= (uint64_t)sm_count * 8 &&
         (size_t)sm_count * 128 * BN * sizeof(float) <= args.workspace_bytes) {
         p.split = 1;
         grid = (unsigned)sm_count;
