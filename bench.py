@@ -361,7 +361,7 @@ def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_ov
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--m", type=int, default=1, help="activation rows (1 decode, 4 verify)")
