@@ -287,7 +287,7 @@ def run_ours(args):
     if world == 1 and not args.no_prefill:
         prefill = prefill_gemm(q4b, ctx, model, peaks)
     elif not args.no_prefill:
-        prefill = sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks)
+        prefill = sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, args.gather)
     extras = {"prefill_gemm": prefill,
               "whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
               "whole_step_frac_of_8TBs": value / world / 8000.0,
@@ -339,10 +339,10 @@ def prefill_gemm(q4b, ctx, model, peaks, layers=8):
     return results
 
 
-def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, layers=8, m=512):
+def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, gather, layers=8, m=512):
     """BASELINE configs[4] at M = 512: every rank runs the tensor-core GEMM on its N-slices of the 27B layer
     set and the slices are all-gathered (NCCL on the context's stream); device time, max over ranks."""
-    stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, layers, m, rank, world, dist, gather="nccl")
+    stack = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, layers, m, rank, world, dist, gather=gather)
     for _ in range(2):
         stack.step()
     barrier()
@@ -354,7 +354,9 @@ def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_ov
     barrier()
     tflops = q4b.layer_flops(q4b.LAYER_27B, m) / (ms * 1e-3) / 1e12
     stack.free()
-    return [{"m_rows": m, "ms_per_layer": ms, "tflops": tflops, "gather": "nccl all-gather per projection",
+    return [{"m_rows": m, "ms_per_layer": ms, "tflops": tflops,
+             "gather": ("slices stored into every rank's output by the GEMM epilogue + rank barrier" if gather == "push"
+                        else "nccl all-gather per projection"),
              "frac_of_measured_bf16_burst_per_gpu": tflops / world / peaks["bf16_tflops"]}]
 
 

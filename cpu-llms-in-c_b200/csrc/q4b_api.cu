@@ -30,6 +30,8 @@ struct q4b_context {
     size_t counter_bytes;
     __half *x16;              // fp16 copy of fp32 activations for the tensor-core GEMM (grown on demand)
     size_t x16_bytes;
+    void *push_y[kMaxSegments][kMaxPeers];  // q4b_context_push_outputs: consumed by the next tensor-core launch
+    uint32_t push_peers;
     float *tc_workspace;      // partial tiles of the tensor-core GEMM when it splits tiles over CTAs
     size_t tc_workspace_bytes;
     uint32_t *tc_flags;
@@ -315,6 +317,11 @@ int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_mess
         context->tc_workspace_bytes = bytes;
     }
     TcGemmArgs gemm = {};
+    gemm.peers = context->push_peers;
+    for (int s = 0; s < kMaxSegments; ++s) {
+        for (int r = 0; r < kMaxPeers; ++r) gemm.peer_y[s][r] = context->push_y[s][r];
+    }
+    context->push_peers = 0;
     gemm.workspace = context->tc_workspace;
     gemm.workspace_bytes = context->tc_workspace_bytes;
     gemm.flags = context->tc_flags;
@@ -350,6 +357,12 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
     // variant bit 15 keeps large M on the small-M kernel (row blocks of 16), for A/B runs
     if (total > limit && !built_in_scratch && ((context->variant >> 15) & 1) == 0) {
         return run_tensor_core(context, args, error_message, error_capacity);
+    }
+    if (context->push_peers != 0) {
+        context->push_peers = 0;
+        set_error(error_message, error_capacity,
+                  "pushed outputs are for M > %u; up to that, ranks share outputs through a sequence", limit);
+        return Q4B_BAD_ARGUMENT;
     }
     for (uint32_t m0 = 0; m0 < total; m0 += limit) {
         GemvArgs block = args;
@@ -621,6 +634,91 @@ int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_p
     if (groups_per_row != nullptr) *groups_per_row = weight->view.groups;
     if (device_bytes != nullptr) *device_bytes = weight->device_bytes;
     return Q4B_OK;
+}
+
+int q4b_context_push_outputs(q4b_context *context, uint32_t world, void *const *peer_y, int count) {
+    if (context == nullptr) return Q4B_BAD_ARGUMENT;
+    context->push_peers = 0;
+    if (peer_y == nullptr || world == 0 || world > (uint32_t)kMaxPeers || count < 1 || count > kMaxSegments) {
+        return Q4B_BAD_ARGUMENT;
+    }
+    for (int s = 0; s < kMaxSegments; ++s) {
+        for (uint32_t r = 0; r < (uint32_t)kMaxPeers; ++r) {
+            context->push_y[s][r] = s < count && r < world ? peer_y[(size_t)s * world + r] : nullptr;
+        }
+    }
+    context->push_peers = world;
+    return Q4B_OK;
+}
+
+struct q4b_barrier {
+    uint32_t *counter;                 // own arrivals, device memory, counts up for ever
+    uint32_t *counters[kMaxPeers];     // every rank's (own included)
+    uint32_t world, rank, round;
+    int device;
+};
+
+int q4b_barrier_create(q4b_context *context, uint32_t world, uint32_t rank, q4b_barrier **barrier,
+                       char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (barrier == nullptr || world == 0 || world > (uint32_t)kMaxPeers || rank >= world) {
+        set_error(error_message, error_capacity, "a barrier joins 1..%d ranks", kMaxPeers);
+        return Q4B_BAD_ARGUMENT;
+    }
+    q4b_barrier *result = new (std::nothrow) q4b_barrier();
+    if (result == nullptr) return Q4B_DEVICE_FAILURE;
+    cudaError_t status = cudaMalloc(&result->counter, 256);
+    if (status == cudaSuccess) status = cudaMemset(result->counter, 0, 256);
+    if (status != cudaSuccess) {
+        delete result;
+        return device_failure(error_message, error_capacity, "barrier counter", status);
+    }
+    result->world = world;
+    result->rank = rank;
+    result->device = context->device;
+    result->counters[rank] = result->counter;
+    *barrier = result;
+    return Q4B_OK;
+}
+
+void *q4b_barrier_counter(q4b_barrier *barrier) { return barrier != nullptr ? barrier->counter : nullptr; }
+
+int q4b_barrier_set_peer(q4b_barrier *barrier, uint32_t peer_rank, void *peer_counter) {
+    if (barrier == nullptr || peer_rank >= barrier->world || peer_counter == nullptr) return Q4B_BAD_ARGUMENT;
+    barrier->counters[peer_rank] = static_cast<uint32_t *>(peer_counter);
+    return Q4B_OK;
+}
+
+int q4b_barrier_queue(q4b_context *context, q4b_barrier *barrier, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (barrier == nullptr || barrier->device != context->device || context->capturing) {
+        set_error(error_message, error_capacity, "no barrier, another device's, or called while recording");
+        return Q4B_BAD_ARGUMENT;
+    }
+    for (uint32_t r = 0; r < barrier->world; ++r) {
+        if (barrier->counters[r] == nullptr) {
+            set_error(error_message, error_capacity, "rank %u's counter is not set", r);
+            return Q4B_BAD_ARGUMENT;
+        }
+    }
+    ++barrier->round;
+    Q4B_CUDA(launch_rank_barrier(barrier->counters, barrier->world, barrier->rank, barrier->world * barrier->round,
+                                 context->status_device, context->stream),
+             "rank barrier");
+    ++context->launches;
+    return Q4B_OK;
+}
+
+void q4b_barrier_free(q4b_context *context, q4b_barrier *barrier) {
+    if (barrier == nullptr) return;
+    if (context != nullptr) {
+        cudaSetDevice(context->device);
+        cudaStreamSynchronize(context->stream);
+    }
+    cudaFree(barrier->counter);
+    delete barrier;
 }
 
 int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, const uint32_t *rows, uint32_t count,

@@ -57,6 +57,8 @@ struct TcParams {
     uint32_t m_group;            // activation blocks walked together (see tc_tile_of)
     // stream-K (split != 0): the (tile, group) iterations are cut into equal contiguous ranges, one per CTA
     uint32_t split, iters_per_cta, iters_extra;
+    void *peer_y[kMaxSegments][kMaxPeers];  // the same output block in the other ranks' memory (null: none)
+    uint32_t peers;              // entries of peer_y in use (0 on a single GPU)
     float *workspace;            // [CTA][128][BN] fp32 partial tiles
     uint32_t *flags;             // [CTA] 1 while that CTA's partial tile waits to be added, else 0
     int y_dtype, residual_dtype;
@@ -492,6 +494,16 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     } else {
                         reinterpret_cast<__half *>(y_out)[at] = __float2half_rn(value);
                     }
+                    // column-parallel ranks: the slice goes straight into every rank's copy of y (plain peer stores)
+                    for (uint32_t r = 0; r < p.peers; ++r) {
+                        void *theirs = p.peer_y[segment][r];
+                        if (theirs == nullptr) continue;
+                        if (p.y_dtype == kF32) {
+                            reinterpret_cast<float *>(theirs)[at] = value;
+                        } else {
+                            reinterpret_cast<__half *>(theirs)[at] = __float2half_rn(value);
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -602,6 +614,10 @@ cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t st
     for (int s = args.segments; s <= kMaxSegments; ++s) p.block_begin[s] = blocks;
     p.segments = args.segments;
     p.up = args.up;
+    p.peers = args.peers;
+    for (int s = 0; s < kMaxSegments; ++s) {
+        for (int r = 0; r < kMaxPeers; ++r) p.peer_y[s][r] = (uint32_t)r < args.peers ? args.peer_y[s][r] : nullptr;
+    }
     p.residual = args.residual;
     p.status = args.status;
     p.ld_residual = args.ld_residual;
@@ -625,6 +641,45 @@ __global__ void convert_f32_to_f16_kernel(const float *in, __half *out, size_t c
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         out[i] = __float2half_rn(in[i]);
     }
+}
+
+struct RankBarrierParams {
+    uint32_t *counters[kMaxPeers];
+    uint32_t world, rank, expected;
+    uint32_t *status;
+};
+// Kernels of different GPUs wait for one another here, never two launches on one GPU.
+__global__ void rank_barrier_kernel(const RankBarrierParams p) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    // everything this GPU stored into the peers' memory before this launch is ordered before the adds
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (uint32_t r = 0; r < p.world; ++r) {
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.counters[r]), "r"(1u) : "memory");
+    }
+    const long long start = clock64();
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters[p.rank]) : "memory");
+        if ((int32_t)(seen - p.expected) >= 0) break;
+        if (clock64() - start > kTcWaitLimit) {
+            atomicExch(p.status, 0x91u);
+            break;
+        }
+        __nanosleep(100);
+    }
+}
+
+cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t expected,
+                                uint32_t *status, cudaStream_t stream) {
+    if (world == 0 || world > (uint32_t)kMaxPeers || rank >= world) return cudaErrorInvalidValue;
+    RankBarrierParams p = {};
+    for (uint32_t r = 0; r < world; ++r) p.counters[r] = counters[r];
+    p.world = world;
+    p.rank = rank;
+    p.expected = expected;
+    p.status = status;
+    rank_barrier_kernel<<<1, 32, 0, stream>>>(p);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream) {

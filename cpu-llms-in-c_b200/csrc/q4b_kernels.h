@@ -28,6 +28,7 @@ cudaError_t launch_synth_x(uint64_t seed, uint64_t stream_id, __half *x, uint64_
 
 // ---- q4b_gemv.cu ----
 constexpr int kMaxSegments = 4;
+constexpr int kMaxPeers = 8;
 struct GemvArgs {
     // up to kMaxSegments matrices that share x (same K); fused gate/up uses
     // segment 0 = gate, `up` = the second matrix, one output
@@ -63,7 +64,6 @@ cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *sc
                                 size_t *counter_bytes);
 
 // ---- q4b_decode.cu: job sequences in one persistent launch ----
-constexpr int kMaxPeers = 8;
 // One projection (a group of matrices sharing x, or a fused gate/up pair) as the
 // sequence kernel reads it from device memory.
 struct DecodeJob {
@@ -111,6 +111,9 @@ struct TcGemmArgs {
     int residual_dtype;
     uint32_t ld_residual;
     uint32_t *status;
+    // column-parallel ranks: where the same output block lives in the other ranks' memory (entries may be null)
+    void *peer_y[kMaxSegments][kMaxPeers];
+    uint32_t peers;
     // optional, for splitting tiles over CTAs when there are few: sm_count x 128 x 256 floats and sm_count
     // zero-initialised flags (left zero by every launch)
     float *workspace;
@@ -119,6 +122,10 @@ struct TcGemmArgs {
 };
 cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream);
 cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream);
+// One thread: system-scope fence, add 1 to every rank's counter, wait (bounded) until the own counter shows
+// `expected` arrivals; a wait that expires stores a code in *status.
+cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t expected,
+                                uint32_t *status, cudaStream_t stream);
 
 // ---- q4b_probe.cu ----
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,

@@ -90,6 +90,12 @@ def library() -> ctypes.CDLL:
         "q4b_matmul_host": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_gate_up_silu_host": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int,
                                          ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_context_push_outputs": (_int, [_vp, _u32, ctypes.POINTER(_vp), _int]),
+        "q4b_barrier_create": (_int, [_vp, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_barrier_counter": (_vp, [_vp]),
+        "q4b_barrier_set_peer": (_int, [_vp, _u32, _vp]),
+        "q4b_barrier_queue": (_int, [_vp, _vp] + err),
+        "q4b_barrier_free": (None, [_vp, _vp]),
         "q4b_embedding_lookup": (_int, [_vp, _vp, _vp, _u32, _vp, _int] + err),
         "q4b_sequence_create": (_int, [_vp, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_sequence_add_matmul": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, ctypes.POINTER(_vp),
@@ -399,6 +405,13 @@ class Q4Context:
         self._check(library().q4b_matmul_group(self.handle, handles, count, x_ptr, x_dtype, m_rows, outputs,
                                                y_dtype, strides, self._err, _ERR))
 
+    def push_outputs(self, world: int, peer_ptrs):
+        """peer_ptrs[s][r]: where segment s of the NEXT M > 16 call lives on rank r (None: skip)."""
+        count = len(peer_ptrs)
+        flat = (_vp * (count * world))(*[peer_ptrs[s][r] for s in range(count) for r in range(world)])
+        if library().q4b_context_push_outputs(self.handle, world, flat, count) != 0:
+            raise Q4Error(1, "invalid pushed outputs")
+
     def embedding_lookup(self, embedding: Q4Weight, rows_ptr: int, count: int, out_ptr: int, out_dtype: int = F16):
         self._check(library().q4b_embedding_lookup(self.handle, embedding.handle, rows_ptr, count, out_ptr, out_dtype,
                                                    self._err, _ERR))
@@ -462,3 +475,31 @@ class Q4Context:
         handle = _vp()
         self._check(library().q4b_graph_end(self.handle, ctypes.byref(handle), self._err, _ERR))
         return Q4Graph(self, handle.value)
+
+
+class Q4Barrier:
+    """All ranks of a node: 'what I queued so far is stored' (q4b_barrier_*)."""
+
+    def __init__(self, context: Q4Context, world: int, rank: int):
+        self.context = context
+        handle = _vp()
+        context._check(library().q4b_barrier_create(context.handle, world, rank, ctypes.byref(handle),
+                                                    context._err, _ERR))
+        self.handle = handle
+
+    @property
+    def counter(self) -> int:
+        return library().q4b_barrier_counter(self.handle)
+
+    def set_peer(self, peer_rank: int, pointer: int):
+        if library().q4b_barrier_set_peer(self.handle, peer_rank, pointer) != 0:
+            raise Q4Error(1, "invalid peer counter")
+
+    def queue(self):
+        self.context._check(library().q4b_barrier_queue(self.context.handle, self.handle, self.context._err, _ERR))
+
+    def free(self):
+        if self.handle:
+            library().q4b_barrier_free(self.context.handle, self.handle)
+            self.handle = None
+

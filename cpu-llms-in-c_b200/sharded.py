@@ -5,10 +5,12 @@ each rank owns its slice's tile stream, computes Y[:, n0:n1] from the full x and
 the slices are gathered so that every rank ends with the whole [M, N].
 
 Two gather paths:
-  * "push"  : (M <= 16) the whole pass is one decode sequence (q4b_decode.cu);
-              every epilogue stores its slice straight into every rank's copy of
-              y over NVLink and a job starts only when all ranks have published
-              the previous one -- no collective call per projection;
+  * "push"  : every epilogue stores its slice straight into every rank's copy of
+              y over NVLink -- no collective call per projection.  M <= 16: the
+              whole pass is one decode sequence (q4b_decode.cu) and a job starts
+              only when all ranks have published the previous one; M > 16: the
+              tensor-core GEMM pushes (q4b_context_push_outputs) and a one-thread
+              barrier kernel follows every projection group (q4b_barrier_queue);
   * "nccl"  : torch.distributed all_gather_into_tensor per gather point, queued
               on the context's stream (the baseline and the cross-check).
 With world == 1 neither runs.  torch is imported only when world > 1 (process
@@ -20,7 +22,7 @@ import ctypes
 
 import numpy as np
 
-from .host import F16, Q4Context, Q4Sequence, library
+from .host import F16, Q4Barrier, Q4Context, Q4Sequence, library
 from .layer import Q4Layer, slice_of
 
 
@@ -58,8 +60,11 @@ class ShardedLayerStack:
         self.h2d_bytes_per_step = self.x_layer_bytes * n_layers
         self.d2h_bytes_per_step = self.y_layer_bytes * n_layers
         self._torch = None
+        self.barrier = None
         if world > 1 and gather == "push" and m_rows <= 16:
             self._setup_push()
+        elif world > 1 and gather == "push":
+            self._setup_push_gemm()
         elif world > 1:
             import torch
             self._torch = torch
@@ -121,6 +126,48 @@ class ShardedLayerStack:
         ctx.sync()
         dist.barrier()  # every rank's counters are zero and mapped before anyone launches
 
+    def _setup_push_gemm(self):
+        """Full y on every rank, shared through IPC handles; a barrier between the ranks."""
+        ctx, dist = self.ctx, self.dist
+        self.y_all = ctx.alloc(self.y_layer_bytes * self.n_layers)
+        self.y_base = self.y_all.ptr
+        handles = [None] * self.world
+        dist.all_gather_object(handles, ctx.ipc_export(self.y_all.ptr))
+        self.peer_y = [self.y_base if r == self.rank else ctx.ipc_open(handles[r]) for r in range(self.world)]
+        self.barrier = Q4Barrier(ctx, self.world, self.rank)
+        counters = [None] * self.world
+        dist.all_gather_object(counters, ctx.ipc_export(self.barrier.counter))
+        self.peer_counters = []
+        for r in range(self.world):
+            if r != self.rank:
+                pointer = ctx.ipc_open(counters[r])
+                self.peer_counters.append(pointer)
+                self.barrier.set_peer(r, pointer)
+        ctx.sync()
+        dist.barrier()
+
+    def _queue_sharded_push_gemm(self):
+        """Every projection group: GEMM on this rank's slices, stored into all ranks' y; then the barrier."""
+        ctx = self.ctx
+        for index, layer in enumerate(self.layers):
+            x_ptrs = self._x_ptrs(index)
+            for kind, members in layer.launch_plan():
+                offsets = [index * self.y_layer_bytes + self.y_offsets[p.name] + layer.slices[p.name][0] * 2
+                           for p in members]
+                ctx.push_outputs(self.world, [[None if r == self.rank else self.peer_y[r] + offset
+                                               for r in range(self.world)] for offset in offsets])
+                x = x_ptrs[members[0].k]
+                if kind == "group":
+                    ctx.matmul_group([layer.weights[p.name][0] for p in members], x, F16, self.m,
+                                     [self.y_base + o for o in offsets], F16, [p.n for p in members])
+                elif kind == "fused":
+                    gate, up = layer.weights[members[0].name]
+                    ctx.gate_up_silu(gate, up, x, F16, self.m, self.y_base + offsets[0], F16, members[0].n)
+                else:
+                    ctx.matmul(layer.weights[members[0].name][0], x, F16, self.m, self.y_base + offsets[0], F16,
+                               members[0].n)
+                self.barrier.queue()
+
     def _pinned(self, nbytes: int) -> int:
         pointer = ctypes.c_void_p()
         self.ctx._check(library().q4b_alloc_host(self.ctx.handle, nbytes, ctypes.byref(pointer), self.ctx._err, 512))
@@ -161,6 +208,9 @@ class ShardedLayerStack:
         """One pass over all layers, queued on the context stream."""
         if self.world > 1 and self.gather == "nccl":
             self._queue_sharded_nccl()
+            return
+        if self.barrier is not None:
+            self._queue_sharded_push_gemm()
             return
         if self.mode == "sequence":
             if self.sequence is None:
@@ -232,6 +282,8 @@ class ShardedLayerStack:
             self.dist.barrier()  # nobody stores into a peer that is about to unmap
             for pointer in [p for r, p in enumerate(self.peer_y) if r != self.rank] + self.peer_counters:
                 self.ctx.ipc_close(pointer)
+            if self.barrier is not None:
+                self.barrier.free()
         for layer in self.layers:
             layer.free()
         if self.graph is not None:

@@ -29,12 +29,10 @@ def main():
     layer_set = q4b.LAYER_SMALL if len(sys.argv) < 2 or sys.argv[1] == "small" else q4b.LAYER_27B
     layers = 3 if layer_set is q4b.LAYER_SMALL else 1
     ctx = q4b.Q4Context(local)
-    # M = 64 takes the tensor-core GEMM on every rank's slice; its gather is the NCCL one
-    sizes = (1, 4, 64) if layer_set is q4b.LAYER_SMALL else (1, 4)
+    # M = 64 and 300 take the tensor-core GEMM on every rank's slice
+    sizes = (1, 4, 64, 300) if layer_set is q4b.LAYER_SMALL else (1, 4)
     for gather in ("push", "nccl"):
         for m in sizes:
-            if m > 16 and gather == "push":
-                continue
             stack = sharded.ShardedLayerStack(ctx, layer_set, layers, m, rank, world, dist, gather=gather)
             assert stack.gather == gather
             for _ in range(3):
