@@ -31,11 +31,11 @@ namespace q4b {
 
 namespace {
 
-// ring stages (one quantisation group each): as many as the shared memory holds next to the fused epilogue's
-// exchange buffer -- the X tiles come from L2 and their latency has to be covered by tiles in flight
+// ring stages (one quantisation group each): as many as the shared memory holds next to the epilogue's
+// staging buffer -- the X tiles come from L2 and their latency has to be covered by tiles in flight
 template <int BN, bool FUSED>
 struct TcStages {
-    static constexpr int value = BN == 256 ? (FUSED ? 5 : 6) : 8;
+    static constexpr int value = BN == 256 ? 5 : 8;  // next to the 32 KB output staging buffer
 };
 constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
 constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
@@ -210,7 +210,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     uint8_t *wbuf = base + kTcStages * kXBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wbuf + kTcStages * kWBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kTcStages + 2 * kTcSlots + 2);
-    float *exchange = reinterpret_cast<float *>(tmem_slot + 4);  // fused epilogue: [warpgroups][2][16][64]
+    float *exchange = reinterpret_cast<float *>(tmem_slot + 4);  // epilogue staging: [warpgroups][16][128]
     const uint32_t full0 = tc_smem_u32(bars), empty0 = full0 + 8 * kTcStages;
     const uint32_t a_full0 = empty0 + 8 * kTcStages, a_free0 = a_full0 + 8 * kTcSlots;
     const uint32_t d_full = a_free0 + 8 * kTcSlots, d_free = d_full + 8;
@@ -389,11 +389,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             // ---- epilogue: this warp's 32 rows x half of the columns ----
             if (!tc_wait(d_full, tile_iter & 1)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t n = FUSED ? nb * 64 + (row & 63) : nb * 128 + row;  // output feature of this thread
-            const bool row_valid = n < p.w[segment].rows;
             void *y_out = p.y[segment];
             const uint32_t ldy = p.ldy[segment];
-            float *swap = exchange + wg * (2 * 16 * 64);
+            float *swap = exchange + wg * (16 * 128);   // this warpgroup's 8 KB of the output staging buffer
             constexpr uint32_t kColumnsPerGroup = BN / kTcWarpgroups;
             if (g0 > 0) {
                 // ---- a later part of a split tile: leave the partial sums for the CTA that holds the first groups ----
@@ -444,11 +442,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(kTcWarpgroups * 128) : "memory");
             }
-            uint32_t chunk = 0;
 #pragma unroll 1
-            for (uint32_t c = wg * kColumnsPerGroup; c < (wg + 1) * kColumnsPerGroup; c += 16, ++chunk) {
+            for (uint32_t c = wg * kColumnsPerGroup; c < (wg + 1) * kColumnsPerGroup; c += 16) {
                 uint32_t d0[16];
-                float other[16];
                 tc_load_16(tmem_d + c + lane_field, d0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 for (uint32_t q = 0; q < partial_count; ++q) {  // partial tiles in CTA order
@@ -462,49 +458,102 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         d0[j + 3] = __float_as_uint(__uint_as_float(d0[j + 3]) + v.w);
                     }
                 }
+                // The chunk (16 activation rows x this warpgroup's output features) goes through shared memory
+                // transposed, so that the stores are 32 or 64 contiguous bytes per thread and whole 128/256-byte
+                // rows per eight threads -- for the peers' copies over NVLink as much as for the own.
+                constexpr uint32_t kFeatures = FUSED ? 64 : 128;   // output features of the tile
+                float *tile_out = swap;                             // [16][kFeatures]
                 if (FUSED) {
                     // rows 64..127 hold `up` of the feature whose `gate` sits 64 rows above
-                    float *buffer = swap + (chunk & 1) * (16 * 64);
                     if (row >= 64) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) buffer[j * 64 + (row - 64)] = __uint_as_float(d0[j]);
+                        for (int j = 0; j < 16; ++j) tile_out[j * kFeatures + (row - 64)] = __uint_as_float(d0[j]);
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");
-                    if (row >= 64) continue;
+                    if (row < 64) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) other[j] = buffer[j * 64 + row];
+                        for (int j = 0; j < 16; ++j) {
+                            // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
+                            const float gate = __uint_as_float(d0[j]);
+                            tile_out[j * kFeatures + row] = (gate / (1.0f + __expf(-gate))) * tile_out[j * kFeatures + row];
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) tile_out[j * kFeatures + row] = __uint_as_float(d0[j]);
                 }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");
+                {
+                    const uint32_t unit = row;                          // 0..127: (activation row j, span of 16 features)
+                    constexpr uint32_t kSpans = kFeatures / 16;
+                    const uint32_t j = unit / kSpans, span = unit % kSpans;
                     const uint32_t m = mb * BN + c + j;
-                    if (!row_valid || m >= p.m_rows) continue;
-                    float value = __uint_as_float(d0[j]);
-                    if (FUSED) {
-                        // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
-                        value = (value / (1.0f + __expf(-value))) * other[j];
-                    }
-                    if (p.residual != nullptr && segment == 0) {
-                        const size_t at = (size_t)m * p.ld_residual + n;
-                        value += p.residual_dtype == kF32 ? reinterpret_cast<const float *>(p.residual)[at]
-                                                          : __half2float(reinterpret_cast<const __half *>(p.residual)[at]);
-                    }
-                    const size_t at = (size_t)m * ldy + n;
-                    if (p.y_dtype == kF32) {
-                        reinterpret_cast<float *>(y_out)[at] = value;
-                    } else {
-                        reinterpret_cast<__half *>(y_out)[at] = __float2half_rn(value);
-                    }
-                    // column-parallel ranks: the slice goes straight into every rank's copy of y (plain peer stores)
-                    for (uint32_t r = 0; r < p.peers; ++r) {
-                        void *theirs = p.peer_y[segment][r];
-                        if (theirs == nullptr) continue;
-                        if (p.y_dtype == kF32) {
-                            reinterpret_cast<float *>(theirs)[at] = value;
+                    const uint32_t n0 = (FUSED ? nb * 64 : nb * 128) + span * 16;
+                    const uint32_t rows_total = p.w[segment].rows;
+                    if (unit < 16 * kSpans && m < p.m_rows && n0 < rows_total) {
+                        float v[16];
+#pragma unroll
+                        for (int q = 0; q < 16; q += 4) {
+                            const float4 f = *reinterpret_cast<const float4 *>(tile_out + j * kFeatures + span * 16 + q);
+                            v[q] = f.x; v[q + 1] = f.y; v[q + 2] = f.z; v[q + 3] = f.w;
+                        }
+                        const uint32_t valid = min(16u, rows_total - n0);
+                        if (p.residual != nullptr && segment == 0) {
+                            const size_t at = (size_t)m * p.ld_residual + n0;
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) {
+                                if ((uint32_t)q < valid) {
+                                    v[q] += p.residual_dtype == kF32
+                                                ? reinterpret_cast<const float *>(p.residual)[at + q]
+                                                : __half2float(reinterpret_cast<const __half *>(p.residual)[at + q]);
+                                }
+                            }
+                        }
+                        const size_t at = (size_t)m * ldy + n0;
+                        const bool f32 = p.y_dtype == kF32;
+                        const bool wide = valid == 16 && ((at * (f32 ? 4 : 2)) & 15u) == 0;
+                        uint4 packed[4];
+                        if (f32) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                packed[q] = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                                                       __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+                            }
                         } else {
-                            reinterpret_cast<__half *>(theirs)[at] = __float2half_rn(value);
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                __half2 h[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+                                packed[q] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
+                                                       *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
+                            }
+                        }
+                        // own copy first, then every peer's (column-parallel ranks: plain stores over NVLink)
+                        for (uint32_t r = 0; r <= p.peers; ++r) {
+                            void *destination = r == 0 ? y_out : p.peer_y[segment][r - 1];
+                            if (destination == nullptr) continue;
+                            if (wide) {
+                                uint4 *out = reinterpret_cast<uint4 *>(static_cast<uint8_t *>(destination) + at * (f32 ? 4 : 2));
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    if (f32 || q < 2) out[q] = packed[q];
+                                }
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 16; ++q) {
+                                    if ((uint32_t)q >= valid) continue;
+                                    if (f32) {
+                                        reinterpret_cast<float *>(destination)[at + q] = v[q];
+                                    } else {
+                                        reinterpret_cast<__half *>(destination)[at + q] = __float2half_rn(v[q]);
+                                    }
+                                }
+                            }
                         }
                     }
                 }
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");  // the buffer is free for the next chunk
             }
             tc_fence_before();
             __syncwarp();
@@ -560,7 +609,7 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     const uint32_t tiles = p.n_blocks * p.m_blocks;
     constexpr int kTcStages = TcStages<BN, FUSED>::value;
     const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
-                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + (FUSED ? kTcWarpgroups * 2 * 16 * 64 * 4 : 0) + 1024;
+                              (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + kTcWarpgroups * 16 * 128 * 4 + 1024;
     auto kernel = tc_gemm_kernel<BN, FUSED>;
     static bool configured = false;
     if (!configured) {
