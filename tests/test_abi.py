@@ -38,6 +38,16 @@ def test_null_arguments_are_rejected_without_touching_a_device(q4b):
     assert b"NULL" in err.value
     assert lib.q4b_matmul(None, None, None, 0, 1, None, 0, 0, None, -1, 0, err, 256) == 1
     assert lib.q4b_graph_launch(None, None, err, 256) == 1
+    # the multi-rank, image and layer entry points refuse missing objects the same way
+    assert lib.q4b_context_push_outputs(None, 2, None, 1) == 1
+    assert lib.q4b_barrier_set_peer(None, 0, None) == 1
+    assert lib.q4b_barrier_queue(None, None, err, 256) == 1
+    assert lib.q4b_image_describe(None, None) == 1
+    assert lib.q4b_image_weight(None, None, 0, 0, 1, None, err, 256) == 1
+    assert lib.q4b_layer_wrap(None, None, None, 0, 1, None) == 1
+    assert lib.q4b_layer_encode_mlp(None, None, None, 1, None, 0, None, 0, None, 0, err, 256) == 1
+    assert lib.q4b_embedding_lookup(None, None, None, 0, None, 0, err, 256) == 1
+    assert lib.q4b_sequence_launch(None, None, err, 256) == 1
 
 
 def test_algorithmic_bytes_match_the_stated_anchors(q4b):
