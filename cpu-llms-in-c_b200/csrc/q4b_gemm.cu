@@ -31,12 +31,13 @@ namespace q4b {
 
 namespace {
 
-// ring stages (one quantisation group each): as many as the shared memory holds next to the epilogue's
-// staging buffer -- the X tiles come from L2 and their latency has to be covered by tiles in flight
+// ring stages (one quantisation group each); a multiple of the number of warpgroups, see the dequantisation loop
 template <int BN, bool FUSED>
 struct TcStages {
-    static constexpr int value = BN == 256 ? 5 : 8;  // next to the 32 KB output staging buffer
+    static constexpr int value = BN == 256 ? 4 : 8;
 };
+static_assert(TcStages<256, false>::value % kTcWarpgroups == 0 && TcStages<128, false>::value % kTcWarpgroups == 0,
+              "a warpgroup must meet every fill of the stages it uses");
 constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
 constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
 constexpr int kTcThreads = 64 + kTcWarpgroups * 128;  // warp 0 producer, warp 1 MMA, then the warpgroups
@@ -346,13 +347,14 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t nb = nb_all - p.block_begin[segment];
             for (uint32_t g = g0; g < g1 && ok; ++g, ++it) {
                 const uint32_t s = it % kTcStages;
-                // Every warpgroup observes every phase of every stage barrier, also for the groups it leaves to
-                // the others: a parity wait that skips a phase (a warpgroup returns to a stage only every third
-                // fill when the ring has six stages) would be satisfied by the phase before last.
-                if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                 for (int once = 0; once < 1; ++once, ++unit) {
                     if (unit % kTcWarpgroups != wg) continue;  // the warpgroups take groups in turn
                     const uint32_t a = unit % kTcSlots;
+                    // A warpgroup waits only for its own groups' stages.  That is sound because the number of
+                    // stages is a multiple of the number of warpgroups: it then meets every fill of the stages it
+                    // uses (a parity wait that skips a fill is satisfied by the fill before last), and a stage it is
+                    // still waiting for cannot be refilled, since the MMA that frees it needs this warpgroup's A tile.
+                    if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
                     const uint8_t *tile_bytes = wbuf + s * kWBytes + tile_offset_bytes;
                     const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
                     const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
