@@ -36,10 +36,10 @@ template <int BN, bool FUSED>
 struct TcStages {
     static constexpr int value = BN == 256 ? 4 : 8;
 };
-static_assert(TcStages<256, false>::value % kTcWarpgroups == 0 && TcStages<128, false>::value % kTcWarpgroups == 0,
-              "a warpgroup must meet every fill of the stages it uses");
 constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
 constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
+static_assert(TcStages<256, false>::value % kTcWarpgroups == 0 && TcStages<128, false>::value % kTcWarpgroups == 0,
+              "a warpgroup must meet every fill of the stages it uses");
 constexpr int kTcThreads = 64 + kTcWarpgroups * 128;  // warp 0 producer, warp 1 MMA, then the warpgroups
 constexpr long long kTcWaitLimit = 4000000000ll;
 
