@@ -9,8 +9,9 @@
 // embedded eight-row references the packer stored for self-checks.  The file
 // layouts are the reference's (qwen38_m3_image.h:26-94, version 3, magic
 // "Q38M3Q4\0"; qwen38_m3_attention_image.h:21-72, version 1, magic "Q38M3ATT";
-// qwen38_m3_global_image.h:14-38, version 1, magic "Q38M3GLB"); they are restated
-// here as field offsets, pinned by a test against the offsets the reference's own
+// qwen38_m3_global_image.h:14-38, version 1, magic "Q38M3GLB"; qwen38_m3_mtp_image.h:
+// 21-51, version 1, magic "Q38M3MTP", validated as qwen38_m3_model_mtp_open does,
+// qwen38_m3_decode.m:2365-2380); they are restated here as field offsets, pinned by a test against the offsets the reference's own
 // headers give.
 //
 // On unified memory the reference wraps the mapping in no-copy buffers; on a B200
@@ -51,6 +52,7 @@ struct Layout {
     uint32_t source_sha256, mlp_source_sha256;            // 65-byte strings (0 = absent)
     uint32_t gate_up_reference, mlp_reference, layer_reference;              // float[8] (0 = absent)
     uint32_t gate_up_reference_count, mlp_reference_count, layer_reference_count;  // uint32 (0 = absent)
+    uint32_t constants_index[3];  // uint64 indices into the constants (0 = absent)
 };
 
 // qwen38_m3_image.h:26-94
@@ -87,6 +89,29 @@ const Layout kGlobal = {
     0, 0, 0,
     0, 0, 0,
 };
+
+// qwen38_m3_mtp_image.h:21-51: the fused fc projection [hidden, 2 x hidden] and three norm vectors; the file
+// ends with the constants
+const Layout kMtp = {
+    {'Q', '3', '8', 'M', '3', 'M', 'T', 'P'}, 1, 1,
+    0, 16, 20, 28, 32,
+    {{40, 48, 56, 64}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}},
+    {{20, 24}, {0, 0}, {0, 0}, {0, 0}, {0, 0}},
+    72, 80, 0xffffffffu,
+    112, 0,
+    0, 0, 0,
+    0, 0, 0,
+    {88, 96, 104},
+};
+
+const Layout &layout_of(int kind) {
+    return kind == Q4B_IMAGE_DELTA ? kDelta : kind == Q4B_IMAGE_ATTENTION ? kAttention
+           : kind == Q4B_IMAGE_GLOBAL ? kGlobal : kMtp;
+}
+const char *name_of(int kind) {
+    return kind == Q4B_IMAGE_DELTA ? "DeltaNet" : kind == Q4B_IMAGE_ATTENTION ? "attention"
+           : kind == Q4B_IMAGE_GLOBAL ? "global" : "MTP extras";
+}
 
 void set_message(char *message, size_t capacity, const char *format, ...) {
     if (message == nullptr || capacity == 0) return;
@@ -125,12 +150,13 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
                    const char *const *allowed_sha256, int allowed_count, q4b_image **image,
                    char *error_message, size_t error_capacity) {
     if (path == nullptr || image == nullptr ||
-        (kind != Q4B_IMAGE_DELTA && kind != Q4B_IMAGE_ATTENTION && kind != Q4B_IMAGE_GLOBAL)) {
+        (kind != Q4B_IMAGE_DELTA && kind != Q4B_IMAGE_ATTENTION && kind != Q4B_IMAGE_GLOBAL &&
+         kind != Q4B_IMAGE_MTP)) {
         set_message(error_message, error_capacity, "path, kind or result pointer missing");
         return Q4B_BAD_ARGUMENT;
     }
     *image = nullptr;
-    const Layout &layout = kind == Q4B_IMAGE_DELTA ? kDelta : kind == Q4B_IMAGE_ATTENTION ? kAttention : kGlobal;
+    const Layout &layout = layout_of(kind);
     // map_file (qwen38_m3_decode.m:374-396): a regular file of at least one page, mapped read-only
     const int file = open(path, O_RDONLY);
     struct stat status;
@@ -179,7 +205,7 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
     else if (kind == Q4B_IMAGE_ATTENTION && layer_index % 4 != 3 && layer_index != kMtpLayerIndex)
         problem = "only layers 3 mod 4 (and the MTP layer) are attention layers";
     else if (info.hidden_size == 0 || info.hidden_size % 64 != 0 || info.intermediate_size == 0 ||
-             (kind != Q4B_IMAGE_GLOBAL && info.intermediate_size % 64 != 0))
+             ((kind == Q4B_IMAGE_DELTA || kind == Q4B_IMAGE_ATTENTION) && info.intermediate_size % 64 != 0))
         problem = "hidden or intermediate size is not a positive multiple of 64";
 
     for (int m = 0; m < (int)layout.matrices && problem == nullptr; ++m) {
@@ -218,7 +244,19 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
             problem = last == 0xffffffffu ? "the file does not end with the constants"
                                           : "the file does not end with the output metadata";
     }
-    if (problem == nullptr && check_27b_shapes && kind == Q4B_IMAGE_GLOBAL) {
+    for (int i = 0; i < 3 && problem == nullptr && layout.constants_index[0] != 0; ++i) {
+        // the three norm vectors of the MTP image, hidden_size floats each, by index into the constants
+        info.constants_index[i] = read_u64(h, layout.constants_index[i]);
+        if (info.constants_index[i] > info.constants_f32_count ||
+            info.hidden_size > info.constants_f32_count - info.constants_index[i])
+            problem = "a norm vector lies outside the constants";
+    }
+    if (problem == nullptr && check_27b_shapes && kind == Q4B_IMAGE_MTP) {
+        // qwen38_m3_model_mtp_open (:2365-2375)
+        if (info.hidden_size != 5120 || info.rows[0] != 5120 || info.groups[0] != 160 ||
+            info.constants_f32_count != 3 * 5120)
+            problem = "not the 27B fc projection and norm vectors";
+    } else if (problem == nullptr && check_27b_shapes && kind == Q4B_IMAGE_GLOBAL) {
         // validate_global_header (:447-460)
         if (info.intermediate_size != 248320 || info.hidden_size != 5120 || info.constants_f32_count != 5120)
             problem = "not the 27B vocabulary and hidden size";
@@ -250,8 +288,7 @@ int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_2
     }
     if (problem != nullptr) {
         set_message(error_message, error_capacity, "invalid %s image at layer %u: %s",
-                    kind == Q4B_IMAGE_DELTA ? "DeltaNet" : kind == Q4B_IMAGE_ATTENTION ? "attention" : "global",
-                    layer_index, problem);
+                    name_of(kind), layer_index, problem);
         q4b_image_close(result);
         return Q4B_LOAD_FAILURE;
     }

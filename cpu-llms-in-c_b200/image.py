@@ -4,7 +4,9 @@ the host-side view of the library's loader.
 File layouts (little-endian, one 4096-byte header, page-aligned segments):
   * DeltaNet layer  -- models/qwen3.8-27b/targets/apple-m3-pro/qwen38_m3_image.h:26-94,
     magic "Q38M3Q4\\0", version 3;
-  * attention layer -- qwen38_m3_attention_image.h:21-72, magic "Q38M3ATT", version 1.
+  * attention layer -- qwen38_m3_attention_image.h:21-72, magic "Q38M3ATT", version 1;
+  * global          -- qwen38_m3_global_image.h:14-38, magic "Q38M3GLB", version 1;
+  * MTP extras      -- qwen38_m3_mtp_image.h:21-51, magic "Q38M3MTP", version 1.
 The packer that writes the real files is compiler/qwen3.8-27b/apple-m3-pro/
 qwen38_m3_pack.c; the checkpoint it reads is not available here, so tests and
 benchmarks build images from seeded matrices with `write_layer_image`.
@@ -19,8 +21,9 @@ import numpy as np
 from .host import Q4Context, Q4Error, Q4Weight, _vp, library
 
 PAGE = 4096
-DELTA, ATTENTION, GLOBAL = 0, 1, 2
+DELTA, ATTENTION, GLOBAL, MTP = 0, 1, 2, 3
 EMBEDDING, LM_HEAD = 0, 1
+FC = 0
 GATE, UP, DOWN, INPUT, OUTPUT = range(5)
 MATRIX_NAMES = ("gate", "up", "down", "input", "output")
 
@@ -71,9 +74,17 @@ _GLOBAL_FIELDS = {
     "constants_offset": (104, "<Q"), "constants_bytes": (112, "<Q"),
     "embedding_source_sha256": (120, "65s"), "lm_head_source_sha256": (185, "65s"),
 }
-FIELDS = {DELTA: _DELTA_FIELDS, ATTENTION: _ATTENTION_FIELDS, GLOBAL: _GLOBAL_FIELDS}
-MAGIC = {DELTA: b"Q38M3Q4\0", ATTENTION: b"Q38M3ATT", GLOBAL: b"Q38M3GLB"}
-VERSION = {DELTA: 3, ATTENTION: 1, GLOBAL: 1}
+_MTP_FIELDS = {
+    "version": (8, "<I"), "header_bytes": (12, "<I"), "hidden_size": (16, "<I"), "fc_rows": (20, "<I"),
+    "fc_groups_per_row": (24, "<I"), "group_size": (28, "<I"), "constants_f32_count": (32, "<I"),
+    "fc_quants_offset": (40, "<Q"), "fc_quants_bytes": (48, "<Q"), "fc_metadata_offset": (56, "<Q"),
+    "fc_metadata_bytes": (64, "<Q"), "constants_offset": (72, "<Q"), "constants_bytes": (80, "<Q"),
+    "embedding_norm_constants_index": (88, "<Q"), "hidden_norm_constants_index": (96, "<Q"),
+    "final_norm_constants_index": (104, "<Q"), "source_sha256": (112, "65s"),
+}
+FIELDS = {DELTA: _DELTA_FIELDS, ATTENTION: _ATTENTION_FIELDS, GLOBAL: _GLOBAL_FIELDS, MTP: _MTP_FIELDS}
+MAGIC = {DELTA: b"Q38M3Q4\0", ATTENTION: b"Q38M3ATT", GLOBAL: b"Q38M3GLB", MTP: b"Q38M3MTP"}
+VERSION = {DELTA: 3, ATTENTION: 1, GLOBAL: 1, MTP: 1}
 _SEGMENT_PREFIX = {DELTA: ("gate", "up", "down", "delta_input", "delta_output"),
                    ATTENTION: ("gate", "up", "down", "attention_input", "attention_output")}
 
@@ -179,6 +190,39 @@ def write_global_image(path: str, hidden_size: int, embedding, lm_head, constant
     return values
 
 
+def write_mtp_image(path: str, hidden_size: int, fc, embedding_norm, hidden_norm, final_norm,
+                    source_sha256: str = "0" * 64, extra_fields: dict | None = None) -> dict:
+    """Write an MTP extras image (qwen38_m3_mtp_image.h): the fused fc projection (quants uint8
+    [hidden, hidden], meta uint16 [hidden, 2 * hidden / 64, 2]) and the three norm vectors, which
+    become the constants (embedding norm, hidden norm, final norm) and end the file."""
+    fields = FIELDS[MTP]
+    constants = np.concatenate([np.ascontiguousarray(v, np.float32).ravel()
+                                for v in (embedding_norm, hidden_norm, final_norm)])
+    quants, meta = fc
+    header = bytearray(PAGE)
+    header[0:8] = MAGIC[MTP]
+    values: dict = {"version": VERSION[MTP], "header_bytes": PAGE, "hidden_size": hidden_size,
+                    "fc_rows": int(quants.shape[0]), "fc_groups_per_row": int(meta.shape[1]), "group_size": 64,
+                    "constants_f32_count": int(constants.size), "embedding_norm_constants_index": 0,
+                    "hidden_norm_constants_index": hidden_size, "final_norm_constants_index": 2 * hidden_size,
+                    "source_sha256": source_sha256.encode()}
+    body = bytearray()
+    for prefix, data in (("fc_quants", np.ascontiguousarray(quants, np.uint8).tobytes()),
+                         ("fc_metadata", np.ascontiguousarray(meta, np.uint16).tobytes()),
+                         ("constants", constants.tobytes())):
+        padded = _padded(data) if prefix != "constants" else data  # the runtime wants offset + bytes == file length
+        values[f"{prefix}_offset"], values[f"{prefix}_bytes"] = PAGE + len(body), len(padded)
+        body.extend(padded)
+    values.update(extra_fields or {})
+    for name, value in values.items():
+        offset, fmt = fields[name]
+        struct.pack_into(fmt, header, offset, value)
+    with open(path, "wb") as handle:
+        handle.write(header)
+        handle.write(body)
+    return values
+
+
 class _Info(ctypes.Structure):
     _fields_ = [("kind", ctypes.c_uint32), ("version", ctypes.c_uint32), ("layer_index", ctypes.c_uint32),
                 ("hidden_size", ctypes.c_uint32), ("intermediate_size", ctypes.c_uint32),
@@ -186,7 +230,7 @@ class _Info(ctypes.Structure):
                 ("constants_f32_count", ctypes.c_uint32), ("reference_counts", ctypes.c_uint32 * 3),
                 ("gate_up_reference_first_8", ctypes.c_float * 8), ("mlp_reference_first_8", ctypes.c_float * 8),
                 ("layer_reference_first_8", ctypes.c_float * 8), ("source_sha256", ctypes.c_char * 65),
-                ("mlp_source_sha256", ctypes.c_char * 65)]
+                ("mlp_source_sha256", ctypes.c_char * 65), ("constants_index", ctypes.c_uint64 * 3)]
 
 
 class Q4Image:

@@ -283,12 +283,19 @@ int q4b_ipc_close(q4b_context *context, void *peer_pointer);
  * digests the caller accepts, the role of pinned_sha.  Failures return
  * Q4B_LOAD_FAILURE with a message.  No GPU is needed to open an image. */
 typedef struct q4b_image q4b_image;
-enum { Q4B_IMAGE_DELTA = 0, Q4B_IMAGE_ATTENTION = 1, Q4B_IMAGE_GLOBAL = 2 };
+enum { Q4B_IMAGE_DELTA = 0, Q4B_IMAGE_ATTENTION = 1, Q4B_IMAGE_GLOBAL = 2, Q4B_IMAGE_MTP = 3 };
 enum { Q4B_MATRIX_GATE = 0, Q4B_MATRIX_UP = 1, Q4B_MATRIX_DOWN = 2, Q4B_MATRIX_INPUT = 3, Q4B_MATRIX_OUTPUT = 4 };
 /* the global image (qwen38_m3_global_image.h:14-38, magic "Q38M3GLB", version 1; load_global, :462-498) holds two
  * [vocabulary, hidden] matrices; its info reports the vocabulary as intermediate_size, the embedding's source
  * digest as source_sha256 and the lm_head's as mlp_source_sha256; layer_index is ignored */
 enum { Q4B_MATRIX_EMBEDDING = 0, Q4B_MATRIX_LM_HEAD = 1 };
+/* the MTP extras image (qwen38_m3_mtp_image.h:21-51, magic "Q38M3MTP", version 1; validated as
+ * qwen38_m3_model_mtp_open does, qwen38_m3_decode.m:2365-2380) holds one matrix, the fused fc projection
+ * [hidden, 2 x hidden] that encode_mtp_pass runs through encode_prefill_gemm_f16 (:1818-1821), and three norm
+ * vectors of hidden_size floats inside its constants: info.constants_index gives where the embedding norm, the
+ * hidden norm and the final norm begin; intermediate_size repeats the fc rows; layer_index is ignored.  The MTP
+ * transformer layer itself is an attention image with layer index 64. */
+enum { Q4B_MATRIX_FC = 0 };
 typedef struct {
     uint32_t kind, version, layer_index, hidden_size, intermediate_size, group_size;
     uint32_t rows[5], groups[5];          /* by Q4B_MATRIX_*: output rows and K/64 */
@@ -298,6 +305,7 @@ typedef struct {
     float mlp_reference_first_8[8];       /* whole MLP + residual, rows 0..7 */
     float layer_reference_first_8[8];
     char source_sha256[65], mlp_source_sha256[65];
+    uint64_t constants_index[3];          /* MTP extras only: embedding norm, hidden norm, final norm */
 } q4b_image_info;
 int q4b_image_open(const char *path, int kind, uint32_t layer_index, int check_27b_shapes,
                    const char *const *allowed_sha256, int allowed_count, q4b_image **image,

@@ -18,6 +18,7 @@ HEADERS = {
     "delta": ("qwen38_m3_image.h", "qwen38_m3_image_header"),
     "attention": ("qwen38_m3_attention_image.h", "qwen38_m3_attention_image_header"),
     "global": ("qwen38_m3_global_image.h", "qwen38_m3_global_image_header"),
+    "mtp": ("qwen38_m3_mtp_image.h", "qwen38_m3_mtp_image_header"),
 }
 
 

@@ -172,3 +172,31 @@ def test_embedding_lookup_from_a_global_image(q4b, orc, ctx, image, tmp_path):
     for weight in (whole, head):
         weight.free()
     opened.close()
+
+
+@pytest.mark.parametrize("batch", [1, 4, 40])
+def test_fc_projection_from_an_mtp_extras_image(q4b, orc, ctx, image, tmp_path, batch):
+    """encode_mtp_pass feeds concat[embedding norm, hidden norm] (2 x hidden) through the fc matrix
+    (qwen38_m3_decode.m:1818-1821); here by row slice over two ranks as well."""
+    hidden = 1024
+    fc = orc.synth_weight(13, 0, hidden, 2 * hidden // 64)
+    path = str(tmp_path / "mtp.img")
+    image.write_mtp_image(path, hidden, fc, *[np.ones(hidden, np.float32)] * 3)
+    opened = image.Q4Image(path, image.MTP, 0)
+    x = orc.synth_x(13, batch, batch, 2 * hidden)
+    _, want = orc.matmul(*fc, 2 * hidden // 64, x, want32=False)
+    dx = ctx.to_device(x)
+    whole = opened.weight(ctx, image.FC)
+    dy = ctx.alloc(batch * hidden * 4)
+    ctx.matmul(whole, dx.ptr, q4b.F16, batch, dy.ptr, q4b.F32)
+    assert_close(dy.download(np.float32, (batch, hidden)), want, "fc from the MTP extras image")
+    whole.free()
+    if batch <= 16:
+        for rank in range(2):
+            begin, count = image.Q4LayerMatmuls.slice_of(hidden, rank, 2)
+            shard = opened.weight(ctx, image.FC, begin, count)
+            part = ctx.alloc(batch * count * 4)
+            ctx.matmul(shard, dx.ptr, q4b.F16, batch, part.ptr, q4b.F32)
+            assert_close(part.download(np.float32, (batch, count)), want[:, begin:begin + count], f"fc rows of rank {rank}")
+            shard.free()
+    opened.close()

@@ -27,7 +27,8 @@ def small_matrices(orc, hidden=256, intermediate=512, input_rows=320, output_gro
 
 def test_restated_layouts_match_the_reference_headers(image):
     golden = json.load(open(GOLDEN))
-    for kind, key in ((image.DELTA, "delta"), (image.ATTENTION, "attention"), (image.GLOBAL, "global")):
+    for kind, key in ((image.DELTA, "delta"), (image.ATTENTION, "attention"), (image.GLOBAL, "global"),
+                      (image.MTP, "mtp")):
         assert golden[key]["sizeof"][0] == image.PAGE
         assert golden[key]["magic"] == [0, 8]
         for name, (offset, fmt) in image.FIELDS[kind].items():
@@ -156,4 +157,45 @@ def test_global_image_opens_and_is_validated(image, orc, tmp_path):
         handle.write(data + b"\0" * 4096)
     with pytest.raises(image.Q4Error) as tail:
         image.Q4Image(broken, image.GLOBAL, 0)
+    assert "does not end with the constants" in tail.value.message
+
+
+def test_mtp_extras_image_opens_and_is_validated(image, orc, tmp_path):
+    """The rules of qwen38_m3_model_mtp_open (qwen38_m3_decode.m:2365-2380) on a small synthetic image."""
+    hidden = 256
+    fc = orc.synth_weight(9, 0, hidden, 2 * hidden // 64)
+    norms = [np.full(hidden, value, dtype=np.float32) for value in (1.0, 2.0, 3.0)]
+    path = str(tmp_path / "mtp.img")
+    image.write_mtp_image(path, hidden, fc, *norms, source_sha256="cc" * 32)
+    opened = image.Q4Image(path, image.MTP, 0)
+    info = opened.info
+    assert (info.kind, info.hidden_size, info.constants_f32_count) == (image.MTP, hidden, 3 * hidden)
+    assert opened.shape(image.FC) == (hidden, 8)
+    assert list(info.constants_index) == [0, hidden, 2 * hidden]
+    assert info.source_sha256 == b"cc" * 32
+    constants = opened.constants()
+    for index, value in zip(info.constants_index, (1.0, 2.0, 3.0)):
+        assert np.all(constants[index:index + hidden] == value)
+    opened.close()
+    image.Q4Image(path, image.MTP, 0, allowed_sha256=["cc" * 32]).close()
+    with pytest.raises(image.Q4Error) as digest:
+        image.Q4Image(path, image.MTP, 0, allowed_sha256=["dd" * 32])
+    assert digest.value.status == 3 and "digest" in digest.value.message
+    with pytest.raises(image.Q4Error) as strict:
+        image.Q4Image(path, image.MTP, 0, check_27b_shapes=True)
+    assert "27B" in strict.value.message
+    # another kind's magic, a norm vector past the constants, bytes after the constants
+    with pytest.raises(image.Q4Error) as magic:
+        image.Q4Image(path, image.GLOBAL, 0)
+    assert "magic" in magic.value.message
+    outside = str(tmp_path / "outside.img")
+    image.write_mtp_image(outside, hidden, fc, *norms, extra_fields={"final_norm_constants_index": 2 * hidden + 1})
+    with pytest.raises(image.Q4Error) as norm:
+        image.Q4Image(outside, image.MTP, 0)
+    assert "norm vector" in norm.value.message
+    longer = str(tmp_path / "longer.img")
+    with open(longer, "wb") as handle:
+        handle.write(open(path, "rb").read() + b"\0" * 4096)
+    with pytest.raises(image.Q4Error) as tail:
+        image.Q4Image(longer, image.MTP, 0)
     assert "does not end with the constants" in tail.value.message
