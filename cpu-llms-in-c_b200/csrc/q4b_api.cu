@@ -87,6 +87,12 @@ int device_failure(char *message, size_t capacity, const char *what, cudaError_t
     } while (0)
 
 bool valid_activation_dtype(int dtype) { return dtype == Q4B_F16 || dtype == Q4B_F32; }
+// bf16 activations (the H3 projections) multiply weights rounded to bf16; outputs and residuals are then bf16 or
+// fp32.  fp16 and fp32 activations keep fp16 or fp32 around them.
+bool valid_dtype_pair(int x_dtype, int other_dtype) {
+    if (x_dtype == Q4B_BF16) return other_dtype == Q4B_BF16 || other_dtype == Q4B_F32;
+    return valid_activation_dtype(x_dtype) && valid_activation_dtype(other_dtype);
+}
 size_t dtype_bytes(int dtype) { return dtype == Q4B_F32 ? 4 : 2; }
 bool aligned16(const void *pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
 
@@ -229,8 +235,9 @@ int check_matmul_arguments(q4b_context *context, const q4b_weight *weight, const
         set_error(error_message, error_capacity, "batch_rows is 0");
         return Q4B_BAD_ARGUMENT;
     }
-    if (!valid_activation_dtype(x_dtype) || !valid_activation_dtype(y_dtype)) {
-        set_error(error_message, error_capacity, "x and y must be fp16 or fp32");
+    if (!valid_dtype_pair(x_dtype, y_dtype)) {
+        set_error(error_message, error_capacity,
+                  "x and y must be fp16 or fp32, or x bf16 with y bf16 or fp32");
         return Q4B_BAD_ARGUMENT;
     }
     if (ldy < weight->view.rows) {
@@ -334,6 +341,7 @@ int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_mess
     gemm.up = args.up;
     gemm.fused_silu = args.fused_silu;
     gemm.x = x;
+    gemm.x_bf16 = args.x_dtype == kBF16;
     gemm.m_rows = args.m_rows;
     gemm.y_dtype = args.y_dtype;
     gemm.residual = args.residual;
@@ -356,6 +364,14 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
     const size_t K = (size_t)args.w[0].groups * kGroup;
     // variant bit 15 keeps large M on the small-M kernel (row blocks of 16), for A/B runs
     if (total > limit && !built_in_scratch && ((context->variant >> 15) & 1) == 0) {
+        return run_tensor_core(context, args, error_message, error_capacity);
+    }
+    if (args.x_dtype == kBF16) {
+        // the small-M kernel multiplies fp16; bf16 activations go to the tensor-core kernel at every M
+        if (built_in_scratch) {
+            set_error(error_message, error_capacity, "bf16 activations need q4b_matmul");
+            return Q4B_BAD_ARGUMENT;
+        }
         return run_tensor_core(context, args, error_message, error_capacity);
     }
     if (context->push_peers != 0) {
@@ -779,8 +795,9 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
     code = check_matmul_arguments(context, weight, x, x_dtype, m_rows, y, y_dtype, ldy, error_message,
                                   error_capacity);
     if (code != Q4B_OK) return code;
-    if (residual != nullptr && (!valid_activation_dtype(residual_dtype) || ld_residual < weight->view.rows)) {
-        set_error(error_message, error_capacity, "residual must be fp16 or fp32 with ld >= rows");
+    if (residual != nullptr && (!valid_dtype_pair(x_dtype, residual_dtype) || ld_residual < weight->view.rows)) {
+        set_error(error_message, error_capacity,
+                  "residual must be fp16 or fp32 (bf16 or fp32 beside bf16 activations) with ld >= rows");
         return Q4B_BAD_ARGUMENT;
     }
     GemvArgs args = {};
@@ -884,7 +901,7 @@ static int host_call(q4b_context *context, const q4b_weight *gate, const q4b_wei
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
     if (gate == nullptr || x_host == nullptr || y_host == nullptr || m_rows == 0 ||
-        !valid_activation_dtype(x_dtype) || !valid_activation_dtype(y_dtype)) {
+        !valid_dtype_pair(x_dtype, y_dtype)) {
         set_error(error_message, error_capacity, "invalid projection");
         return Q4B_BAD_ARGUMENT;
     }

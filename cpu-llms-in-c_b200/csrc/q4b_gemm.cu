@@ -195,7 +195,10 @@ __device__ inline uint32_t tc_cta_of_iteration(const TcParams &p, uint32_t itera
 
 // BN   : activation rows per tile (columns of D)
 // FUSED: the A tile is 64 rows of `w` (gate) over 64 rows of `up`; epilogue silu(gate) * up
-template <int BN, bool FUSED>
+// BF   : bf16 activations against weights rounded to bf16 (the arithmetic of
+//        minimax_h3_q4_gemm_bf16_activation, minimax_h3_attention.metal:512-592, and of its CPU check,
+//        minimax_h3_m3_real_gemm.c:25-42); otherwise fp16 activations against fp16 weights
+template <int BN, bool FUSED, bool BF>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
     constexpr int kTcStages = TcStages<BN, FUSED>::value;
@@ -293,7 +296,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            // D fp32; A and B fp16 (format 0) or bf16 (format 1, bits 7 and 10); N and M
+            const uint32_t idesc = (1u << 4) | (BF ? (1u << 7) | (1u << 10) : 0u) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((128u >> 4) << 24);
             const uint64_t desc_base = ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
                                        ((uint64_t)2 << 61);
             uint32_t it = 0, unit = 0, tile_iter = 0, tile, g0, g1;
@@ -359,6 +364,10 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
                     const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
                     const __half2 scale = __half2half2(__low2half(sb)), bias = __half2half2(__high2half(sb));
+                    // bf16 weights: scale and bias come back from the fp16 record unchanged when the planes were
+                    // bf16 to begin with (every bf16 in fp16's normal range is an fp16)
+                    const __nv_bfloat162 scale_b = __float2bfloat162_rn(__low2float(sb));
+                    const __nv_bfloat162 bias_b = __float2bfloat162_rn(__high2float(sb));
                     uint32_t regs[32];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
@@ -366,6 +375,23 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         const uint32_t word[4] = {piece.x, piece.y, piece.z, piece.w};
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
+                            if constexpr (BF) {
+                                // 0x4300 | q is 128 + q in bf16 (seven fraction bits), so the odd nibbles are
+                                // shifted down first; q = (128 + q) - 128 exactly, then one fused multiply-add
+                                // rounds s q + b to bf16 once
+                                const uint32_t wa = word[i] >> (hi ? 4 : 0), wb = word[i] >> (hi ? 12 : 8);
+                                uint32_t v01, v23;
+                                asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(v01) : "r"(wa));
+                                asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(v23) : "r"(wb));
+                                const __nv_bfloat162 offset = __float2bfloat162_rn(128.0f);
+                                const __nv_bfloat162 q01 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v01), offset);
+                                const __nv_bfloat162 q23 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v23), offset);
+                                const __nv_bfloat162 w01 = __hfma2(q01, scale_b, bias_b);
+                                const __nv_bfloat162 w23 = __hfma2(q23, scale_b, bias_b);
+                                regs[8 * t + 2 * i] = *reinterpret_cast<const uint32_t *>(&w01);
+                                regs[8 * t + 2 * i + 1] = *reinterpret_cast<const uint32_t *>(&w23);
+                                continue;
+                            }
                             uint32_t v01, v23;
                             const uint32_t w8 = word[i] >> 8;
                             asm("lop3.b32 %0, %1, %2, 0x64006400, 0xEA;" : "=r"(v01) : "r"(word[i]), "r"(mask));
@@ -507,6 +533,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                                 if ((uint32_t)q < valid) {
                                     v[q] += p.residual_dtype == kF32
                                                 ? reinterpret_cast<const float *>(p.residual)[at + q]
+                                            : p.residual_dtype == kBF16
+                                                ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.residual)[at + q])
                                                 : __half2float(reinterpret_cast<const __half *>(p.residual)[at + q]);
                                 }
                             }
@@ -520,6 +548,15 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                             for (int q = 0; q < 4; ++q) {
                                 packed[q] = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
                                                        __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+                            }
+                        } else if (p.y_dtype == kBF16) {
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                __nv_bfloat162 h[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+                                packed[q] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
+                                                       *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
                             }
                         } else {
 #pragma unroll
@@ -547,6 +584,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                                     if ((uint32_t)q >= valid) continue;
                                     if (f32) {
                                         reinterpret_cast<float *>(destination)[at + q] = v[q];
+                                    } else if (p.y_dtype == kBF16) {
+                                        reinterpret_cast<__nv_bfloat16 *>(destination)[at + q] = __float2bfloat16_rn(v[q]);
                                     } else {
                                         reinterpret_cast<__half *>(destination)[at + q] = __float2half_rn(v[q]);
                                     }
@@ -589,7 +628,7 @@ EncodeTiledFn encode_tiled() {
     return function;
 }
 
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, bool BF>
 cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr) return cudaErrorNotSupported;
@@ -597,7 +636,7 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     const cuuint64_t strides[1] = {(cuuint64_t)args.w[0].groups * kGroup * sizeof(__half)};
     const cuuint32_t box[2] = {(cuuint32_t)kGroup, (cuuint32_t)BN};
     const cuuint32_t element_strides[2] = {1, 1};
-    if (encode(&p.x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(args.x), dims, strides, box,
+    if (encode(&p.x_map, BF ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(args.x), dims, strides, box,
                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
         return cudaErrorInvalidValue;
@@ -612,7 +651,7 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     constexpr int kTcStages = TcStages<BN, FUSED>::value;
     const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
                               (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + kTcWarpgroups * 16 * 128 * 4 + 1024;
-    auto kernel = tc_gemm_kernel<BN, FUSED>;
+    auto kernel = tc_gemm_kernel<BN, FUSED, BF>;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -678,12 +717,20 @@ cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t st
     if (blocks == 0) return cudaSuccess;
     p.y_dtype = args.y_dtype;
     p.residual_dtype = args.residual_dtype;
-    if (args.fused_silu) {
-        return args.m_rows <= 128 ? launch_tc_instance<128, true>(p, args, sm_count, stream)
-                                  : launch_tc_instance<256, true>(p, args, sm_count, stream);
+    if (args.x_bf16) {
+        if (args.fused_silu) {
+            return args.m_rows <= 128 ? launch_tc_instance<128, true, true>(p, args, sm_count, stream)
+                                      : launch_tc_instance<256, true, true>(p, args, sm_count, stream);
+        }
+        return args.m_rows <= 128 ? launch_tc_instance<128, false, true>(p, args, sm_count, stream)
+                                  : launch_tc_instance<256, false, true>(p, args, sm_count, stream);
     }
-    return args.m_rows <= 128 ? launch_tc_instance<128, false>(p, args, sm_count, stream)
-                              : launch_tc_instance<256, false>(p, args, sm_count, stream);
+    if (args.fused_silu) {
+        return args.m_rows <= 128 ? launch_tc_instance<128, true, false>(p, args, sm_count, stream)
+                                  : launch_tc_instance<256, true, false>(p, args, sm_count, stream);
+    }
+    return args.m_rows <= 128 ? launch_tc_instance<128, false, false>(p, args, sm_count, stream)
+                              : launch_tc_instance<256, false, false>(p, args, sm_count, stream);
 }
 
 // fp32 activations -> fp16 (the tensor pipe multiplies fp16)

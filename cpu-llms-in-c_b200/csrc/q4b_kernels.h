@@ -104,7 +104,8 @@ struct TcGemmArgs {
     int segments;
     WeightView up;        // valid when fused_silu (single segment)
     int fused_silu;
-    const void *x;        // [M][K] fp16, 16-byte aligned
+    const void *x;        // [M][K] fp16 (bf16 when x_bf16), 16-byte aligned
+    int x_bf16;           // bf16 activations against weights rounded to bf16
     uint32_t m_rows;
     int y_dtype;
     const void *residual; // [M][ld_residual] or null

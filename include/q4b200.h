@@ -122,7 +122,19 @@ int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *c
  * of the shard lets a shard write its column slice of a wider matrix),
  * residual is [M][ld_residual] fp16 or fp32 or NULL.  DEVICE pointers, 16-byte
  * aligned; asynchronous.  The kernel is chosen by M: the decode kernel for
- * M <= 16, the tcgen05 GEMM above. */
+ * M <= 16, the tcgen05 GEMM above.
+ *
+ * bf16 activations (x_dtype = Q4B_BF16) select the arithmetic of the H3
+ * projections (minimax_h3_q4_gemm_bf16_activation, minimax_h3_attention.metal:
+ * 512-592; CPU check benchmarks/minimax_h3_m3_real_gemm.c:25-42): every weight
+ * is rounded to bf16, w = bf16(scale * q + bias), multiplied with bf16 x on the
+ * tensor cores and summed in fp32 over the whole of K; y and the residual are
+ * then bf16 or fp32.  The tcgen05 GEMM serves this at every M.  Meant for
+ * weights uploaded from bf16 planes (q4b_weight_upload_planes with Q4B_BF16):
+ * scale and bias are taken from the fp16 records and rounded to bf16, which
+ * gives the plane's own values back wherever they lie in fp16's normal range.
+ * Sequences, q4b_matmul_no_alloc and mixed pairs (fp16/fp32 x with bf16 y, bf16
+ * x with fp16 y) are refused with status 1. */
 int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
                uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, const void *residual,
                int residual_dtype, uint32_t ld_residual,

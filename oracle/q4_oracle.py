@@ -280,6 +280,31 @@ def matmul_bf16(quants, scales_bf16, biases_bf16, groups, x_bf16, row_begin=0,
     return y
 
 
+def round_bf16(values: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bits, round to nearest even: bfloat_bits of the H3 CPU check
+    (benchmarks/minimax_h3_m3_real_gemm.c:18-23).  Finite inputs only."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    rounding = np.uint64(0x7FFF) + ((bits >> np.uint64(16)) & np.uint64(1))
+    return ((bits + rounding) >> np.uint64(16)).astype(np.uint16)
+
+
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    """bf16 bits -> float32 (bfloat_value, benchmarks/minimax_h3_m3_real_gemm.c:11-16)."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def dequant_wbf16(quants, scales_bf16, biases_bf16, rows, groups) -> np.ndarray:
+    """The weights the H3 bf16 GEMM multiplies, as bf16 bits [rows, 64 * groups]:
+    bf16(scale * float(q) + bias) with scale and bias widened from bf16, the
+    product and the sum in fp32 (benchmarks/minimax_h3_m3_real_gemm.c:31-38;
+    minimax_h3_attention.metal:542-551).  scale * q is exact in fp32."""
+    codes = unpack_codes(quants, rows, groups).astype(np.float32).reshape(rows, groups, 64)
+    scale = bf16_to_f32(np.asarray(scales_bf16).reshape(rows, groups, 1))
+    bias = bf16_to_f32(np.asarray(biases_bf16).reshape(rows, groups, 1))
+    product = scale * codes                   # float32, exact
+    return round_bf16(product + bias).reshape(rows, groups * 64)
+
+
 def round_f16(values: np.ndarray) -> np.ndarray:
     flat = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
     out = np.empty(flat.size, dtype=np.uint16)
