@@ -288,7 +288,8 @@ def run_ours(args):
         prefill = prefill_gemm(q4b, ctx, model, peaks)
     elif not args.no_prefill:
         prefill = sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, args.gather)
-    extras = {"prefill_gemm": prefill,
+    h3 = h3_bf16_gemm(q4b, ctx, peaks) if world == 1 and not args.no_prefill else None
+    extras = {"prefill_gemm": prefill, "h3_bf16_gemm": h3,
               "whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
               "whole_step_frac_of_8TBs": value / world / 8000.0,
               "tflops": layer_flops * LAYERS / (ms_per_step * 1e-3) / 1e12}
@@ -337,6 +338,44 @@ def prefill_gemm(q4b, ctx, model, peaks, layers=8):
         for b in list(xs.values()) + list(ys.values()):
             b.free()
     return results
+
+
+def h3_bf16_gemm(q4b, ctx, peaks, blocks=2, m=2048):
+    """The four Q4 projections of a MiniMax-H3 block (qkv 5376->21504, out 7168->5376, fc1 5376->28672,
+    fc2 14336->5376; compiler/minimax-h3/apple-m3-pro/minimax_h3_q4_layer.c:15-20) with bf16 activations and
+    outputs, weights rounded to bf16, M = 2048 rows per call, rotating over `blocks` blocks of distinct weights
+    (432 MB, larger than L2); TFLOP/s = 2*M*N*K over device time (CUDA events)."""
+    import numpy as np
+    shapes = [("qkv_proj", 21504, 5376), ("out_proj", 5376, 7168), ("fc1", 28672, 5376), ("fc2", 5376, 14336)]
+    rng = np.random.default_rng(0)
+    weights = [[ctx.synth_weight(100 + b, i, n, k // 64) for i, (_, n, k) in enumerate(shapes)] for b in range(blocks)]
+    xs, ys = {}, {}
+    for name, n, k in shapes:
+        values = rng.standard_normal((m, k), dtype=np.float32)
+        xs[name] = ctx.to_device((values.view(np.uint32) >> 16).astype(np.uint16))  # bf16 bits (truncated)
+        ys[name] = ctx.alloc(m * n * 2)
+
+    def run():
+        for block in weights:
+            for weight, (name, _, _) in zip(block, shapes):
+                ctx.matmul(weight, xs[name].ptr, q4b.BF16, m, ys[name].ptr, q4b.BF16)
+    run()
+    ctx.sync()
+    reps = 3
+    ctx.timer_start()
+    for _ in range(reps):
+        run()
+    ms = ctx.sync(timed=True) / (reps * blocks)
+    flops = sum(2.0 * m * n * k for _, n, k in shapes)
+    tflops = flops / (ms * 1e-3) / 1e12
+    for block in weights:
+        for weight in block:
+            weight.free()
+    for b in list(xs.values()) + list(ys.values()):
+        b.free()
+    return {"m_rows": m, "ms_per_block": ms, "tflops": tflops, "dtype": "u4*bf16->f32->bf16",
+            "frac_of_measured_bf16_burst": tflops / peaks["bf16_tflops"],
+            "frac_of_measured_bf16_sustained": tflops / peaks["bf16_tflops_sustained"]}
 
 
 def sharded_prefill(q4b, sharded, ctx, rank, world, dist, peaks, barrier, max_over_ranks, gather, layers=8, m=512):
