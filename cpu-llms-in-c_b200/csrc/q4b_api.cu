@@ -753,6 +753,23 @@ int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, cons
     return Q4B_OK;
 }
 
+int q4b_rmsnorm(q4b_context *context, const void *input, int input_dtype, const float *weight, void *output_f16,
+                uint32_t hidden, uint32_t batch_rows, float epsilon, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (input == nullptr || weight == nullptr || output_f16 == nullptr || hidden == 0 || batch_rows == 0 ||
+        !valid_activation_dtype(input_dtype) || !(epsilon >= 0.0f)) {
+        set_error(error_message, error_capacity,
+                  "input (fp16 or fp32), weight, output, hidden, batch_rows or epsilon missing or invalid");
+        return Q4B_BAD_ARGUMENT;
+    }
+    cudaError_t status = launch_rmsnorm(input, input_dtype, weight, output_f16, hidden, batch_rows, epsilon,
+                                        context->stream);
+    if (!context->capturing) ++context->launches;
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "rms norm", status);
+    return Q4B_OK;
+}
+
 int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *codes, float *w32,
                       uint16_t *w16, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);

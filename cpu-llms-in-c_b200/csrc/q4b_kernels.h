@@ -19,6 +19,9 @@ cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
 // out[i][K] fp16 or fp32; rows the shard does not hold give zeros
 cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t count, uint32_t row_base, void *out,
                                int out_dtype, cudaStream_t stream);
+// output[b][i] = half(input[b][i] * inv_rms(b) * weight[i]), input fp16 or fp32 [batch][hidden], one block per row
+cudaError_t launch_rmsnorm(const void *input, int input_dtype, const float *weight, void *output, uint32_t hidden,
+                           uint32_t batch, float epsilon, cudaStream_t stream);
 cudaError_t launch_synth_codes(uint64_t seed, uint64_t stream_id, uint32_t *words,
                                uint64_t word_begin, uint64_t word_count, cudaStream_t stream);
 cudaError_t launch_synth_meta(uint64_t seed, uint64_t stream_id, __half *meta,

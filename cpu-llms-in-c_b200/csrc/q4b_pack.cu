@@ -220,6 +220,57 @@ cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t coun
 }
 
 // ---------------------------------------------------------------------------
+// RMS norm: the step that produces the fp16 x of a layer's in-projections and of the MLP
+// (qwen38_rmsnorm_f16_to_f16 / qwen38_rmsnorm_f32_to_f16, qwen38_layer.metal:21-69; one thread block per
+// activation row as in their batched forms).  Same order of operations as the reference: 256 strided partial
+// sums of squares, a halving tree over them, out = half(x * inv_rms * weight) with both products in fp32.
+// Every operation is rounded on its own (no fused multiply-add, IEEE square root and division), so the result
+// is a function of the inputs alone and a CPU restatement reproduces it bit for bit.
+// ---------------------------------------------------------------------------
+template <typename In>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const In *__restrict__ input, const float *__restrict__ weight, __half *__restrict__ output,
+               uint32_t hidden, float epsilon) {
+    __shared__ float partials[256];
+    const uint32_t tid = threadIdx.x;
+    const In *row = input + (size_t)blockIdx.x * hidden;
+    auto value_at = [&](uint32_t index) {
+        if constexpr (sizeof(In) == 2) return __half2float(row[index]);
+        else return (float)row[index];
+    };
+    float sum = 0.0f;
+    for (uint32_t index = tid; index < hidden; index += 256) {
+        const float value = value_at(index);
+        sum = __fadd_rn(sum, __fmul_rn(value, value));
+    }
+    partials[tid] = sum;
+    __syncthreads();
+    for (uint32_t stride = 128; stride != 0; stride >>= 1) {
+        if (tid < stride) partials[tid] = __fadd_rn(partials[tid], partials[tid + stride]);
+        __syncthreads();
+    }
+    const float mean = __fadd_rn(__fdiv_rn(partials[0], (float)hidden), epsilon);
+    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(mean));
+    __half *out = output + (size_t)blockIdx.x * hidden;
+    for (uint32_t index = tid; index < hidden; index += 256) {
+        out[index] = __float2half_rn(__fmul_rn(__fmul_rn(value_at(index), inv_rms), weight[index]));
+    }
+}
+
+cudaError_t launch_rmsnorm(const void *input, int input_dtype, const float *weight, void *output, uint32_t hidden,
+                           uint32_t batch, float epsilon, cudaStream_t stream) {
+    if (batch == 0) return cudaSuccess;
+    if (input_dtype == kF32) {
+        rmsnorm_kernel<float><<<batch, 256, 0, stream>>>(static_cast<const float *>(input), weight,
+                                                         static_cast<__half *>(output), hidden, epsilon);
+    } else {
+        rmsnorm_kernel<__half><<<batch, 256, 0, stream>>>(static_cast<const __half *>(input), weight,
+                                                          static_cast<__half *>(output), hidden, epsilon);
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // seeded generator
 // ---------------------------------------------------------------------------
 __global__ void synth_codes_kernel(uint64_t key, uint32_t *words, uint64_t word_begin,

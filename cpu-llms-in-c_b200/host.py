@@ -97,6 +97,7 @@ def library() -> ctypes.CDLL:
         "q4b_barrier_queue": (_int, [_vp, _vp] + err),
         "q4b_barrier_free": (None, [_vp, _vp]),
         "q4b_embedding_lookup": (_int, [_vp, _vp, _vp, _u32, _vp, _int] + err),
+        "q4b_rmsnorm": (_int, [_vp, _vp, _int, _vp, _vp, _u32, _u32, ctypes.c_float] + err),
         "q4b_sequence_create": (_int, [_vp, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_sequence_add_matmul": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, ctypes.POINTER(_vp),
                                            ctypes.POINTER(_u32), _int] + err),
@@ -415,6 +416,12 @@ class Q4Context:
     def embedding_lookup(self, embedding: Q4Weight, rows_ptr: int, count: int, out_ptr: int, out_dtype: int = F16):
         self._check(library().q4b_embedding_lookup(self.handle, embedding.handle, rows_ptr, count, out_ptr, out_dtype,
                                                    self._err, _ERR))
+
+    def rmsnorm(self, input_ptr: int, input_dtype: int, weight_ptr: int, output_ptr: int, hidden: int,
+                batch_rows: int, epsilon: float = 1e-6):
+        """fp16 x of a layer's matmuls from its hidden state (q4b_rmsnorm)."""
+        self._check(library().q4b_rmsnorm(self.handle, input_ptr, input_dtype, weight_ptr, output_ptr, hidden,
+                                          batch_rows, epsilon, self._err, _ERR))
 
     def gate_up_silu(self, gate: Q4Weight, up: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int,
                      y_dtype: int = F16, ldy: int | None = None):

@@ -107,6 +107,18 @@ int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_p
 int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, const uint32_t *rows,
                          uint32_t count, void *out, int out_dtype,
                          char *error_message, size_t error_capacity);
+
+/* ---- the step before a layer's matmuls: RMS norm of the hidden state into the fp16 x
+ * that the in-projections and the MLP read.  Replaces qwen38_rmsnorm_f16_to_f16 and
+ * qwen38_rmsnorm_f32_to_f16 (qwen38_layer.metal:21-69) and their batched forms:
+ * output[b][i] = half(input[b][i] * inv_rms(b) * weight[i]) with
+ * inv_rms = 1 / sqrt(mean(input[b]^2) + epsilon), in the reference's order of
+ * operations (256 strided partial sums, a halving tree, two fp32 products), every
+ * operation rounded on its own.  input is [batch_rows][hidden] fp16 or fp32, weight
+ * fp32 [hidden] (the layer image's constants hold it), output fp16; DEVICE pointers;
+ * asynchronous on the context's stream.  The reference's epsilon is 1e-6. */
+int q4b_rmsnorm(q4b_context *context, const void *input, int input_dtype, const float *weight, void *output_f16,
+                uint32_t hidden, uint32_t batch_rows, float epsilon, char *error_message, size_t error_capacity);
 /* Dequantisation in isolation (the job of qwen38_q4_embedding_lookup,
  * qwen38_global.metal:13-28) over the whole shard, written to HOST buffers, any
  * of which may be NULL: codes uint8 [rows][K], w32 float [rows][K] =

@@ -280,6 +280,31 @@ def matmul_bf16(quants, scales_bf16, biases_bf16, groups, x_bf16, row_begin=0,
     return y
 
 
+def rmsnorm(values: np.ndarray, weight: np.ndarray, epsilon: float = 1e-6) -> np.ndarray:
+    """qwen38_rmsnorm_f16_to_f16 / _f32_to_f16 (qwen38_layer.metal:21-69), per row of
+    `values` [batch, hidden] (float16 or float32): 256 strided partial sums of squares
+    in index order, the halving tree over them, inv_rms = 1 / sqrt(sum / hidden +
+    epsilon), out = half(x * inv_rms * weight).  Every operation is a separately
+    rounded float32 operation; returns float16 [batch, hidden]."""
+    x = np.ascontiguousarray(values).astype(np.float32)
+    batch, hidden = x.shape
+    chunks = -(-hidden // 256)
+    squares = np.zeros((batch, chunks * 256), dtype=np.float32)
+    squares[:, :hidden] = x * x
+    squares = squares.reshape(batch, chunks, 256)
+    partials = np.zeros((batch, 256), dtype=np.float32)
+    for chunk in range(chunks):                      # thread t adds elements t, t + 256, ... in this order
+        partials = partials + squares[:, chunk, :]
+    stride = 128
+    while stride:
+        partials[:, :stride] = partials[:, :stride] + partials[:, stride:2 * stride]
+        stride >>= 1
+    mean = partials[:, 0] / np.float32(hidden) + np.float32(epsilon)
+    inv_rms = np.float32(1.0) / np.sqrt(mean, dtype=np.float32)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    return ((x * inv_rms[:, None]) * w[None, :]).astype(np.float16)
+
+
 def round_bf16(values: np.ndarray) -> np.ndarray:
     """float32 -> bf16 bits, round to nearest even: bfloat_bits of the H3 CPU check
     (benchmarks/minimax_h3_m3_real_gemm.c:18-23).  Finite inputs only."""

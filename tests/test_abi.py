@@ -47,6 +47,7 @@ def test_null_arguments_are_rejected_without_touching_a_device(q4b):
     assert lib.q4b_layer_wrap(None, None, None, 0, 1, None) == 1
     assert lib.q4b_layer_encode_mlp(None, None, None, 1, None, 0, None, 0, None, 0, err, 256) == 1
     assert lib.q4b_embedding_lookup(None, None, None, 0, None, 0, err, 256) == 1
+    assert lib.q4b_rmsnorm(None, None, 0, None, None, 0, 0, ctypes.c_float(1e-6), err, 256) == 1
     assert lib.q4b_sequence_launch(None, None, err, 256) == 1
 
 
