@@ -4,6 +4,7 @@
     python cpu-llms-in-c_b200/profile_case.py gemv down 4        # decode kernel, down projection, M = 4
     python cpu-llms-in-c_b200/profile_case.py gemm gate_up 2048  # tcgen05 kernel, fused gate/up, M = 2048
     python cpu-llms-in-c_b200/profile_case.py sequence 2 1       # decode sequence: 2 whole 27B layers, M = 1
+    python cpu-llms-in-c_b200/profile_case.py gemm h3_fc1 2048 bf16  # tcgen05 kernel, H3 fc1, bf16 activations
 
 The 27B shapes over a few sets of distinct weights (about 0.4 GB on the device,
 more than L2, so DRAM counters mean something), two passes, a handful of
@@ -16,7 +17,9 @@ import sys
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 SHAPES = {"q": (5120, 6144, False), "o": (6144, 5120, False), "gate_up": (5120, 17408, True),
-          "down": (17408, 5120, False)}
+          "down": (17408, 5120, False),
+          # MiniMax-H3 block projections (compiler/minimax-h3/apple-m3-pro/minimax_h3_q4_layer.c:15-20)
+          "h3_qkv": (5376, 21504, False), "h3_fc1": (5376, 28672, False), "h3_fc2": (14336, 5376, False)}
 
 
 def sequence(q4b, layers, m):
@@ -42,6 +45,9 @@ def main(argv):
     if kind == "gemv" and m > 16 or kind == "gemm" and m <= 16:
         raise SystemExit("gemv takes M <= 16, gemm M > 16")
     k, n, fused = SHAPES[which]
+    dtype = q4b.BF16 if len(argv) > 4 and argv[4] == "bf16" else q4b.F16
+    if dtype == q4b.BF16 and kind != "gemm":
+        raise SystemExit("bf16 activations run on the tcgen05 kernel: use gemm")
     sets = max(2, int(0.4e9 // (k * n * (1.0 if fused else 0.5) * 1.125)))
     ctx = q4b.Q4Context(0)
     weights = [(ctx.synth_weight(index, 0, n, k // 64), ctx.synth_weight(index, 1, n, k // 64) if fused else None)
@@ -51,9 +57,9 @@ def main(argv):
     for _ in range(2):
         for gate, up in weights:
             if fused:
-                ctx.gate_up_silu(gate, up, x.ptr, q4b.F16, m, y.ptr)
+                ctx.gate_up_silu(gate, up, x.ptr, dtype, m, y.ptr, dtype)
             else:
-                ctx.matmul(gate, x.ptr, q4b.F16, m, y.ptr)
+                ctx.matmul(gate, x.ptr, dtype, m, y.ptr, dtype)
     ctx.sync()
     print(f"{kind} {which} M={m}: {2 * sets} launches over {sets} weight sets")
     ctx.close()

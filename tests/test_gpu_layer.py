@@ -62,3 +62,41 @@ def test_27b_layer_matches_oracle_at_decode(q4b, orc, mode):
         for name in want:
             assert_close(got[name], want[name], f"27B {name}")
         stack.free()
+
+
+def rank_slice_set(q4b, world):
+    """The projections one of `world` column-parallel ranks works on: 1/world of every N, the whole of every K."""
+    projection = importlib.import_module("cpu-llms-in-c_b200.shapes").Projection
+    return tuple(projection(p.name, p.k, p.n // world, p.fused, p.group) for p in q4b.LAYER_27B)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("m,mode", [(1, "sequence"), (4, "sequence"), (1, "graph"), (512, "graph")])
+def test_shapes_of_one_rank_among_many(q4b, orc, world, m, mode):
+    """One GPU stands in for a single rank of a 4- or 8-rank job: same shapes, same kernels and work split
+    (few row blocks, long K), checked on sampled weight rows."""
+    sharded = importlib.import_module("cpu-llms-in-c_b200.sharded")
+    layer_set = rank_slice_set(q4b, world)
+    with q4b.Q4Context(0) as ctx:
+        stack = sharded.ShardedLayerStack(ctx, layer_set, 2, m, mode=mode)
+        stack.step()
+        stack.step()
+        got = stack.outputs(1)
+        seed, index = 1, 0
+        for p in layer_set:
+            groups = p.k // 64
+            x = orc.synth_x(seed, 0, m, p.k)
+            rows = sorted({0, 1, p.n // 2, p.n - 65, p.n - 1})
+            for row in rows:
+                if p.fused:
+                    gq, gm = orc.synth_weight_rows(seed, index, groups, [row])
+                    uq, um = orc.synth_weight_rows(seed, index + 1, groups, [row])
+                    want = orc.gate_up_silu(gq, gm, uq, um, groups, x, want32=False)[1]
+                else:
+                    q, mt = orc.synth_weight_rows(seed, index, groups, [row])
+                    want = orc.matmul(q, mt, groups, x, want32=False)[1]
+                # sampled rows, so max|ref| is taken from the device's whole output of this projection
+                scale = float(np.max(np.abs(got[p.name].astype(np.float32))))
+                assert np.max(np.abs(got[p.name][:, row:row + 1] - want)) / scale <= 2e-3, (p.name, row, m, mode)
+            index += 2 if p.fused else 1
+        stack.free()
