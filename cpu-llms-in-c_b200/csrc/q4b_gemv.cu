@@ -166,19 +166,32 @@ __device__ inline void load_x16(const void *x, size_t element, bool valid, uint3
     }
 }
 
+// u8 x s8 -> s32, m16n8k32: the codes as bytes against activations as signed 8-bit digits
+__device__ inline void mma_16832_u8s8(int d[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+
 // NT   : 8-column output tiles per warp (M <= 8*NT)
 // FUSED: second matrix (`up`) shares x; epilogue silu(gate) * up
 // SUBN : feed the codes to the tensor pipe as fp16 subnormals (no unpack math)
 // X32  : x arrives as fp32 and is rounded to fp16 while it is staged
+// I8   : (fused gate/up, M <= 4, fp16 x) integer form: every consumer warp turns its group of x into two signed
+//        8-bit digits per value with one power-of-two step per group and row (15 bits relative to the group's
+//        largest value, where fp16 itself carries 11 per value), the codes go to the tensor pipe as bytes
+//        (mma.sync m16n8k32 u8 x s8, exact s32 sums) and scale, step and bias are applied per group in fp32
 //
 // Warps 0..7 consume, warp 8 produces.  A ring stage holds up to 8 consecutive
 // groups of one 64-row block (8 x 2304 bytes, one bulk copy; fused gate/up adds the
 // same groups of the second matrix as a second copy).  Consumer warp w takes group
 // w of the stage: four independent tiles (eight when fused, sharing one read of
 // x), accumulated in registers across stages.
-template <int NT, bool FUSED, bool SUBN, bool X32>
+template <int NT, bool FUSED, bool SUBN, bool X32, bool I8 = false>
 __global__ void __launch_bounds__(288, (FUSED && NT > 1) ? 1 : 2)
 gemv_kernel(const GemvParams p) {
+    static_assert(!I8 || (NT == 1 && FUSED && !X32), "the integer form serves fused gate/up at M <= 4 with fp16 x");
     constexpr int NW = FUSED ? 2 : 1;
     constexpr int W = 8;                             // consumer warps
     constexpr uint32_t S = W;                        // groups per full stage
@@ -317,11 +330,41 @@ gemv_kernel(const GemvParams p) {
             }
         };
 
+        // Integer form: lane (gid, t) accumulates rows gid (slot 0) and gid + 8 (slot 2) of activation row m = t.
+        // The block sums expect the fp16 form's layout -- slots 0..3 = (gid, m = 2t), (gid, 2t+1), (gid+8, 2t),
+        // (gid+8, 2t+1) -- so the sums change lanes once per finished row block.
+        auto settle = [&]() {
+            if constexpr (I8) {
+                const int base = lane & ~3, from = (2 * t) & 3;
+#pragma unroll
+                for (int k = 0; k < NW; ++k)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float top = acc[k][r][0][0], low = acc[k][r][0][2];
+                        const float top0 = __shfl_sync(0xffffffffu, top, base + from);
+                        const float top1 = __shfl_sync(0xffffffffu, top, base + from + 1);
+                        const float low0 = __shfl_sync(0xffffffffu, low, base + from);
+                        const float low1 = __shfl_sync(0xffffffffu, low, base + from + 1);
+                        const bool holds = t < 2;  // activation rows 2t, 2t+1 exist only below 4
+                        acc[k][r][0][0] = holds ? top0 : 0.0f;
+                        acc[k][r][0][1] = holds ? top1 : 0.0f;
+                        acc[k][r][0][2] = holds ? low0 : 0.0f;
+                        acc[k][r][0][3] = holds ? low1 : 0.0f;
+                    }
+            }
+        };
+
         // B fragments come straight from global memory (x is small and stays in L1/L2): lane (gid, t)
         // holds x[m = gid][64 g + 16 t .. +15] for each column tile.  They are fetched one stage ahead,
         // so that their latency hides behind the tiles of the stage before.
         uint32_t x_ahead[NT][8];
         auto fetch_x = [&](uint32_t group) {
+            if constexpr (I8) {
+                const uint32_t m = (uint32_t)gid >> 1;  // column gid of B = (row m, digit gid & 1)
+                // the same 16 consecutive columns as in the fp16 form: this lane's code words cover 16t .. 16t+15
+                load_x16<false>(p.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, x_ahead[0]);
+                return;
+            }
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const uint32_t m = n * 8 + gid;
@@ -336,6 +379,7 @@ gemv_kernel(const GemvParams p) {
             const uint32_t s = it % stages;
             const uint32_t count = min(min(S, G - g), u1 - ua);
             if (grb != cur_grb) {
+                settle();
                 flush(cur_grb - grb0);
                 cur_grb = grb;
             }
@@ -351,6 +395,84 @@ gemv_kernel(const GemvParams p) {
             // what the next stage holds, for the fetch ahead
             const uint32_t ua_next = ua + count, g_next = g + count == G ? 0u : g + count;
             const uint32_t count_next = ua_next < u1 ? min(min(S, G - g_next), u1 - ua_next) : 0u;
+            if constexpr (I8) {
+              if (j_mine < count) {
+                uint32_t raw[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) raw[i] = x_ahead[0][i];
+                if (j_mine < count_next) fetch_x(g_next + j_mine);
+                // one power-of-two step per (group, activation row): the largest |x| of the 64 columns
+                __half2 biggest = __habs2(*reinterpret_cast<__half2 *>(&raw[0]));
+#pragma unroll
+                for (int i = 1; i < 8; ++i) biggest = __hmax2(biggest, __habs2(*reinterpret_cast<__half2 *>(&raw[i])));
+                float top = fmaxf(__low2float(biggest), __high2float(biggest));
+                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+                top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+                int e = (int)((__float_as_uint(top) >> 23) & 0xffu) - 127;  // top in [2^e, 2^(e+1))
+                e = min(max(e, -10), 15);  // 2^(5-e) must be an fp16; smaller groups keep fewer bits, of a tiny value
+                const float factor = __uint_as_float((uint32_t)(127 + 5 - e) << 23);     // |x| * factor < 64
+                const float step_here = __uint_as_float((uint32_t)(127 + e - 13) << 23);  // one unit of the low digit
+                const __half2 f_hi = __float2half2_rn(factor);
+                const __half2 magic = __float2half2_rn(1536.0f), times256 = __float2half2_rn(256.0f);
+                const __half2 cap = __float2half2_rn(127.0f);
+                const bool low_digit = (gid & 1) != 0;
+                uint32_t b[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t digit[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        // x * 2^(13-e) = 256 hi + lo: v = x * 2^(5-e) lies in (-64, 64); hi = v rounded to nearest in
+                        // the 1536 binade (one unit per ulp), lo = 256 (v - hi) exactly, in [-128, 128], capped at 127
+                        // (a tie leaves 128: one unit of error, 2^-14 of the group's top) and rounded the same way
+                        const __half2 x2 = *reinterpret_cast<__half2 *>(&raw[2 * i + h]);
+                        const __half2 v = __hmul2(x2, f_hi);
+                        const __half2 hi_m = __hadd2(v, magic);
+                        const __half2 hi = __hsub2(hi_m, magic);
+                        const __half2 lo = __hmul2(__hsub2(v, hi), times256);
+                        const __half2 lo_m = __hadd2(__hmin2(lo, cap), magic);
+                        digit[h] = low_digit ? *reinterpret_cast<const uint32_t *>(&lo_m)
+                                             : *reinterpret_cast<const uint32_t *>(&hi_m);
+                    }
+                    // bytes in the order of the code bytes of word i: columns 4i, 4i+2, 4i+1, 4i+3 of this lane's 16
+                    b[i] = __byte_perm(digit[0], digit[1], 0x6240);
+                }
+                // as an accumulator owner this lane serves activation row m = t: that row's step sits in lane 8t
+                const float step = __shfl_sync(0xffffffffu, step_here, 8 * t);
+                // the group's sum of x, exact: a row of ones against the digits
+                const uint32_t ones[4] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
+                int s0[4], s1[4];
+                mma_16832_u8s8(s0, ones, b[0], b[1]);
+                mma_16832_u8s8(s1, ones, b[2], b[3]);
+                const float sum_x = step * (float)((s0[0] + s1[0]) * 256 + (s0[1] + s1[1]));
+#pragma unroll
+                for (int k = 0; k < NW; ++k) {
+                    const uint8_t *unit = ring + (size_t)s * kStageBytes + (size_t)(k * S + j_mine) * kUnitBytes;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint8_t *tile = unit + r * kTileBytes;
+                        const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
+                        const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
+                        // even nibbles: row gid, odd nibbles: row gid + 8; word i covers columns 4i .. 4i+3
+                        const uint32_t a0[4] = {codes.x & 0x0F0F0F0Fu, (codes.x >> 4) & 0x0F0F0F0Fu,
+                                                codes.y & 0x0F0F0F0Fu, (codes.y >> 4) & 0x0F0F0F0Fu};
+                        const uint32_t a1[4] = {codes.z & 0x0F0F0F0Fu, (codes.z >> 4) & 0x0F0F0F0Fu,
+                                                codes.w & 0x0F0F0F0Fu, (codes.w >> 4) & 0x0F0F0F0Fu};
+                        int c0[4], c1[4];
+                        mma_16832_u8s8(c0, a0, b[0], b[1]);
+                        mma_16832_u8s8(c1, a1, b[2], b[3]);
+                        const float top_row = (float)((c0[0] + c1[0]) * 256 + (c0[1] + c1[1]));
+                        const float low_row = (float)((c0[2] + c1[2]) * 256 + (c0[3] + c1[3]));
+                        const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
+                        const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
+                        acc[k][r][0][0] = fmaf(lo.x * step, top_row, fmaf(lo.y, sum_x, acc[k][r][0][0]));
+                        acc[k][r][0][2] = fmaf(hi.x * step, low_row, fmaf(hi.y, sum_x, acc[k][r][0][2]));
+                    }
+                }
+              } else if (j_mine < count_next) {
+                fetch_x(g_next + j_mine);
+              }
+            } else
             if (j_mine < count) {
                 uint32_t xb[NT][8];
                 float2 sums[NT];
@@ -433,6 +555,7 @@ gemv_kernel(const GemvParams p) {
             // Last row block of the range: the ring is drained, so every warp parks its
             // sums in its own slice of it at once and the block sums are formed in one
             // pass, still in warp order.
+            settle();
             consumer_barrier(kConsumers);
             float *parked = reinterpret_cast<float *>(ring);  // [W][PER_CTA]
 #pragma unroll
@@ -539,10 +662,10 @@ gemv_kernel(const GemvParams p) {
     Q4B_STAMP(7);
 }
 
-template <int NT, bool FUSED, bool SUBN, bool X32>
+template <int NT, bool FUSED, bool SUBN, bool X32, bool I8 = false>
 cudaError_t launch_instance(const GemvParams &p, unsigned ctas, int threads, size_t smem_bytes,
                             bool dependent_launch, cudaStream_t stream) {
-    auto kernel = gemv_kernel<NT, FUSED, SUBN, X32>;
+    auto kernel = gemv_kernel<NT, FUSED, SUBN, X32, I8>;
     static size_t configured = 0;  // per instantiation
     if (smem_bytes > configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -619,7 +742,7 @@ cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *sc
 // variant encoding (0 = heuristics): bits 0-3 CTAs per SM, 8-11 ring stages,
 // bit 12 equal unit ranges even when an even split of the row blocks exists,
 // bit 13 exact-fp16 codes instead of subnormals, bit 14 no programmatic
-// dependent launch
+// dependent launch, bit 4 the fp16 form also for fused gate/up at M <= 4 (default there: the integer form)
 cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan) {
     const uint32_t G = args.w[0].groups;
     const int NT = args.m_rows <= 8 ? 1 : 2;
@@ -704,6 +827,9 @@ cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant,
     const bool exact_codes = (variant >> 13) & 1, pdl = ((variant >> 14) & 1) == 0;
     const bool subnormal = !exact_codes, x32 = args.x_dtype == kF32;
     const int NT = args.m_rows <= 8 ? 1 : 2;
+    if (args.fused_silu && ((variant >> 4) & 1) == 0 && subnormal && args.m_rows <= 4 && !x32) {
+        return launch_instance<1, true, true, false, true>(p, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream);
+    }
     if (args.fused_silu) {
         return NT == 1 ? launch_by_flags<1, true>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream)
                        : launch_by_flags<2, true>(p, subnormal, x32, plan.ctas, plan.threads, plan.smem_bytes, pdl, stream);
