@@ -268,13 +268,13 @@ class ShardedLayerStack:
     def ncu_traffic_bytes(self):
         """DRAM bytes (read + written) per launch of the dominant kernel, from the
         profiler capture summarised in profiles/gemv_kernel_gate_up_27b_m1.md:
-        100.63 MB read + 3.95 MB written for the whole 27B gate/up pair at M = 1.
+        100.33 MB read + 3.59 MB written for the whole 27B gate/up pair at M = 1.
         Traffic is the weight stream, so a rank's slice moves 1/world of it; no
         capture exists for other shapes or M."""
         fused = next(p for p in self.layer_set if p.fused)
         if (fused.k, fused.n) != (5120, 17408) or self.m != 1:
             return None
-        return 104.58e6 / self.world
+        return 103.92e6 / self.world
 
     def free(self):
         if self.world > 1 and self.gather == "push":
