@@ -264,3 +264,49 @@ def test_bad_arguments_return_status_1(q4b, orc, ctx):
     with pytest.raises(q4b.Q4Error):
         ctx.matmul(weight, dx.ptr, q4b.F16, 1, dx.ptr, q4b.F16, 8)  # ldy < rows
     ctx.sync()  # the context is still usable
+
+
+def test_gate_up_integer_form_on_awkward_activations(q4b, orc, ctx):
+    """Fused gate/up at M <= 4 turns x into two 8-bit digits per value with a power-of-two step per group
+    (the default there; variant bit 4 keeps the fp16 form).  Rows that stress the digits: zeros, values around
+    the top of a binade (high digit at its limit), ties of the high digit, tiny and huge magnitudes, and one
+    outlier per group that pushes everything else into the low digit."""
+    n, k = 640, 1024
+    groups = k // 64
+    gq, gm = orc.synth_weight(51, 0, n, groups)
+    uq, um = orc.synth_weight(51, 1, n, groups)
+    gate, up = ctx.upload(gq, gm, n, groups), ctx.upload(uq, um, n, groups)
+    rng = np.random.default_rng(51)
+    base = rng.standard_normal((4, k)).astype(np.float32)
+    cases = {
+        "zeros and binade tops": np.stack([np.zeros(k, np.float32), np.where(base[1] > 0, 1.9990234, -1.9990234),
+                                           np.where(base[2] > 0, 0.99951172, 0.5), base[3]]),
+        "ties of the high digit": np.stack([np.round(base[0] * 8) / 8 + 0.0625, np.full(k, 1.5, np.float32),
+                                            np.full(k, -1.5, np.float32), np.round(base[3] * 16) / 16]),
+        "tiny and huge": np.stack([base[0] * 1e-4, base[1] * 3e-3, base[2] * 900.0, base[3] * 6000.0]),
+        "one outlier per group": np.stack([np.where(np.arange(k) % 64 == 5, 200.0, base[m] * 0.01)
+                                           for m in range(4)]).astype(np.float32),
+    }
+    for name, values in cases.items():
+        x = values.astype(np.float16)
+        for m in (1, 4):
+            _, ref = orc.gate_up_silu(gq, gm, uq, um, groups, x[:m], want32=False)
+            dx, dy = ctx.to_device(x[:m]), ctx.alloc(m * n * 4)
+            got = {}
+            try:
+                for variant in (0, 0x10):
+                    ctx.set_variant(variant)
+                    ctx.gate_up_silu(gate, up, dx.ptr, q4b.F16, m, dy.ptr, q4b.F32)
+                    got[variant] = dy.download(np.float32, (m, n))
+            finally:
+                ctx.set_variant(0)
+            for row in range(m):
+                scale = float(np.max(np.abs(ref[row])))
+                if scale == 0.0:
+                    assert not got[0][row].any() and not got[0x10][row].any(), name
+                    continue
+                for variant in (0, 0x10):
+                    error = float(np.max(np.abs(got[variant][row] - ref[row]))) / scale
+                    assert error <= 2e-3, (name, m, row, hex(variant), error)
+    gate.free()
+    up.free()
