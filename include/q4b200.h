@@ -185,7 +185,18 @@ int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int
                      const uint32_t *ldy, char *error_message, size_t error_capacity);
 /* Fused gate/up with SiLU-gate epilogue: out = silu(gate x) * (up x), replaces
  * qwen38_q4_gate_up_silu (qwen38_q4.metal:129-151, qwen38_m3_decode.m:643-651)
- * and the prefill pair + qwen38_prefill_silu_mul (:1019-1033). */
+ * and the prefill pair + qwen38_prefill_silu_mul (:1019-1033).
+ *
+ * At M <= 4 with fp16 x the kernel multiplies on the integer tensor pipe: every
+ * 64-column group of an activation row is taken as two signed 8-bit digits per
+ * value with one power-of-two step for the group (15 bits relative to the group's
+ * largest |x|; fp16 itself carries 11 per value), the sums of code x digit are
+ * exact integers, scale, step and bias are applied per group in fp32.  Measured
+ * max|y - ref| / max|ref| = 3e-5 .. 8e-5 on fp32 outputs (the fp16 form of the
+ * other kernels: 1e-6; both far inside 2e-3, and an fp16 output rounds at 5e-4).
+ * A row's result does not depend on M or on the other rows.  Infinite or NaN
+ * activations give undefined results in this form.  Bit 4 of
+ * q4b_context_set_variant (or Q4B_VARIANT) keeps the fp16 form here too. */
 int q4b_gate_up_silu(q4b_context *context, const q4b_weight *gate, const q4b_weight *up,
                      const void *x, int x_dtype, uint32_t m_rows, void *y, int y_dtype,
                      uint32_t ldy, char *error_message, size_t error_capacity);
