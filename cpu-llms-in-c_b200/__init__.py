@@ -9,7 +9,7 @@ works anywhere, but every compute entry point needs the CUDA library and a B200.
 from __future__ import annotations
 
 from .host import (  # noqa: F401
-    BF16, F16, F32, NONE, Q4Context, Q4Error, Q4Graph, Q4Barrier, Q4Sequence, Q4Weight, DeviceBuffer,
+    BF16, F16, F32, NONE, Q4Context, Q4Error, Q4Graph, Q4Barrier, Q4Comm, Q4Sequence, Q4Weight, DeviceBuffer,
     declared_symbols, library, library_path,
 )
 from .shapes import (  # noqa: F401

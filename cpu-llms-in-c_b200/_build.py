@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBRARY = os.path.join(HERE, "libq4b200.so")
-SOURCES = ["q4b_api.cu", "q4b_pack.cu", "q4b_gemv.cu", "q4b_gemm.cu", "q4b_comm.cu", "q4b_probe.cu", "q4b_decode.cu", "q4b_image.cu", "q4b_layer.cu"]
+SOURCES = ["q4b_api.cu", "q4b_pack.cu", "q4b_gemm.cu", "q4b_comm.cu", "q4b_probe.cu", "q4b_decode.cu", "q4b_image.cu", "q4b_layer.cu"]
 HEADERS = ["q4b_common.cuh", "q4b_kernels.h", os.path.join("..", "..", "include", "q4b200.h")]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC"]

@@ -43,15 +43,17 @@ struct q4b_weight {
     uint32_t rows_total;  // rows of the source matrix
     uint32_t row_begin;   // first source row held
     int device;
+    bool borrowed;        // a row range of another weight: the tile stream is not this handle's to free
 };
 
 struct q4b_sequence {
     std::vector<DecodeJob> jobs;
-    uint32_t m_rows, world, rank, epoch;
+    uint32_t m_rows, world, rank;
     int device;
     bool finalized;
     DecodeJob *device_jobs;
-    uint32_t *done;
+    uint32_t *done;        // [jobs][8] completion counters (kDoneStride words apart) + the epoch and exit words
+    size_t done_words;
     uint32_t *peer_done[kMaxPeers];
     float *scratch;
     uint32_t *counters;
@@ -255,7 +257,10 @@ int check_matmul_arguments(q4b_context *context, const q4b_weight *weight, const
 // Grow the context's split-K scratch to what a launch needs.  Never during
 // recording: an allocation cannot be captured, so the sequence must have run
 // once (or q4b_reserve_scratch been called) before q4b_graph_begin.
-int ensure_scratch(q4b_context *context, const GemvPlan &plan, char *error_message, size_t error_capacity) {
+struct ScratchNeed {
+    size_t scratch_bytes, counter_bytes;
+};
+int ensure_scratch(q4b_context *context, const ScratchNeed &plan, char *error_message, size_t error_capacity) {
     if (plan.scratch_bytes <= context->scratch_bytes && plan.counter_bytes <= context->counter_bytes) return Q4B_OK;
     if (context->capturing) {
         set_error(error_message, error_capacity,
@@ -287,7 +292,7 @@ int ensure_scratch(q4b_context *context, const GemvPlan &plan, char *error_messa
 }
 
 // M above the small-M kernel's limit: the tcgen05 GEMM, one launch per matrix
-int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_message, size_t error_capacity) {
+int run_tensor_core(q4b_context *context, const ProjectionArgs &args, char *error_message, size_t error_capacity) {
     const size_t K = (size_t)args.w[0].groups * kGroup;
     const void *x = args.x;
     if (args.x_dtype == kF32) {
@@ -354,12 +359,12 @@ int run_tensor_core(q4b_context *context, const GemvArgs &args, char *error_mess
     return Q4B_OK;
 }
 
-// one launch sequence for any M: GEMV kernel up to its row limit, row blocks above.
+// One projection at any M: the decode kernel up to its row limit, the tensor-core GEMM above.
 // With built_in_scratch the split-K scratch is the library's file-scope device
 // array and nothing is allocated, grown or freed.
-int run_projection(q4b_context *context, GemvArgs args, char *error_message, size_t error_capacity,
+int run_projection(q4b_context *context, ProjectionArgs args, char *error_message, size_t error_capacity,
                    bool built_in_scratch = false) {
-    const uint32_t limit = gemv_max_m();
+    const uint32_t limit = decode_max_m();
     const uint32_t total = args.m_rows;
     const size_t K = (size_t)args.w[0].groups * kGroup;
     // variant bit 15 keeps large M on the small-M kernel (row blocks of 16), for A/B runs
@@ -367,7 +372,7 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
         return run_tensor_core(context, args, error_message, error_capacity);
     }
     if (args.x_dtype == kBF16) {
-        // the small-M kernel multiplies fp16; bf16 activations go to the tensor-core kernel at every M
+        // the small-M kernel multiplies fp16 or integer digits; bf16 activations go to the tensor-core kernel at every M
         if (built_in_scratch) {
             set_error(error_message, error_capacity, "bf16 activations need q4b_matmul");
             return Q4B_BAD_ARGUMENT;
@@ -381,48 +386,74 @@ int run_projection(q4b_context *context, GemvArgs args, char *error_message, siz
         return Q4B_BAD_ARGUMENT;
     }
     for (uint32_t m0 = 0; m0 < total; m0 += limit) {
-        GemvArgs block = args;
-        block.m_rows = total - m0 < limit ? total - m0 : limit;
-        block.x = static_cast<const uint8_t *>(args.x) + (size_t)m0 * K * dtype_bytes(args.x_dtype);
+        const uint32_t m_rows = total - m0 < limit ? total - m0 : limit;
+        DecodeJob job = {};
         for (int s = 0; s < args.segments; ++s) {
-            block.y[s] = static_cast<uint8_t *>(args.y[s]) + (size_t)m0 * args.ldy[s] * dtype_bytes(args.y_dtype);
+            job.tiles[s] = args.w[s].tiles;
+            job.rows[s] = args.w[s].rows;
+            job.ldy[s] = args.ldy[s];
+            job.y[s][0] = static_cast<uint8_t *>(args.y[s]) + (size_t)m0 * args.ldy[s] * dtype_bytes(args.y_dtype);
         }
+        job.segments = (uint32_t)args.segments;
+        job.groups = args.w[0].groups;
+        if (args.fused_silu) {
+            job.fused = 1;
+            job.up_tiles = args.up.tiles;
+        }
+        job.x = static_cast<const uint8_t *>(args.x) + (size_t)m0 * K * dtype_bytes(args.x_dtype);
+        job.x_dtype = args.x_dtype;
+        job.y_dtype = args.y_dtype;
+        job.residual_dtype = args.residual_dtype;
+        job.ld_residual = args.ld_residual;
         if (args.residual != nullptr) {
-            block.residual = static_cast<const uint8_t *>(args.residual) +
-                             (size_t)m0 * args.ld_residual * dtype_bytes(args.residual_dtype);
+            job.residual = static_cast<const uint8_t *>(args.residual) +
+                           (size_t)m0 * args.ld_residual * dtype_bytes(args.residual_dtype);
         }
-        GemvPlan plan;
-        cudaError_t status = plan_gemv(block, context->variant, context->sm_count, &plan);
-        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv plan", status);
-        block.status = context->status_device;
+        DecodeGeometry geometry;
+        cudaError_t status = decode_geometry(m_rows, context->variant, context->sm_count, false, &geometry);
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "decode geometry", status);
+        ScratchNeed need = {};
+        plan_decode_job(&job, m_rows, geometry, &need.scratch_bytes, &need.counter_bytes);
+        float *scratch = nullptr;
+        uint32_t *counters = nullptr;
         if (built_in_scratch) {
             size_t scratch_bytes = 0, counter_bytes = 0;
-            status = gemv_static_scratch(&block.scratch, &block.counters, &scratch_bytes, &counter_bytes);
+            status = decode_static_scratch(&scratch, &counters, &scratch_bytes, &counter_bytes);
             if (status != cudaSuccess) return device_failure(error_message, error_capacity, "built-in scratch", status);
-            if (plan.scratch_bytes > scratch_bytes || plan.counter_bytes > counter_bytes) {
+            if (need.scratch_bytes > scratch_bytes || need.counter_bytes > counter_bytes) {
                 set_error(error_message, error_capacity,
                           "this shape needs %zu bytes of scratch and %zu of counters; the built-in scratch holds "
                           "%zu and %zu -- use q4b_matmul, which allocates",
-                          plan.scratch_bytes, plan.counter_bytes, scratch_bytes, counter_bytes);
+                          need.scratch_bytes, need.counter_bytes, scratch_bytes, counter_bytes);
                 return Q4B_BAD_ARGUMENT;
             }
             // the array keeps whatever the previous call left: the counters must start at zero
-            status = cudaMemsetAsync(block.counters, 0, plan.counter_bytes, context->stream);
-            if (status != cudaSuccess) return device_failure(error_message, error_capacity, "counter reset", status);
+            if (need.counter_bytes > 0) {
+                status = cudaMemsetAsync(counters, 0, need.counter_bytes, context->stream);
+                if (status != cudaSuccess) return device_failure(error_message, error_capacity, "counter reset", status);
+            }
         } else {
-            int code = ensure_scratch(context, plan, error_message, error_capacity);
+            int code = ensure_scratch(context, need, error_message, error_capacity);
             if (code != Q4B_OK) return code;
-            block.scratch = context->scratch;
-            block.counters = context->counters;
+            scratch = context->scratch;
+            counters = context->counters;
         }
-        status = launch_gemv(block, plan, context->variant, context->stream);
+        status = launch_decode(job, m_rows, geometry, context->variant, scratch, counters, context->status_device,
+                               context->stream);
         if (!context->capturing) ++context->launches;  // recorded launches count at replay
-        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "gemv launch", status);
+        if (status != cudaSuccess) return device_failure(error_message, error_capacity, "decode launch", status);
     }
     return Q4B_OK;
 }
 
 }  // namespace
+
+namespace q4b {
+int context_device(const q4b_context *context) { return context->device; }
+void context_count_launch(q4b_context *context) {
+    if (!context->capturing) ++context->launches;
+}
+}  // namespace q4b
 
 extern "C" {
 
@@ -546,6 +577,16 @@ int q4b_copy_to_host(q4b_context *context, void *host_destination, const void *d
     return Q4B_OK;
 }
 
+int q4b_copy_2d(q4b_context *context, void *destination, size_t destination_pitch, const void *source,
+                size_t source_pitch, size_t row_bytes, size_t rows, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    Q4B_CUDA(cudaMemcpy2DAsync(destination, destination_pitch, source, source_pitch, row_bytes, rows,
+                               cudaMemcpyDeviceToDevice, context->stream),
+             "strided copy");
+    return Q4B_OK;
+}
+
 int q4b_weight_upload(q4b_context *context, const void *quants, const void *meta, uint32_t rows,
                       uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
                       q4b_weight **weight, char *error_message, size_t error_capacity) {
@@ -639,8 +680,47 @@ void q4b_weight_free(q4b_context *context, q4b_weight *weight) {
         cudaSetDevice(context->device);
         cudaStreamSynchronize(context->stream);
     }
-    cudaFree(const_cast<uint8_t *>(weight->view.tiles));
+    if (!weight->borrowed) cudaFree(const_cast<uint8_t *>(weight->view.tiles));
     delete weight;
+}
+
+int q4b_weight_rows(const q4b_weight *weight, uint32_t row_begin, uint32_t row_count, q4b_weight **rows,
+                    char *error_message, size_t error_capacity) {
+    if (weight == nullptr || rows == nullptr || row_count == 0 || row_begin % 128 != 0 ||
+        row_begin >= weight->view.rows || row_count > weight->view.rows - row_begin) {
+        set_error(error_message, error_capacity,
+                  "a row range starts at a multiple of 128 rows and lies inside the weight");
+        return Q4B_BAD_ARGUMENT;
+    }
+    q4b_weight *result = new (std::nothrow) q4b_weight(*weight);
+    if (result == nullptr) return Q4B_LOAD_FAILURE;
+    result->view.tiles = weight->view.tiles + (size_t)(row_begin / 64) * weight->view.groups * kUnitBytes;
+    result->view.rows = row_count;
+    result->view.row_tiles = ceil_div(row_count, kTileRows);
+    result->row_begin = weight->row_begin + row_begin;
+    result->device_bytes = 0;
+    result->borrowed = true;
+    *rows = result;
+    return Q4B_OK;
+}
+
+int q4b_matmul_rows(q4b_context *context, const q4b_weight *weight, const uint32_t *row_ids, uint32_t count,
+                    const void *x, int x_dtype, uint32_t m_rows, void *y, int y_dtype, uint32_t ldy,
+                    char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weight == nullptr || row_ids == nullptr || x == nullptr || y == nullptr || weight->device != context->device ||
+        m_rows == 0 || m_rows > 16 || ldy < count || !valid_activation_dtype(x_dtype) ||
+        !valid_activation_dtype(y_dtype) || !aligned16(x)) {
+        set_error(error_message, error_capacity,
+                  "weight, row list, x or y missing; 1..16 activation rows, fp16 or fp32, ldy >= count, x 16-byte aligned");
+        return Q4B_BAD_ARGUMENT;
+    }
+    cudaError_t status = launch_matmul_rows(weight->view, row_ids, count, weight->row_begin, x, x_dtype, m_rows, y,
+                                            y_dtype, ldy, context->stream);
+    if (!context->capturing) ++context->launches;
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "listed-rows matmul", status);
+    return Q4B_OK;
 }
 
 int q4b_weight_info(const q4b_weight *weight, uint32_t *rows, uint32_t *groups_per_row,
@@ -817,7 +897,7 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
                   "residual must be fp16 or fp32 (bf16 or fp32 beside bf16 activations) with ld >= rows");
         return Q4B_BAD_ARGUMENT;
     }
-    GemvArgs args = {};
+    ProjectionArgs args = {};
     args.w[0] = weight->view;
     args.y[0] = y;
     args.ldy[0] = ldy;
@@ -840,7 +920,7 @@ int q4b_matmul_no_alloc(q4b_context *context, const q4b_weight *weight, const vo
     code = check_matmul_arguments(context, weight, x, x_dtype, m_rows, y, y_dtype, ldy, error_message,
                                   error_capacity);
     if (code != Q4B_OK) return code;
-    GemvArgs args = {};
+    ProjectionArgs args = {};
     args.w[0] = weight->view;
     args.y[0] = y;
     args.ldy[0] = ldy;
@@ -862,7 +942,7 @@ int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int
         set_error(error_message, error_capacity, "a group holds 1..%d matrices", kMaxSegments);
         return Q4B_BAD_ARGUMENT;
     }
-    GemvArgs args = {};
+    ProjectionArgs args = {};
     for (int s = 0; s < count; ++s) {
         code = check_matmul_arguments(context, weights[s], x, x_dtype, m_rows, y[s], y_dtype, ldy[s],
                                       error_message, error_capacity);
@@ -897,7 +977,7 @@ int q4b_gate_up_silu(q4b_context *context, const q4b_weight *gate, const q4b_wei
         set_error(error_message, error_capacity, "gate and up must have the same shape and device");
         return Q4B_BAD_ARGUMENT;
     }
-    GemvArgs args = {};
+    ProjectionArgs args = {};
     args.w[0] = gate->view;
     args.up = up->view;
     args.fused_silu = 1;
@@ -1029,12 +1109,14 @@ int q4b_sequence_create(q4b_context *context, uint32_t m_rows, uint32_t world, u
 }
 
 static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights, int count, const q4b_weight *up,
-                        const void *x, void *const *y, const uint32_t *ldy, int y_dtype, char *error_message,
+                        const void *x, int x_dtype, void *const *y, const uint32_t *ldy, int y_dtype,
+                        const void *residual, int residual_dtype, uint32_t ld_residual, char *error_message,
                         size_t error_capacity) {
     if (sequence == nullptr || sequence->finalized || weights == nullptr || y == nullptr || ldy == nullptr ||
-        x == nullptr || count < 1 || count > kMaxSegments || !valid_activation_dtype(y_dtype) || !aligned16(x)) {
-        set_error(error_message, error_capacity, "invalid job (1..%d matrices, 16-byte aligned fp16 x, fp16/fp32 y)",
-                  kMaxSegments);
+        x == nullptr || count < 1 || count > kMaxSegments || !valid_activation_dtype(y_dtype) ||
+        !valid_activation_dtype(x_dtype) || !aligned16(x)) {
+        set_error(error_message, error_capacity,
+                  "invalid job (1..%d matrices, 16-byte aligned fp16 or fp32 x, fp16 or fp32 y)", kMaxSegments);
         return Q4B_BAD_ARGUMENT;
     }
     DecodeJob job = {};
@@ -1057,10 +1139,18 @@ static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights
         job.up_tiles = up->view.tiles;
         job.fused = 1;
     }
+    if (residual != nullptr && (!valid_activation_dtype(residual_dtype) || ld_residual < weights[0]->view.rows)) {
+        set_error(error_message, error_capacity, "residual must be fp16 or fp32 with ld >= rows");
+        return Q4B_BAD_ARGUMENT;
+    }
     job.x = x;
+    job.x_dtype = x_dtype;
+    job.residual = residual;
+    job.residual_dtype = residual != nullptr ? residual_dtype : (int)kNone;
+    job.ld_residual = ld_residual;
     job.groups = weights[0]->view.groups;
     job.segments = (uint32_t)count;
-    job.y_dtype = (uint32_t)y_dtype;
+    job.y_dtype = y_dtype;
     sequence->jobs.push_back(job);
     return Q4B_OK;
 }
@@ -1068,7 +1158,15 @@ static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights
 int q4b_sequence_add_matmul(q4b_sequence *sequence, const q4b_weight *const *weights, int count, const void *x,
                             void *const *y, const uint32_t *ldy, int y_dtype, char *error_message,
                             size_t error_capacity) {
-    return sequence_add(sequence, weights, count, nullptr, x, y, ldy, y_dtype, error_message, error_capacity);
+    return sequence_add(sequence, weights, count, nullptr, x, Q4B_F16, y, ldy, y_dtype, nullptr, Q4B_NONE, 0,
+                        error_message, error_capacity);
+}
+
+int q4b_sequence_add_projection(q4b_sequence *sequence, const q4b_weight *weight, const void *x, int x_dtype, void *y,
+                                int y_dtype, uint32_t ldy, const void *residual, int residual_dtype,
+                                uint32_t ld_residual, char *error_message, size_t error_capacity) {
+    return sequence_add(sequence, &weight, 1, nullptr, x, x_dtype, &y, &ldy, y_dtype, residual, residual_dtype,
+                        ld_residual, error_message, error_capacity);
 }
 
 int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, const q4b_weight *up, const void *x,
@@ -1077,7 +1175,8 @@ int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, con
         set_error(error_message, error_capacity, "up is NULL");
         return Q4B_BAD_ARGUMENT;
     }
-    return sequence_add(sequence, &gate, 1, up, x, &y, &ldy, y_dtype, error_message, error_capacity);
+    return sequence_add(sequence, &gate, 1, up, x, Q4B_F16, &y, &ldy, y_dtype, nullptr, Q4B_NONE, 0, error_message,
+                        error_capacity);
 }
 
 int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t segment, uint32_t peer_rank,
@@ -1105,57 +1204,45 @@ int q4b_sequence_finalize(q4b_context *context, q4b_sequence *sequence, char *er
         set_error(error_message, error_capacity, "nothing to finalize");
         return Q4B_BAD_ARGUMENT;
     }
-    const char *stages_text = getenv("Q4B_SEQUENCE_STAGES");
-    uint32_t stages = stages_text != nullptr ? (uint32_t)strtoul(stages_text, nullptr, 0) : 2u;
-    uint32_t ctas = 0, max_local = 2;
-    size_t smem_bytes = 0, scratch_bytes = 0, counter_bytes = 0;
-    for (int attempt = 0; attempt < 2; ++attempt) {
-        Q4B_CUDA(sequence_geometry(sequence->m_rows, context->sm_count, stages, max_local, &ctas, &smem_bytes),
-                 "sequence geometry");
-        uint32_t needed_local = 1;
-        scratch_bytes = counter_bytes = 0;
-        for (DecodeJob &job : sequence->jobs) {
-            size_t s = 0, c = 0;
-            plan_decode_job(&job, sequence->m_rows, ctas, &s, &c);
-            if (s > scratch_bytes) scratch_bytes = s;
-            if (c > counter_bytes) counter_bytes = c;
-            if (job.local_blocks > needed_local) needed_local = job.local_blocks;
-            if (attempt == 0) {
-                const uint32_t own = job.block_begin[kMaxSegments];
-                if (job.expected_blocks == 0) job.expected_blocks = own * sequence->world;
-                if (job.expected_blocks < own) {
-                    set_error(error_message, error_capacity, "a job's block count over all ranks is below this rank's own");
-                    return Q4B_BAD_ARGUMENT;
-                }
-            }
+    SequenceLaunch &launch = sequence->launch;
+    Q4B_CUDA(decode_geometry(sequence->m_rows, context->variant, context->sm_count, true, &launch.geometry),
+             "sequence geometry");
+    size_t scratch_bytes = 0, counter_bytes = 0;
+    for (DecodeJob &job : sequence->jobs) {
+        size_t s = 0, c = 0;
+        plan_decode_job(&job, sequence->m_rows, launch.geometry, &s, &c);
+        if (s > scratch_bytes) scratch_bytes = s;
+        if (c > counter_bytes) counter_bytes = c;
+        uint32_t own = 0;
+        for (uint32_t q = 0; q < job.segments; ++q) own += ceil_div(job.rows[q], 64);
+        if (job.expected_blocks == 0) job.expected_blocks = own * sequence->world;
+        if (job.expected_blocks < own) {
+            set_error(error_message, error_capacity, "a job's block count over all ranks is below this rank's own");
+            return Q4B_BAD_ARGUMENT;
         }
-        if (needed_local <= max_local) break;
-        max_local = needed_local;
     }
     const size_t job_bytes = sequence->jobs.size() * sizeof(DecodeJob);
+    // completion counters, then one line for the epoch word and one for the exit count
+    sequence->done_words = (sequence->jobs.size() * 8 + 2) * kDoneStride;
     cudaError_t status = cudaMalloc(&sequence->device_jobs, job_bytes);
-    if (status == cudaSuccess) status = cudaMalloc(&sequence->done, sequence->jobs.size() * sizeof(uint32_t));
+    if (status == cudaSuccess) status = cudaMalloc(&sequence->done, sequence->done_words * sizeof(uint32_t));
     if (status == cudaSuccess) status = cudaMalloc(&sequence->scratch, scratch_bytes + 256);
     if (status == cudaSuccess) status = cudaMalloc(&sequence->counters, counter_bytes + 256);
     if (status == cudaSuccess) status = cudaMemcpy(sequence->device_jobs, sequence->jobs.data(), job_bytes, cudaMemcpyHostToDevice);
-    if (status == cudaSuccess) status = cudaMemset(sequence->done, 0, sequence->jobs.size() * sizeof(uint32_t));
+    if (status == cudaSuccess) status = cudaMemset(sequence->done, 0, sequence->done_words * sizeof(uint32_t));
     if (status == cudaSuccess) status = cudaMemset(sequence->counters, 0, counter_bytes + 256);
     if (status != cudaSuccess) return device_failure(error_message, error_capacity, "sequence buffers", status);
     sequence->peer_done[sequence->rank] = sequence->done;
-    SequenceLaunch &launch = sequence->launch;
     launch.jobs = sequence->device_jobs;
     launch.job_count = (uint32_t)sequence->jobs.size();
     launch.m_rows = sequence->m_rows;
-    launch.stages = stages;
-    launch.ctas = ctas;
-    launch.max_local_blocks = max_local;
     launch.world = sequence->world;
-    launch.rank = sequence->rank;
     launch.done = sequence->done;
+    launch.epoch = sequence->done + sequence->jobs.size() * 8 * kDoneStride;
+    launch.exit_count = launch.epoch + kDoneStride;
     launch.scratch = sequence->scratch;
     launch.counters = sequence->counters;
     launch.status = context->status_device;
-    launch.smem_bytes = smem_bytes;
     sequence->finalized = true;
     return Q4B_OK;
 }
@@ -1186,7 +1273,6 @@ int q4b_sequence_launch(q4b_context *context, q4b_sequence *sequence, char *erro
         }
         sequence->launch.peer_done[r] = sequence->peer_done[r];
     }
-    sequence->launch.epoch = ++sequence->epoch;
     Q4B_CUDA(launch_sequence(sequence->launch, context->stream), "sequence launch");
     if (!context->capturing) ++context->launches;
     return Q4B_OK;

@@ -1,79 +1,125 @@
-// Decode sequences: a list of Q4 projections executed by ONE persistent launch.
+// Decode GEMV (M = 1) and small-M verify GEMM (M <= 16) on the Q4 tile stream: one
+// kernel, launched either once per projection or once for a whole chain of
+// projections ("sequence": one persistent cooperative grid walks a job table).
 //
-// The reference encodes a whole token -- every layer's fixed chain of Q4 matmuls --
-// into one command buffer (qwen38_m3_decode.m:1614-1690).  At M = 1 on a B200 each
-// projection streams for only a few microseconds, so a kernel boundary per
-// projection (drain, launch, refill the pipeline) costs as much as the work.  Here
-// the chain is a job table in device memory and one cooperative grid walks it:
+// Replaces the reference's row kernels: qwen38_q4_matvec / qwen38_q4_gate_up_silu
+// (qwen38_q4.metal:111-151), the fused in-projections (qwen38_layer.metal:71-100,
+// qwen38_attention.metal:28-52), the residual second projections
+// (qwen38_layer.metal:193-255), the lm_head (qwen38_global.metal:37-61) and the
+// small-batch verify GEMMs (qwen38_prefill.metal:144-248, :1090-1363); the sequence
+// form is the counterpart of the reference encoding a whole token into one command
+// buffer (qwen38_m3_decode.m:1614-1690).
 //
-//   * the producer warp of every CTA streams job after job through the same
-//     shared-memory ring (cp.async.bulk + mbarrier) without ever draining it:
-//     weights never depend on earlier jobs, so the next job's tiles arrive while
-//     this job's sums are still being combined;
-//   * jobs form a chain: before a CTA reads x of job j it waits (bounded) until
-//     every CTA has published job j-1's outputs -- the same ordering as separate
-//     dependent launches, at the cost of one counter in L2;
-//   * the per-job work split, arithmetic and cross-CTA sums are those of the
-//     single-projection kernel (q4b_gemv.cu): mma.sync m16n8k16 on the exact codes,
-//     per-group scale/bias in fp32, deterministic slot sums for split row blocks.
+// HBM bound: every weight byte is read once.  Work is cut into units: one "pair
+// block" (128 output rows = two 64-row blocks of the tile stream, or 64 gate rows
+// and the same 64 up rows when fused) times one contiguous range of K groups.  A
+// CTA has three kinds of warps:
 //
-// With peers set (column-parallel ranks, one process per GPU) the epilogue stores
-// this rank's output slice into every rank's copy of y over NVLink and the
-// completion counter of every rank is advanced, so the gather is part of the same
-// kernel: no collective call per projection.
+//   * warp 8, the weight producer: one thread streams the CTA's units -- job after
+//     job in a sequence, never draining -- through a shared-memory ring with bulk
+//     asynchronous copies (cp.async.bulk + mbarrier), 8 groups x 2 blocks = 36 KB
+//     per stage.  Weights never depend on earlier work, so the ring runs ahead of
+//     the consumers across job boundaries and kernel boundaries (programmatic
+//     dependent launch): the wait for the previous projection's output is hidden
+//     behind loads that are needed anyway.
+//   * warp 9, the activation loader: turns x, group by group, into the B operands
+//     the consumers feed to the tensor pipe and parks them in a small ring of its
+//     own.  For M <= 4 that is the integer form: two signed 8-bit digits per value
+//     with one power-of-two step per (group, activation row), 15 bits relative to
+//     the group's largest value (fp16 itself carries 11 per value), so the codes go
+//     to the tensor pipe as bytes (mma.sync m16n8k32 u8 x s8, exact s32 sums).  For
+//     M = 5..16 it is the fp16 form (codes as fp16 subnormal bit patterns,
+//     m16n8k16, fp32 accumulate).  fp32 activations are scaled per group by a power
+//     of two first, so their magnitude does not matter.  In a sequence this warp
+//     is also the one that waits for the previous job's outputs.
+//   * warps 0..7, the consumers: warp w owns ONE 16-row tile of the pair block
+//     (tile w & 3 of block w >> 2) and walks the unit's groups with it, so a row's
+//     sum lives in one lane from the first group to the last: no reduction inside
+//     the CTA, no barrier between units.  Per group: y += (s * step) * (q . x')
+//     + b * sum(x) in fp32, the reference's arithmetic re-associated per group.
+//
+// Units that share a pair block (K split over CTAs when a job has fewer pair
+// blocks than the grid has CTAs) park their sums in global slots; the last warp
+// to arrive for a tile adds the slots in part order -- results do not depend on
+// timing -- applies the epilogue (SiLU gate, residual) and stores y, on every
+// rank's copy when the ranks of a column-parallel job share outputs.  In a
+// sequence it then advances the job's completion counters; the loaders of the next
+// job start when every tile of every rank has been counted.
+//
+// Every wait is bounded.  The first wait that expires sets a CTA-wide flag and a
+// code in the status word; from then on no wait in that CTA waits, every role
+// walks the rest of its control flow (so every barrier still gets its arrivals),
+// and the host turns the status word into an error.
 #include "q4b_kernels.h"
 
-#include <cstdlib>
-
-#include <cooperative_groups.h>
-
-#ifdef Q4B_TRACE
-__device__ long long q4b_decode_trace[1024 * 8];
-#define SQ_CLOCK() clock64()
-#define SQ_ADD(slot, since) do { if (threadIdx.x == 0) q4b_decode_trace[blockIdx.x * 8 + (slot)] += clock64() - (since); } while (0)
-extern "C" int q4b_decode_trace_read(long long *out, int count) {
-    return (int)cudaMemcpyFromSymbol(out, q4b_decode_trace, sizeof(long long) * count);
-}
-#else
-#define SQ_CLOCK() 0ll
-#define SQ_ADD(slot, since) do { } while (0)
-#endif
+#include <mutex>
 
 namespace q4b {
 
 namespace {
 
-constexpr int kSeqMaxStages = 8;
-constexpr int kSeqWarps = 8;  // consumer warps; warp 8 produces
-constexpr long long kSeqWaitLimit = 4000000000ll;
+constexpr int kConsumers = 8;                 // consumer warps
+constexpr int kProducerWarp = 8, kLoaderWarp = 9;  // loader warps: 9 and 10, one per slot of the activation ring
+constexpr int kLoaders = 2;
+constexpr int kDecodeThreads = 32 * (kConsumers + 1 + kLoaders);
+constexpr uint32_t kStageGroups = 8;          // groups per ring stage, both blocks of the pair
+constexpr uint32_t kStageBytes = 2 * kStageGroups * kUnitBytes;  // 36,864
+constexpr uint32_t kChunkGroups = 4;          // groups per hand-over of activations
+constexpr uint32_t kChunks = 2;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // every wait gives up after ~2 s of SM clocks
 
-struct SeqParams {
-    const DecodeJob *jobs;
+// MODE 0: integer form, M <= 4.  MODE 1 / 2: fp16 form, M <= 8 / M <= 16.
+template <int MODE> struct Form;
+template <> struct Form<0> {
+    static constexpr int NT = 1, VALS = 2, STAGES = 3;
+    static constexpr uint32_t XGROUP = 544;   // 512 B of digit fragments + 4 x {step, sum}
+    static constexpr uint32_t XCHG_VALS = 1;  // values per lane handed from an up warp to its gate warp at a time
+};
+template <> struct Form<1> {
+    static constexpr int NT = 1, VALS = 4, STAGES = 2;
+    static constexpr uint32_t XGROUP = 1088;  // 1024 B of fp16 fragments + 8 x {step, sum}
+    static constexpr uint32_t XCHG_VALS = 4;
+};
+template <> struct Form<2> {
+    static constexpr int NT = 2, VALS = 8, STAGES = 2;
+    static constexpr uint32_t XGROUP = 2176;
+    static constexpr uint32_t XCHG_VALS = 8;
+};
+
+template <int MODE> constexpr uint32_t smem_bytes_of() {
+    return 128 + Form<MODE>::STAGES * kStageBytes + kChunks * kChunkGroups * Form<MODE>::XGROUP +
+           4 * 32 * Form<MODE>::XCHG_VALS * 4;
+}
+
+struct PassParams {
+    DecodeJob job;                   // one projection per launch: the job itself
+    const DecodeJob *jobs;           // sequence: the job table in device memory
     uint32_t job_count;
-    uint32_t stages;
     uint32_t m_rows;
-    uint32_t max_local_blocks;
-    uint32_t world;           // ranks that publish into `done` (1 without peers)
-    uint32_t rank;
-    uint32_t epoch;           // launches so far, this one included: `done` counts up across launches
-    uint32_t *done;           // [job_count] CTAs (of all ranks) that published the job's outputs
-    uint32_t *peer_done[kMaxPeers];  // the same array on every rank (index `rank` = own)
+    uint32_t world;
+    uint32_t *epoch;                 // sequence: launches completed so far (device word)
+    uint32_t *exit_count;            // sequence: CTAs of this launch that have finished
+    uint32_t *done;                  // sequence: [job][8] completion counters, kDoneStride words apart
+    uint32_t *peer_done[kMaxPeers];  // the same array on every rank (own rank included)
     float *scratch;
     uint32_t *counters;
     uint32_t *status;
 };
 
-__device__ inline uint32_t sq_smem_u32(const void *pointer) { return (uint32_t)__cvta_generic_to_shared(pointer); }
-__device__ inline void sq_mbar_init(uint32_t bar, uint32_t count) {
+// ---------------------------------------------------------------------------
+// small PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ inline uint32_t smem_u32(const void *pointer) { return (uint32_t)__cvta_generic_to_shared(pointer); }
+__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ inline void sq_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+__device__ inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ inline void sq_mbar_arrive(uint32_t bar) {
+__device__ inline void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ inline bool sq_try_wait(uint32_t bar, uint32_t parity) {
+__device__ inline bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -84,22 +130,29 @@ __device__ inline bool sq_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-__device__ inline bool sq_wait(uint32_t bar, uint32_t parity) {  // false when the wait expired
-    if (sq_try_wait(bar, parity)) return true;
+// Bounded wait.  Once any wait of the CTA has expired (*failed != 0) nobody waits any more.
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *failed, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*failed != 0) return false;
     const long long start = clock64();
-    while (!sq_try_wait(bar, parity)) {
-        if (clock64() - start > kSeqWaitLimit) return false;
+    while (!mbar_try_wait(bar, parity)) {
+        if (*failed != 0) return false;
+        if (clock64() - start > kWaitLimitCycles) {
+            *failed = code;
+            return false;
+        }
     }
     return true;
 }
-__device__ inline void sq_bulk_copy(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar) {
+__device__ inline void bulk_copy_to_shared(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(destination), "l"(source), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ inline void sq_consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ inline void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
-__device__ inline void sq_mma(float d[4], const uint32_t a[4], uint32_t b0, uint32_t b1, bool first) {
+// D = A * B + C (C zero when first), fp16 operands, fp32 accumulate
+__device__ inline void mma_16816(float d[4], const uint32_t a[4], uint32_t b0, uint32_t b1, bool first) {
     if (first) {
         asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
             "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -112,540 +165,905 @@ __device__ inline void sq_mma(float d[4], const uint32_t a[4], uint32_t b0, uint
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
 }
-
-__device__ inline uint32_t sq_cta_of_unit(uint32_t unit, uint32_t share, uint32_t extra) {
-    const uint32_t boundary = extra * (share + 1);
-    return unit < boundary ? unit / (share + 1) : extra + (unit - boundary) / share;
-}
-
-// unit range [u0, u0 + range) of CTA `cta` in job `job`
-__device__ inline void sq_range(const DecodeJob &job, uint32_t cta, uint32_t &u0, uint32_t &range) {
-    if (cta >= job.active_ctas) {
-        u0 = 0;
-        range = 0;
-    } else if (job.parts > 0) {
-        const uint32_t block = cta / job.parts, j = cta % job.parts;
-        const uint32_t from = job.groups * j / job.parts, to = job.groups * (j + 1) / job.parts;
-        u0 = block * job.groups + from;
-        range = to - from;
+// u8 x s8 -> s32, m16n8k32: codes as bytes against activations as signed 8-bit digits
+__device__ inline void mma_16832_u8s8(int d[4], const uint32_t a[4], uint32_t b0, uint32_t b1, bool first) {
+    if (first) {
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
     } else {
-        u0 = cta * job.units_per_cta + min(cta, job.units_extra);
-        range = job.units_per_cta + (cta < job.units_extra ? 1u : 0u);
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
 }
 
-__device__ inline int sq_segment_of(const DecodeJob &job, uint32_t grb) {
-    int segment = 0;
+// ---------------------------------------------------------------------------
+// geometry of a job, the same in every role
+// ---------------------------------------------------------------------------
+struct Unit {
+    uint32_t pair;      // pair block, counted over the job's segments
+    uint32_t part;      // which K range of it
+    uint32_t g0, g1;    // groups [g0, g1)
+    int segment;
+    uint32_t local;     // pair block inside its segment
+    bool has_b;         // the pair's second block exists (always when fused)
+};
+
+__device__ inline Unit unit_of(const DecodeJob &job, uint32_t index) {
+    Unit u;
+    u.pair = index / job.parts;
+    u.part = index % job.parts;
+    u.g0 = job.groups * u.part / job.parts;
+    u.g1 = job.groups * (u.part + 1) / job.parts;
+    u.segment = 0;
 #pragma unroll
     for (int q = 1; q < kMaxSegments; ++q) {
-        if (q < (int)job.segments && grb >= job.block_begin[q]) segment = q;
+        if (q < (int)job.segments && u.pair >= job.pair_begin[q]) u.segment = q;
     }
-    return segment;
+    u.local = u.pair - job.pair_begin[u.segment];
+    u.has_b = job.fused != 0 || 2 * u.local + 1 < ceil_div(job.rows[u.segment], 64);
+    return u;
 }
 
+// ---------------------------------------------------------------------------
+// the activation loaders' work (all 32 lanes of a loader warp)
+// ---------------------------------------------------------------------------
+// Where a loader stands in the CTA's work: job, unit, first group of the next chunk, chunks so far.
+struct Cursor {
+    uint32_t j, index, g, xi;
+    Unit u;
+    bool have_unit, valid;
+};
 
-// NT: 8-column output tiles per warp (M <= 8*NT).  Warps 0..7 consume, warp 8
-// produces.  A ring stage holds 16 sub-units of 2304 bytes of ONE 64-row block:
-// 16 consecutive groups, or 8 groups of gate followed by the same 8 groups of up.
-// Consumer warp w takes sub-units w and w + 8.
+template <bool SEQ>
+__device__ inline void cursor_settle(Cursor &c, const PassParams &p, uint32_t job_count, uint32_t cta, uint32_t ctas) {
+    for (;;) {
+        if (c.j >= job_count) {
+            c.valid = false;
+            return;
+        }
+        const DecodeJob &job = SEQ ? p.jobs[c.j] : p.job;
+        if (c.index < job.units) {
+            if (!c.have_unit) {
+                c.u = unit_of(job, c.index);
+                c.g = c.u.g0;
+                c.have_unit = true;
+            }
+            if (c.g < c.u.g1) {
+                c.valid = true;
+                return;
+            }
+            c.index += ctas;
+            c.have_unit = false;
+        } else {
+            ++c.j;
+            c.index = cta;
+            c.have_unit = false;
+        }
+    }
+}
+template <bool SEQ>
+__device__ inline void cursor_advance(Cursor &c, const PassParams &p, uint32_t job_count, uint32_t cta, uint32_t ctas) {
+    c.g += kChunkGroups;
+    ++c.xi;
+    cursor_settle<SEQ>(c, p, job_count, cta, ctas);
+}
+
+// 16 consecutive fp16 activations of this lane in one group (8 registers), zeros when not `live`
+__device__ inline void fetch_x16(const void *x, size_t element, bool live, uint32_t raw[8]) {
+    uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+    if (live) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(x) + element);
+        lo = __ldcg(p);
+        hi = __ldcg(p + 1);
+    }
+    raw[0] = lo.x; raw[1] = lo.y; raw[2] = lo.z; raw[3] = lo.w;
+    raw[4] = hi.x; raw[5] = hi.y; raw[6] = hi.z; raw[7] = hi.w;
+}
+__device__ inline void fetch_x32(const void *x, size_t element, bool live, float v[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (live) f = __ldcg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + element) + i);
+        v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+    }
+}
+
+// Integer form.  Lane (gid, t): activation row m = gid >> 1, digit gid & 1 (0 high, 1 low), the 16 columns
+// 16 t .. 16 t + 15 of the group -- the columns this lane's code words cover in a tile.  A slot receives:
+//   [lane * 16, +16)  the four B registers of the two m16n8k32 MMAs of a tile (column n = 2 m + digit),
+//                     bytes of register i in the order of the code bytes of word i: columns 4i, 4i+2, 4i+1, 4i+3
+//   [512 + 8 m, +8)   {step, sum}: one unit of the low digit as a float, and the sum of the group's 64 values
+//                     as the digits represent them (exact)
+// A group whose largest magnitude is infinite, NaN (or, for fp32 input, 2^100 or more) gets step = NaN, so
+// that every output row of that activation row comes out NaN as the reference's arithmetic would have it.
+//
+// fp16 input: x * 2^(13-e) = 256 hi + lo with v = x * 2^(5-e) in (-64, 64); hi = v rounded to nearest in the
+// 1536 binade of fp16 (one unit per ulp: the digit is the low byte of the sum), lo = 256 (v - hi) exactly, in
+// [-128, 128], capped at 127 (a tie leaves 128: one unit of error, 2^-14 of the group's top) and rounded the
+// same way.
+__device__ inline void digits_of_f16(const uint32_t raw[8], bool low_digit, uint32_t b[4], float &step_here) {
+    // largest |x| of the 64 columns by bit pattern: NaN patterns sort above infinity, infinity above the rest
+    uint32_t big = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) big = __vmaxu2(big, raw[i] & 0x7fff7fffu);
+    uint32_t top = max(big & 0xffffu, big >> 16);
+    top = max(top, __shfl_xor_sync(0xffffffffu, top, 1));
+    top = max(top, __shfl_xor_sync(0xffffffffu, top, 2));
+    const bool finite = top < 0x7c00u;
+    int e = (int)(top >> 10) - 15;  // largest |x| in [2^e, 2^(e+1)) (subnormals: below 2^-14)
+    e = min(max(e, -10), 15);       // 2^(5-e) must be an fp16; smaller groups keep fewer bits, of a tiny value
+    const float factor = __uint_as_float((uint32_t)(127 + 5 - e) << 23);
+    step_here = finite ? __uint_as_float((uint32_t)(127 + e - 13) << 23) : __uint_as_float(0x7fc00000u);
+    const __half2 f_hi = __float2half2_rn(factor);
+    const __half2 magic = __float2half2_rn(1536.0f), times256 = __float2half2_rn(256.0f);
+    const __half2 cap = __float2half2_rn(127.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t digit[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t bits = finite ? raw[2 * i + h] : 0u;
+            const __half2 x2 = *reinterpret_cast<const __half2 *>(&bits);
+            const __half2 v = __hmul2(x2, f_hi);
+            const __half2 hi_m = __hadd2(v, magic);
+            const __half2 hi = __hsub2(hi_m, magic);
+            const __half2 lo = __hmul2(__hsub2(v, hi), times256);
+            const __half2 lo_m = __hadd2(__hmin2(lo, cap), magic);
+            digit[h] = low_digit ? *reinterpret_cast<const uint32_t *>(&lo_m)
+                                 : *reinterpret_cast<const uint32_t *>(&hi_m);
+        }
+        b[i] = __byte_perm(digit[0], digit[1], 0x6240);
+    }
+}
+// fp32 input: the same digits from v = x * 2^(5-e) in fp32, e the exponent of the group's largest magnitude
+__device__ inline void digits_of_f32(const float v[16], bool low_digit, uint32_t b[4], float &step_here) {
+    uint32_t big = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) big = max(big, __float_as_uint(v[i]) & 0x7fffffffu);
+    big = max(big, __shfl_xor_sync(0xffffffffu, big, 1));
+    big = max(big, __shfl_xor_sync(0xffffffffu, big, 2));
+    const bool finite = big < (227u << 23);  // below 2^100
+    int e = (int)(big >> 23) - 127;           // largest |x| in [2^e, 2^(e+1))
+    e = min(max(e, -100), 100);
+    const float factor = __uint_as_float((uint32_t)(127 + 5 - e) << 23);  // |x| * factor < 64
+    step_here = finite ? __uint_as_float((uint32_t)(127 + e - 13) << 23) : __uint_as_float(0x7fc00000u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int column = 4 * i + ((q & 1) << 1) + (q >> 1);  // 4i, 4i+2, 4i+1, 4i+3
+            const float scaled = finite ? v[column] * factor : 0.0f;
+            const float hi = rintf(scaled);
+            const float lo = fminf(rintf((scaled - hi) * 256.0f), 127.0f);
+            const int digit = (int)(low_digit ? lo : hi);
+            word |= ((uint32_t)digit & 0xffu) << (8 * q);
+        }
+        b[i] = word;
+    }
+}
+__device__ inline void store_digits(const uint32_t b[4], float step_here, uint8_t *slot, int lane, bool live) {
+    const int gid = lane >> 2, t = lane & 3;
+    // as the owner of accumulator column pair t this lane reports activation row t: its step sits in lane 8 t
+    const float step = __shfl_sync(0xffffffffu, step_here, 8 * t);
+    // the group's sum of x, exact: a row of ones against the digits
+    const uint32_t ones[4] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
+    int s[4];
+    mma_16832_u8s8(s, ones, b[0], b[1], true);
+    mma_16832_u8s8(s, ones, b[2], b[3], false);
+    if (live) {
+        *reinterpret_cast<uint4 *>(slot + lane * 16) = make_uint4(b[0], b[1], b[2], b[3]);
+        if (gid == 0) {
+            const float sum = step * (float)(s[0] * 256 + s[1]);
+            *reinterpret_cast<float2 *>(slot + 512 + t * 8) = make_float2(step, sum);
+        }
+    }
+}
+
+// One chunk of the integer form from registers fetched earlier (fp16 x): the four groups advance together,
+// stage by stage, so that their dependency chains overlap.
+__device__ inline void digitize_chunk_f16(const uint32_t raw[kChunkGroups][8], uint32_t count, uint8_t *chunk,
+                                          int lane) {
+    const bool low_digit = ((lane >> 2) & 1) != 0;
+    uint32_t b[kChunkGroups][4];
+    float step[kChunkGroups];
+#pragma unroll
+    for (uint32_t q = 0; q < kChunkGroups; ++q) digits_of_f16(raw[q], low_digit, b[q], step[q]);
+#pragma unroll
+    for (uint32_t q = 0; q < kChunkGroups; ++q) store_digits(b[q], step[q], chunk + q * Form<0>::XGROUP, lane, q < count);
+}
+// the same from fp32 x, loads included (no prefetch: twice the registers)
+__device__ inline void digitize_chunk_f32(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t g, uint32_t count,
+                                          uint8_t *chunk, int lane) {
+    const int gid = lane >> 2, t = lane & 3;
+    const uint32_t m = (uint32_t)gid >> 1;
+    const bool low_digit = (gid & 1) != 0;
+#pragma unroll
+    for (uint32_t half = 0; half < kChunkGroups; half += 2) {
+        float v[2][16];
+        uint32_t b[2][4];
+        float step[2];
+#pragma unroll
+        for (uint32_t q = 0; q < 2; ++q) {
+            fetch_x32(job.x, (size_t)m * K + (size_t)(g + half + q) * kGroup + 16 * t, m < m_rows && half + q < count, v[q]);
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 2; ++q) digits_of_f32(v[q], low_digit, b[q], step[q]);
+#pragma unroll
+        for (uint32_t q = 0; q < 2; ++q) {
+            store_digits(b[q], step[q], chunk + (half + q) * Form<0>::XGROUP, lane, half + q < count);
+        }
+    }
+}
+
+// fp16 form.  Lane (gid, t), column tile n: activation row m = 8 n + gid, columns 16 t .. 16 t + 15.  A slot gets:
+//   [n * 1024 + lane * 32, +32)           the eight B registers of the four m16n8k16 MMAs of a tile
+//   [NT * 1024 + 8 (8 n + m'), +8)        {step, step * sum} of activation row 8 n + m'
+// fp16 input passes through unchanged (step = 1); fp32 input is scaled by the power of two that brings the
+// group's largest magnitude into [1, 2) and then rounded to fp16, the power going into step.
 template <int NT>
-__global__ void __launch_bounds__(288, NT > 1 ? 1 : 2)
-decode_sequence_kernel(const SeqParams p) {
-    constexpr int W = kSeqWarps;
-    constexpr uint32_t kStageBytes = 16 * kUnitBytes;       // 36,864
-    constexpr uint32_t kPerBlock = 2 * NT * 4 * 128;         // floats of one 64-row block (gate + up planes)
-    extern __shared__ __align__(128) uint8_t sq_smem[];
+__device__ inline void load_group_f16(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t group, uint8_t *slot,
+                                      int lane, bool live) {
+    const int gid = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        const uint32_t m = n * 8 + gid;
+        const bool valid = live && m < m_rows;
+        const size_t element = (size_t)m * K + (size_t)group * kGroup + 16 * t;
+        uint32_t raw[8];
+        float step_here = 1.0f;
+        if (job.x_dtype == kF32) {
+            float v[16];
+            fetch_x32(job.x, element, valid, v);
+            uint32_t big = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) big = max(big, __float_as_uint(v[i]) & 0x7fffffffu);
+            big = max(big, __shfl_xor_sync(0xffffffffu, big, 1));
+            big = max(big, __shfl_xor_sync(0xffffffffu, big, 2));
+            const bool finite = big < (227u << 23);
+            int e = (int)(big >> 23) - 127;
+            e = min(max(e, -100), 100);
+            const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+            step_here = finite ? __uint_as_float((uint32_t)(127 + e) << 23) : __uint_as_float(0x7fc00000u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half2 pair = finite ? __floats2half2_rn(v[2 * i] * down, v[2 * i + 1] * down)
+                                            : __float2half2_rn(0.0f);
+                raw[i] = *reinterpret_cast<const uint32_t *>(&pair);
+            }
+        } else {
+            fetch_x16(job.x, element, valid, raw);
+        }
+        // group sums of x on the tensor pipe: a fragment of ones times the same B
+        const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+        float total[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_16816(total, ones, raw[2 * i], raw[2 * i + 1], i == 0);
+        // accumulator columns 2t, 2t+1 are activation rows 8n + 2t, 8n + 2t + 1: their steps sit in lanes 8t, 8t + 4
+        const float step0 = __shfl_sync(0xffffffffu, step_here, 8 * t);
+        const float step1 = __shfl_sync(0xffffffffu, step_here, 8 * t + 4);
+        if (live) {
+            uint4 *out = reinterpret_cast<uint4 *>(slot + n * 1024 + lane * 32);
+            out[0] = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+            out[1] = make_uint4(raw[4], raw[5], raw[6], raw[7]);
+            if (gid == 0) {
+                *reinterpret_cast<float4 *>(slot + NT * 1024 + (n * 8 + 2 * t) * 8) =
+                    make_float4(step0, step0 * total[0], step1, step1 * total[1]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// a consumer warp's work on one tile of one group
+// ---------------------------------------------------------------------------
+// Integer form: lane (gid, t) accumulates rows gid (acc[0]) and gid + 8 (acc[1]) of activation row t.
+__device__ inline void tile_digits(const uint8_t *tile, const uint8_t *slot, int lane, float acc[2]) {
+    const int gid = lane >> 2, t = lane & 3;
+    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
+    const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
+    const uint4 b = *reinterpret_cast<const uint4 *>(slot + lane * 16);
+    const float2 ss = *reinterpret_cast<const float2 *>(slot + 512 + t * 8);
+    // even nibbles: row gid, odd nibbles: row gid + 8; word i covers columns 4i .. 4i+3 of this lane's 16
+    const uint32_t a0[4] = {codes.x & 0x0F0F0F0Fu, (codes.x >> 4) & 0x0F0F0F0Fu,
+                            codes.y & 0x0F0F0F0Fu, (codes.y >> 4) & 0x0F0F0F0Fu};
+    const uint32_t a1[4] = {codes.z & 0x0F0F0F0Fu, (codes.z >> 4) & 0x0F0F0F0Fu,
+                            codes.w & 0x0F0F0F0Fu, (codes.w >> 4) & 0x0F0F0F0Fu};
+    int c[4];
+    mma_16832_u8s8(c, a0, b.x, b.y, true);
+    mma_16832_u8s8(c, a1, b.z, b.w, false);
+    const float top_row = (float)(c[0] * 256 + c[1]);
+    const float low_row = (float)(c[2] * 256 + c[3]);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
+    acc[0] = fmaf(lo.x * ss.x, top_row, fmaf(lo.y, ss.y, acc[0]));
+    acc[1] = fmaf(hi.x * ss.x, low_row, fmaf(hi.y, ss.y, acc[1]));
+}
+
+// fp16 form: lane (gid, t), column tile n: acc[4n + j] = (row gid + 8 (j >> 1), activation row 8n + 2t + (j & 1))
+template <int NT>
+__device__ inline void tile_f16(const uint8_t *tile, const uint8_t *slot, int lane, float acc[4 * NT]) {
+    const int gid = lane >> 2, t = lane & 3;
+    const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
+    const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
+    float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
+    float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
+    lo.x *= 16777216.0f;  // the codes go to the tensor pipe as q * 2^-24 (fp16 subnormal bit patterns)
+    hi.x *= 1048576.0f;   // and 16 q * 2^-24
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        const uint4 *xs = reinterpret_cast<const uint4 *>(slot + n * 1024 + lane * 32);
+        const uint4 x0 = xs[0], x1 = xs[1];
+        const float4 ss = *reinterpret_cast<const float4 *>(slot + NT * 1024 + (n * 8 + 2 * t) * 8);
+        const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        float c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t word = i == 0 ? codes.x : i == 1 ? codes.y : i == 2 ? codes.z : codes.w;
+            uint32_t a[4];
+            word_to_codes_subnormal(word, a);
+            mma_16816(c, a, xb[2 * i], xb[2 * i + 1], i == 0);
+        }
+        acc[4 * n + 0] = fmaf(lo.x * ss.x, c[0], fmaf(lo.y, ss.y, acc[4 * n + 0]));
+        acc[4 * n + 1] = fmaf(lo.x * ss.z, c[1], fmaf(lo.y, ss.w, acc[4 * n + 1]));
+        acc[4 * n + 2] = fmaf(hi.x * ss.x, c[2], fmaf(hi.y, ss.y, acc[4 * n + 2]));
+        acc[4 * n + 3] = fmaf(hi.x * ss.z, c[3], fmaf(hi.y, ss.w, acc[4 * n + 3]));
+    }
+}
+
+// row offset inside the 16-row tile and activation row of accumulator v of lane (gid, t)
+template <int MODE>
+__device__ inline void place_of(int v, int gid, int t, uint32_t &row, uint32_t &m) {
+    if (MODE == 0) {
+        row = gid + 8 * v;
+        m = t;
+    } else {
+        row = gid + 8 * ((v >> 1) & 1);
+        m = 8 * (v >> 2) + 2 * t + (v & 1);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <int MODE, bool SEQ>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+decode_kernel(const __grid_constant__ PassParams p) {
+    using F = Form<MODE>;
+    constexpr int NT = F::NT, VALS = F::VALS, STAGES = F::STAGES;
+    constexpr uint32_t kChunkBytes = kChunkGroups * F::XGROUP;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    if (!SEQ) asm volatile("griddepcontrol.launch_dependents;");  // the next launch may start prefetching weights
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, t = lane & 3;
-    const uint32_t cta = blockIdx.x, stages = p.stages;
+    const uint32_t cta = blockIdx.x, ctas = gridDim.x;
 
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sq_smem);  // full[8], empty[8]
-    uint8_t *ring = sq_smem + 128;
-    float *red = reinterpret_cast<float *>(ring + (size_t)stages * kStageBytes);   // [L][kPerBlock]
-    uint32_t *flags = reinterpret_cast<uint32_t *>(red + (size_t)p.max_local_blocks * kPerBlock);
-    float *part = reinterpret_cast<float *>(flags + ((p.max_local_blocks + 3u) & ~3u));  // [W][512], M <= 4 only
-    const uint32_t full0 = sq_smem_u32(bars), empty0 = sq_smem_u32(bars + kSeqMaxStages);
-    const uint32_t ring0 = sq_smem_u32(ring);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[4], empty[4], xfull[2], xempty[2]
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem_raw + 96);
+    uint8_t *ring = smem_raw + 128;
+    uint8_t *xring = ring + STAGES * kStageBytes;
+    float *xchg = reinterpret_cast<float *>(xring + kChunks * kChunkBytes);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 32, xfull0 = full0 + 64, xempty0 = full0 + 80;
+    const uint32_t ring0 = smem_u32(ring);
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < stages; ++s) {
-            sq_mbar_init(full0 + 8 * s, 1);
-            sq_mbar_init(empty0 + 8 * s, W);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumers);
         }
+        for (uint32_t c = 0; c < kChunks; ++c) {
+            mbar_init(xfull0 + 8 * c, 1);
+            mbar_init(xempty0 + 8 * c, kConsumers);
+        }
+        *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        flags[0] = 0;
     }
     __syncthreads();
 
-    if (warp == W) {
-        // ---- producer: stream every job's byte range, never draining the ring ----
+    const uint32_t job_count = SEQ ? p.job_count : 1u;
+    const uint32_t m_rows = p.m_rows;
+
+    if (warp == kProducerWarp) {
+        // ---- weight producer: one thread streams every unit of every job, never draining the ring ----
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t j = 0; j < p.job_count && ok; ++j) {
-                const DecodeJob &job = p.jobs[j];
-                const uint32_t G = job.groups, per_stage = job.fused ? 8u : 16u;
-                uint32_t u0, range;
-                sq_range(job, cta, u0, range);
-                uint32_t ua = u0, g = range > 0 ? u0 % G : 0;
-                const uint32_t u1 = u0 + range;
-                while (ua < u1) {
-                    const uint32_t s = it % stages;
-                    if (it >= stages && !sq_wait(empty0 + 8 * s, ((it / stages) - 1) & 1)) {
-                        ok = false;
+            uint32_t it = 0, issued = 0;
+            for (uint32_t j = 0; j < job_count; ++j) {
+                const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
+                const uint32_t G = job.groups;
+                for (uint32_t index = cta; index < job.units; index += ctas) {
+                    const Unit u = unit_of(job, index);
+                    const uint8_t *a = job.tiles[u.segment] +
+                                       (size_t)(job.fused ? u.local : 2 * u.local) * G * kUnitBytes;
+                    const uint8_t *b = job.fused ? job.up_tiles + (size_t)u.local * G * kUnitBytes
+                                                 : a + (size_t)G * kUnitBytes;
+                    for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
+                        const uint32_t s = it % STAGES;
+                        if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, failed, 0x91u);
+                        if (*failed != 0) continue;  // no new copies once a wait has expired
+                        const uint32_t bytes = min(kStageGroups, u.g1 - g) * kUnitBytes;
+                        mbar_expect_tx(full0 + 8 * s, u.has_b ? 2 * bytes : bytes);
+                        bulk_copy_to_shared(ring0 + s * kStageBytes, a + (size_t)g * kUnitBytes, bytes, full0 + 8 * s);
+                        if (u.has_b) {
+                            bulk_copy_to_shared(ring0 + s * kStageBytes + kStageGroups * kUnitBytes,
+                                                b + (size_t)g * kUnitBytes, bytes, full0 + 8 * s);
+                        }
+                        issued = it + 1;
+                    }
+                }
+            }
+            if (*failed != 0) {
+                // the copies already issued must land before this CTA's shared memory is released: the last
+                // fill of every stage (a bounded spin of its own, whatever the failure flag says)
+                for (uint32_t i = issued > (uint32_t)STAGES ? issued - STAGES : 0; i < issued; ++i) {
+                    const long long start = clock64();
+                    while (!mbar_try_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1) &&
+                           clock64() - start < kWaitLimitCycles) {
+                    }
+                }
+            }
+        }
+    } else if (warp >= kLoaderWarp) {
+        // ---- activation loaders: loader L fills slot L of the ring, i.e. every other chunk ----
+        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // x may be what the previous launch wrote
+        const uint32_t which = (uint32_t)(warp - kLoaderWarp);
+        uint32_t epoch = 0;
+        if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
+        Cursor c = {};
+        c.index = cta;
+        cursor_settle<SEQ>(c, p, job_count, cta, ctas);
+        for (uint32_t skip = 0; skip < which && c.valid; ++skip) cursor_advance<SEQ>(c, p, job_count, cta, ctas);
+        uint32_t ready_job = 0;  // the outputs every job up to this one may read are complete
+        uint32_t fills = 0;      // chunks this loader has handed over
+        uint32_t held[kChunkGroups][8];  // integer form, fp16 x: the current chunk's activations, fetched a chunk ahead
+        bool have_held = false;
+        const uint32_t row = (uint32_t)gid >> 1;  // integer form: this lane's activation row
+        while (c.valid) {
+            const DecodeJob &job = SEQ ? p.jobs[c.j] : p.job;
+            const size_t K = (size_t)job.groups * kGroup;
+            if (SEQ && c.j > ready_job) {
+                // x of this job may be what the previous job wrote, on this or any rank: wait until every
+                // 16-row tile of it, on every rank, has been counted in this launch
+                const uint32_t expected = 4u * p.jobs[c.j - 1].expected_blocks * epoch;
+                const uint32_t *counter = p.done + ((size_t)(c.j - 1) * 8 + (lane & 7)) * kDoneStride;
+                const long long start = clock64();
+                for (;;) {
+                    uint32_t seen = 0;
+                    if (lane < 8) {
+                        if (p.world > 1) {
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                        } else {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                        }
+                    }
+                    seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                    seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                    seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+                    seen = __shfl_sync(0xffffffffu, seen, 0);
+                    if ((int32_t)(seen - expected) >= 0 || *failed != 0) break;
+                    if (clock64() - start > kWaitLimitCycles) {
+                        *failed = 0x95u;
                         break;
                     }
-                    const uint32_t count = min(min(per_stage, G - g), u1 - ua);  // never across a row block
-                    const uint32_t bytes = count * kUnitBytes;
-                    sq_mbar_expect_tx(full0 + 8 * s, job.fused ? 2 * bytes : bytes);
-                    const uint32_t grb = ua / G;
-                    const int segment = sq_segment_of(job, grb);
-                    const size_t offset = (size_t)(ua - job.block_begin[segment] * G) * kUnitBytes;
-                    sq_bulk_copy(ring0 + s * kStageBytes, job.tiles[segment] + offset, bytes, full0 + 8 * s);
-                    if (job.fused) {
-                        sq_bulk_copy(ring0 + s * kStageBytes + 8 * kUnitBytes, job.up_tiles + offset, bytes, full0 + 8 * s);
+                }
+                asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                __syncwarp();
+                ready_job = c.j;
+                have_held = false;
+            }
+            const uint32_t count = min(kChunkGroups, c.u.g1 - c.g);
+            uint8_t *chunk = xring + which * kChunkBytes;
+            const uint32_t g = c.g, j = c.j;
+            // this loader's next chunk
+            for (int step = 0; step < kLoaders && c.valid; ++step) cursor_advance<SEQ>(c, p, job_count, cta, ctas);
+            bool fetch_next = false;
+            if (MODE == 0 && job.x_dtype != kF32) {
+                if (!have_held) {
+#pragma unroll
+                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
+                        fetch_x16(job.x, (size_t)row * K + (size_t)(g + q) * kGroup + 16 * t,
+                                  row < m_rows && q < count, held[q]);
                     }
-                    ua += count;
-                    g += count;
-                    if (g == G) g = 0;
-                    ++it;
                 }
-            }
-            if (!ok) {
-                atomicExch(p.status, 0x81u);
-                for (uint32_t back = 0; back < stages && back < it; ++back) {  // let issued copies land
-                    const uint32_t i = it - 1 - back;
-                    sq_wait(full0 + 8 * (i % stages), (i / stages) & 1);
-                }
-            }
-        }
-        return;  // the producer warp takes part in no later barrier
-    }
-
-    // ---- consumers ----
-    const uint32_t m_rows = p.m_rows;
-    uint32_t it = 0;
-    bool ok = true;
-    for (uint32_t j = 0; j < p.job_count && ok; ++j) {
-        const DecodeJob &job = p.jobs[j];
-        const uint32_t G = job.groups;
-        const bool fused = job.fused != 0;
-        const uint32_t per_stage = fused ? 8u : 16u;
-        const size_t K = (size_t)G * kGroup;
-        uint32_t u0, range;
-        sq_range(job, cta, u0, range);
-        const uint32_t u1 = u0 + range;
-        const uint32_t grb0 = range > 0 ? u0 / G : 0, g_first = range > 0 ? u0 % G : 0;
-
-        for (uint32_t i = threadIdx.x; i < job.local_blocks * kPerBlock; i += 256) red[i] = 0.0f;
-        // x of this job may be what the previous job wrote (on this or any rank): wait for all of it
-        const long long t_dep = SQ_CLOCK();
-        if (j > 0 && range > 0 && threadIdx.x == 0) {
-            // every row block of the previous job, on every rank, announces itself once
-            const uint32_t expected = p.jobs[j - 1].expected_blocks * p.epoch;
-            const long long start = clock64();
-            uint32_t seen = 0;
-            for (;;) {
-                if (p.world > 1) {  // peers add to the counter over NVLink after a system-scope fence
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.done + (j - 1)) : "memory");
-                } else {
-                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.done + (j - 1)) : "memory");
-                }
-                if ((int32_t)(seen - expected) >= 0) break;
-                if (clock64() - start > kSeqWaitLimit) { flags[0] = 0xdeadu; break; }
-                __nanosleep(32);
-            }
-            // the acquire above (system scope with peers) ordered the peers' stores; a system-scope fence here
-            // measured 3 us per job, the device-scope one passes the order on to the CTA's other threads
-            asm volatile("fence.acq_rel.gpu;" ::: "memory");
-        }
-        sq_consumer_barrier();
-        if (flags[0] == 0xdeadu) {
-            ok = false;
-            if (threadIdx.x == 0) atomicExch(p.status, 0x83u);
-            break;
-        }
-        SQ_ADD(0, t_dep);
-        const long long t_loop = SQ_CLOCK();
-
-        float acc[2][4][NT][4];
-#pragma unroll
-        for (int k = 0; k < 2; ++k)
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-#pragma unroll
-                for (int n = 0; n < NT; ++n)
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) acc[k][r][n][q] = 0.0f;
-
-        // add every warp's sums of a finished row block into the block sums, in warp order
-        auto flush_in_turns = [&](uint32_t lrb) {
-            float *target = red + (size_t)lrb * kPerBlock;
-            for (int turn = 0; turn < W; ++turn) {
-                if (warp == turn) {
-#pragma unroll
-                    for (int k = 0; k < 2; ++k)
-#pragma unroll
-                        for (int n = 0; n < NT; ++n)
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) {
-                                float4 *at = reinterpret_cast<float4 *>(target + k * (NT * 512)) + (n * 4 + r) * 32 + lane;
-                                float4 v = *at;
-                                v.x += acc[k][r][n][0]; v.y += acc[k][r][n][1];
-                                v.z += acc[k][r][n][2]; v.w += acc[k][r][n][3];
-                                *at = v;
-                                acc[k][r][n][0] = acc[k][r][n][1] = acc[k][r][n][2] = acc[k][r][n][3] = 0.0f;
-                            }
-                }
-                sq_consumer_barrier();
-            }
-        };
-
-        // The same for M <= 4 in two barriers: only columns 0..3 of the 8-wide tiles carry activations,
-        // so every warp parks those (2 planes x 64 rows x 4 columns) in its own slice and the CTA's
-        // threads add the eight slices in warp order.
-        auto flush_small = [&](uint32_t lrb) {
-            float *mine = part + (size_t)warp * 512;
-            if (t < 2) {
-#pragma unroll
-                for (int k = 0; k < 2; ++k)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t row = r * 16 + gid;
-                        *reinterpret_cast<float2 *>(mine + (k * 64 + row) * 4 + 2 * t) =
-                            make_float2(acc[k][r][0][0], acc[k][r][0][1]);
-                        *reinterpret_cast<float2 *>(mine + (k * 64 + row + 8) * 4 + 2 * t) =
-                            make_float2(acc[k][r][0][2], acc[k][r][0][3]);
-                    }
-            }
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) acc[k][r][0][0] = acc[k][r][0][1] = acc[k][r][0][2] = acc[k][r][0][3] = 0.0f;
-            sq_consumer_barrier();
-            float *target = red + (size_t)lrb * kPerBlock;
-            for (uint32_t o = threadIdx.x; o < 512; o += 256) {
-                const uint32_t k = o >> 8, row = (o >> 2) & 63u, col = o & 3u;
-                float total = 0.0f;
-#pragma unroll
-                for (int w = 0; w < W; ++w) total += part[(size_t)w * 512 + o];
-                // fragment layout of the block sums: tile r = row / 16, lane = 4 (row % 8) + col / 2,
-                // element 2 (row / 8 % 2) + col % 2
-                const uint32_t index = k * (NT * 512) + (row >> 4) * 128 + ((row & 7u) * 4 + (col >> 1)) * 4 +
-                                       ((row >> 3) & 1u) * 2 + (col & 1u);
-                target[index] += total;
-            }
-            sq_consumer_barrier();
-        };
-        auto flush = [&](uint32_t lrb) {
-            if (NT == 1 && m_rows <= 4) {
-                flush_small(lrb);
+                if (fills >= 1) mbar_wait(xempty0 + 8 * which, (fills - 1) & 1, failed, 0x94u);
+                digitize_chunk_f16(held, count, chunk, lane);
+                // this loader's next chunk of the same job leaves for the registers as soon as this one is handed
+                // over (below): its latency passes while the consumers work (the job after may not be written yet)
+                fetch_next = c.valid && c.j == j;
             } else {
-                flush_in_turns(lrb);
-            }
-        };
-
-        uint32_t ua = u0, g = g_first, cur_grb = grb0, grb = grb0;
-        while (ua < u1) {
-            const uint32_t s = it % stages;
-            const uint32_t count = min(min(per_stage, G - g), u1 - ua);
-            if (grb != cur_grb) {
-                flush(cur_grb - grb0);
-                cur_grb = grb;
-            }
-            if (!sq_wait(full0 + 8 * s, (it / stages) & 1)) {
-                ok = false;
-                break;
-            }
-            const uint8_t *stage = ring + (size_t)s * kStageBytes;
+                if (fills >= 1) mbar_wait(xempty0 + 8 * which, (fills - 1) & 1, failed, 0x94u);
+                if (MODE == 0) {
+                    digitize_chunk_f32(job, m_rows, K, g, count, chunk, lane);
+                } else {
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                // fused: sub = matrix (gate, up) of group `warp`; else sub selects group warp or warp + 8
-                const uint32_t j_group = fused ? (uint32_t)warp : (uint32_t)warp + 8u * sub;
-                if (j_group >= count) continue;
-                const int plane = fused ? sub : 0;
-                const uint32_t group = g + j_group;
-                uint32_t xb[NT][8];
-                float2 sums[NT];
-#pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    const uint32_t m = n * 8 + gid;
-                    if (m < m_rows) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(
-                            reinterpret_cast<const __half *>(job.x) + (size_t)m * K + (size_t)group * kGroup + 16 * t);
-                        const uint4 a = __ldg(src), b = __ldg(src + 1);
-                        xb[n][0] = a.x; xb[n][1] = a.y; xb[n][2] = a.z; xb[n][3] = a.w;
-                        xb[n][4] = b.x; xb[n][5] = b.y; xb[n][6] = b.z; xb[n][7] = b.w;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) xb[n][i] = 0u;
-                    }
-                    // group sums of x on the tensor pipe: a fragment of ones times the same B
-                    const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
-                    float total[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) sq_mma(total, ones, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
-                    sums[n] = make_float2(total[0], total[1]);
-                }
-                const uint8_t *unit = stage + (size_t)((fused ? 8u * sub : 0u) + j_group) * kUnitBytes;
-                uint4 codes[4];
-                uint2 meta[4];
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const uint8_t *tile = unit + r * kTileBytes;
-                    codes[r] = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
-                    meta[r] = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
-                }
-                float c[4][NT][4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t word = i == 0 ? codes[r].x : i == 1 ? codes[r].y : i == 2 ? codes[r].z : codes[r].w;
-                        uint32_t a[4];
-                        word_to_codes_subnormal(word, a);
-#pragma unroll
-                        for (int n = 0; n < NT; ++n) sq_mma(c[r][n], a, xb[n][2 * i], xb[n][2 * i + 1], i == 0);
-                    }
-                }
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta[r].x));
-                    float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta[r].y));
-                    lo.x *= 16777216.0f;  // codes arrive as q * 2^-24
-                    hi.x *= 1048576.0f;   // and 16 q * 2^-24
-#pragma unroll
-                    for (int n = 0; n < NT; ++n) {
-                        if (plane == 0) {
-                            acc[0][r][n][0] = fmaf(lo.x, c[r][n][0], fmaf(lo.y, sums[n].x, acc[0][r][n][0]));
-                            acc[0][r][n][1] = fmaf(lo.x, c[r][n][1], fmaf(lo.y, sums[n].y, acc[0][r][n][1]));
-                            acc[0][r][n][2] = fmaf(hi.x, c[r][n][2], fmaf(hi.y, sums[n].x, acc[0][r][n][2]));
-                            acc[0][r][n][3] = fmaf(hi.x, c[r][n][3], fmaf(hi.y, sums[n].y, acc[0][r][n][3]));
-                        } else {
-                            acc[1][r][n][0] = fmaf(lo.x, c[r][n][0], fmaf(lo.y, sums[n].x, acc[1][r][n][0]));
-                            acc[1][r][n][1] = fmaf(lo.x, c[r][n][1], fmaf(lo.y, sums[n].y, acc[1][r][n][1]));
-                            acc[1][r][n][2] = fmaf(hi.x, c[r][n][2], fmaf(hi.y, sums[n].x, acc[1][r][n][2]));
-                            acc[1][r][n][3] = fmaf(hi.x, c[r][n][3], fmaf(hi.y, sums[n].y, acc[1][r][n][3]));
-                        }
+                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
+                        load_group_f16<NT>(job, m_rows, K, g + q, chunk + q * F::XGROUP, lane, q < count);
                     }
                 }
             }
             __syncwarp();
-            if (lane == 0) sq_mbar_arrive(empty0 + 8 * s);
-            ++it;
-            ua += count;
-            g += count;
-            if (g == G) { g = 0; ++grb; }
-        }
-        if (!ok) {
-            if (lane == 0) atomicExch(p.status, 0x82u);
-            break;
-        }
-        if (range == 0) continue;
-        SQ_ADD(1, t_loop);
-        const long long t_flush = SQ_CLOCK();
-        flush(cur_grb - grb0);  // ends with a consumer barrier
-        SQ_ADD(2, t_flush);
-        const long long t_finish = SQ_CLOCK();
-        // ---- finish every row block this CTA touched ----
-        const uint32_t grb_last = (u1 - 1) / G;
-        const uint32_t share = job.units_per_cta, extra = job.units_extra, parts = job.parts;
-        const uint32_t floats = fused ? kPerBlock : kPerBlock / 2;  // planes in use
-        // (1) park the sums of row blocks that other CTAs share
-        for (uint32_t b = grb0; b <= grb_last; ++b) {
-            const uint32_t contributed = min(u1, (b + 1) * G) - max(u0, b * G);
-            if (contributed == G) continue;
-            const uint32_t first_cta = parts > 0 ? b * parts : sq_cta_of_unit(b * G, share, extra);
-            const float *mine = red + (size_t)(b - grb0) * kPerBlock;
-            float *slot = p.scratch + ((size_t)b * job.slots + (cta - first_cta)) * kPerBlock;
-            for (uint32_t o = threadIdx.x; o < floats; o += 256) slot[o] = mine[o];
-        }
-        sq_consumer_barrier();
-        // (2) one thread per row block publishes and learns whether this CTA completes the block
-        if (threadIdx.x <= grb_last - grb0) {
-            const uint32_t b = grb0 + threadIdx.x;
-            const uint32_t contributed = min(u1, (b + 1) * G) - max(u0, b * G);
-            uint32_t finish = 1;
-            if (contributed != G) {
-                // release: the CTA's parked sums (ordered before this by the barrier) are visible to whoever reads
-                // the count; acquire: the last arriver sees everybody else's
-                uint32_t before;
-                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
-                             : "=r"(before) : "l"(p.counters + b), "r"(contributed) : "memory");
-                finish = before + contributed == G ? 2u : 0u;
-                if (finish) p.counters[b] = 0;  // ready for the next job (ordered by the publishing release below)
-            }
-            flags[threadIdx.x] = finish;
-        }
-        sq_consumer_barrier();
-        // (3) outputs of the blocks that are complete here, stored on every rank
-        for (uint32_t b = grb0; b <= grb_last; ++b) {
-            const uint32_t finish = flags[b - grb0];
-            if (finish == 0) continue;
-            const float *mine = red + (size_t)(b - grb0) * kPerBlock;
-            const uint32_t first_cta = parts > 0 ? b * parts : sq_cta_of_unit(b * G, share, extra);
-            const uint32_t last_cta = parts > 0 ? first_cta + parts - 1 : sq_cta_of_unit((b + 1) * G - 1, share, extra);
-            const uint32_t contributors = last_cta - first_cta + 1;
-            const float *slots = p.scratch + ((size_t)b * job.slots) * kPerBlock;
-            const int segment = sq_segment_of(job, b);
-            const uint32_t rb = b - job.block_begin[segment];
-            const uint32_t rows = job.rows[segment], ldy = job.ldy[segment];
-            for (uint32_t o = threadIdx.x; o < NT * 4 * 128; o += 256) {
-                const uint32_t n = o / 512, rr = (o >> 7) & 3u, ln = (o >> 2) & 31u, q = o & 3u;
-                const uint32_t row = rb * 64 + rr * kTileRows + (ln >> 2) + 8 * (q >> 1);
-                const uint32_t m = n * 8 + 2 * (ln & 3u) + (q & 1u);
-                if (row >= rows || m >= m_rows) continue;
-                float value = 0.0f, second = 0.0f;
-                if (finish == 1) {
-                    value = mine[o];
-                    if (fused) second = mine[NT * 512 + o];
-                } else {  // the slots in CTA order: the same sum whichever CTA arrives last
-                    for (uint32_t c0 = 0; c0 < contributors; c0 += 4) {  // four loads in flight at a time
-                        float a[4], b[4];
+            if (lane == 0) mbar_arrive(xfull0 + 8 * which);
+            ++fills;
+            if (MODE == 0) {
+                have_held = fetch_next;
+                if (fetch_next) {
+                    const uint32_t next_count = min(kChunkGroups, c.u.g1 - c.g);
 #pragma unroll
-                        for (uint32_t q = 0; q < 4; ++q) {
-                            const bool live = c0 + q < contributors;
-                            a[q] = live ? __ldcg(slots + (size_t)(c0 + q) * kPerBlock + o) : 0.0f;
-                            b[q] = live && fused ? __ldcg(slots + (size_t)(c0 + q) * kPerBlock + NT * 512 + o) : 0.0f;
-                        }
-#pragma unroll
-                        for (uint32_t q = 0; q < 4; ++q) {
-                            value += a[q];
-                            second += b[q];
-                        }
-                    }
-                }
-                if (fused) {
-                    // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
-                    value = (value / (1.0f + __expf(-value))) * second;
-                }
-                const size_t at = (size_t)m * ldy + row;
-                for (uint32_t r = 0; r < p.world; ++r) {
-                    void *destination = job.y[segment][r];
-                    if (destination == nullptr) continue;
-                    if (job.y_dtype == kF32) {
-                        reinterpret_cast<float *>(destination)[at] = value;
-                    } else {
-                        reinterpret_cast<__half *>(destination)[at] = __float2half_rn(value);
+                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
+                        fetch_x16(job.x, (size_t)row * K + (size_t)(c.g + q) * kGroup + 16 * t,
+                                  row < m_rows && q < next_count, held[q]);
                     }
                 }
             }
         }
-        // (4) publish the row blocks whose outputs this CTA wrote (CTAs that only
-        // contributed partial sums have nothing more to say and move on)
-        uint32_t finished = 0;
-        for (uint32_t b = grb0; b <= grb_last; ++b) finished += flags[b - grb0] != 0 ? 1u : 0u;
-        sq_consumer_barrier();
-        if (threadIdx.x == 0 && finished > 0) {
-            if (p.world > 1) {
-                const long long t_publish = SQ_CLOCK();
-                // one system-scope fence for the CTA's stores to all ranks, then one add per rank
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                for (uint32_t r = 0; r < p.world; ++r)
-                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_done[r] + j), "r"(finished) : "memory");
-                SQ_ADD(5, t_publish);
-            } else {
-                asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.done + j), "r"(finished) : "memory");
+    } else {
+        // ---- consumers: warp w owns tile w & 3 of block w >> 2 of every pair block this CTA visits ----
+        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // y, residual and scratch belong to stream order
+        const int k = warp >> 2, r = warp & 3;
+        uint32_t it = 0, xi = 0;
+        for (uint32_t j = 0; j < job_count; ++j) {
+            const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
+            const bool fused = job.fused != 0;
+            for (uint32_t index = cta; index < job.units; index += ctas) {
+                const Unit u = unit_of(job, index);
+                const bool active = k == 0 || u.has_b;
+                float acc[VALS];
+#pragma unroll
+                for (int v = 0; v < VALS; ++v) acc[v] = 0.0f;
+                for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
+                    const uint32_t s = it % STAGES;
+                    mbar_wait(full0 + 8 * s, (it / STAGES) & 1, failed, 0x92u);
+                    const uint8_t *stage = ring + s * kStageBytes + (size_t)k * kStageGroups * kUnitBytes + r * kTileBytes;
+                    const uint32_t in_stage = min(kStageGroups, u.g1 - g);
+                    for (uint32_t h = 0; h < in_stage; h += kChunkGroups, ++xi) {
+                        const uint32_t c = xi % kChunks;
+                        mbar_wait(xfull0 + 8 * c, (xi / kChunks) & 1, failed, 0x93u);
+                        const uint32_t count = min(kChunkGroups, in_stage - h);
+                        if (active) {
+                            const uint8_t *tiles = stage + (size_t)h * kUnitBytes;
+                            const uint8_t *slots = xring + c * kChunkBytes;
+                            if (count == kChunkGroups) {  // the common case without a branch between the tiles
+#pragma unroll
+                                for (uint32_t q = 0; q < kChunkGroups; ++q) {
+                                    if (MODE == 0) {
+                                        tile_digits(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
+                                    } else {
+                                        tile_f16<NT>(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
+                                    }
+                                }
+                            } else {
+                                for (uint32_t q = 0; q < count; ++q) {
+                                    if (MODE == 0) {
+                                        tile_digits(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
+                                    } else {
+                                        tile_f16<NT>(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(xempty0 + 8 * c);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                }
+
+                // ---- the unit is done: finish this warp's tile ----
+                float second[VALS];  // the up half of a fused pair, once known
+#pragma unroll
+                for (int v = 0; v < VALS; ++v) second[v] = 0.0f;
+                bool finisher;
+                if (job.parts == 1) {
+                    if (fused) {
+                        // the up warp hands its sums to the gate warp of the same tile through shared memory
+                        float *mine = xchg + (size_t)(r * 32 + lane) * F::XCHG_VALS;
+#pragma unroll
+                        for (int round = 0; round < VALS / (int)F::XCHG_VALS; ++round) {
+                            if (k == 1) {
+#pragma unroll
+                                for (int v = 0; v < (int)F::XCHG_VALS; ++v) mine[v] = acc[round * F::XCHG_VALS + v];
+                            }
+                            pair_barrier(2 + r);
+                            if (k == 0) {
+#pragma unroll
+                                for (int v = 0; v < (int)F::XCHG_VALS; ++v) second[round * F::XCHG_VALS + v] = mine[v];
+                            }
+                            pair_barrier(2 + r);
+                        }
+                    }
+                    finisher = fused ? k == 0 : active;
+                } else {
+                    // K is split over CTAs: park the sums; the last warp to arrive for this tile adds every
+                    // part's in part order (the same sum whoever is last)
+                    finisher = false;
+                    if (active) {
+                        float *slot = p.scratch + (size_t)index * (8 * 32 * VALS);
+#pragma unroll
+                        for (int v = 0; v < VALS; ++v) slot[(v * 8 + warp) * 32 + lane] = acc[v];
+                        __syncwarp();
+                        uint32_t before = 0;
+                        uint32_t *counter = p.counters + (size_t)u.pair * 8 + (fused ? r : warp);
+                        if (lane == 0) {
+                            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                                         : "=r"(before) : "l"(counter), "r"(1u) : "memory");
+                        }
+                        before = __shfl_sync(0xffffffffu, before, 0);
+                        __syncwarp();
+                        const uint32_t needed = fused ? 2 * job.parts : job.parts;
+                        if (before + 1 == needed) {
+                            finisher = true;
+                            if (lane == 0) *counter = 0;  // ready for the next job or launch (ordered by what follows)
+                            asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                            const float *base = p.scratch + (size_t)(u.pair * job.parts) * (8 * 32 * VALS);
+                            const int gate_warp = fused ? r : warp;
+#pragma unroll
+                            for (int v = 0; v < VALS; ++v) acc[v] = 0.0f;
+                            for (uint32_t q = 0; q < job.parts; ++q) {
+                                const float *from = base + (size_t)q * (8 * 32 * VALS);
+#pragma unroll
+                                for (int v = 0; v < VALS; ++v) {
+                                    acc[v] += __ldcg(from + (v * 8 + gate_warp) * 32 + lane);
+                                    if (fused) second[v] += __ldcg(from + (v * 8 + gate_warp + 4) * 32 + lane);
+                                }
+                            }
+                        }
+                    }
+                }
+                if (finisher) {
+                    const int out_k = fused ? 0 : k;
+                    const uint32_t row0 = (fused ? u.local * 64 : u.local * 128 + out_k * 64) + r * kTileRows;
+                    const uint32_t rows = job.rows[u.segment], ldy = job.ldy[u.segment];
+#pragma unroll
+                    for (int v = 0; v < VALS; ++v) {
+                        uint32_t row, m;
+                        place_of<MODE>(v, gid, t, row, m);
+                        row += row0;
+                        if (row >= rows || m >= m_rows) continue;
+                        float value = acc[v];
+                        // silu(g) * u from the un-rounded accumulators (qwen38_q4.metal:146-149)
+                        if (fused) value = (value / (1.0f + __expf(-value))) * second[v];
+                        if (job.residual != nullptr && u.segment == 0) {
+                            const size_t at = (size_t)m * job.ld_residual + row;
+                            value += job.residual_dtype == kF32
+                                         ? reinterpret_cast<const float *>(job.residual)[at]
+                                         : __half2float(reinterpret_cast<const __half *>(job.residual)[at]);
+                        }
+                        const size_t at = (size_t)m * ldy + row;
+                        for (uint32_t rank = 0; rank < p.world; ++rank) {
+                            void *destination = job.y[u.segment][rank];
+                            if (destination == nullptr) continue;
+                            if (job.y_dtype == kF32) {
+                                reinterpret_cast<float *>(destination)[at] = value;
+                            } else {
+                                reinterpret_cast<__half *>(destination)[at] = __float2half_rn(value);
+                            }
+                        }
+                    }
+                    if (SEQ) {
+                        // this tile is stored everywhere: count it on every rank
+                        __syncwarp();
+                        if (lane == 0) {
+                            const size_t at = ((size_t)j * 8 + warp) * kDoneStride;
+                            if (p.world > 1) {
+                                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                                for (uint32_t rank = 0; rank < p.world; ++rank) {
+                                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;"
+                                                 ::"l"(p.peer_done[rank] + at), "r"(1u) : "memory");
+                                }
+                            } else {
+                                asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.done + at), "r"(1u) : "memory");
+                            }
+                        }
+                    }
+                }
             }
         }
-        SQ_ADD(3, t_finish);
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (*failed != 0) atomicExch(p.status, *failed);
+        if (SEQ) {
+            // the last CTA to leave closes the launch: the next one expects one more round of completions
+            __threadfence();
+            const uint32_t left = atomicAdd(p.exit_count, 1u);
+            if (left + 1 == ctas) {
+                *p.exit_count = 0;
+                *reinterpret_cast<volatile uint32_t *>(p.epoch) = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
+            }
+        }
     }
 }
 
-template <int NT>
-cudaError_t sequence_attributes(size_t smem_bytes, int *blocks_per_sm) {
-    auto kernel = decode_sequence_kernel<NT>;
+int mode_of(uint32_t m_rows, int variant) {
+    if (m_rows <= 4 && ((variant >> 4) & 1) == 0) return 0;
+    return m_rows <= 8 ? 1 : 2;
+}
+
+size_t smem_of(int mode) {
+    return mode == 0 ? smem_bytes_of<0>() : mode == 1 ? smem_bytes_of<1>() : smem_bytes_of<2>();
+}
+
+template <int MODE, bool SEQ>
+cudaError_t configure(size_t smem_bytes, int *blocks_per_sm) {
+    auto kernel = decode_kernel<MODE, SEQ>;
+    static int resident[kMaxDevices];  // per instantiation and device; 0 = not configured yet
+    const int slot = device_slot();
+    if (slot >= 0 && resident[slot] > 0) {
+        *blocks_per_sm = resident[slot];
+        return cudaSuccess;
+    }
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (status != cudaSuccess) return status;
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, kernel, 288, smem_bytes);
+    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, kernel, kDecodeThreads, smem_bytes);
+    if (status != cudaSuccess) return status;
+    if (*blocks_per_sm < 1) return cudaErrorInvalidConfiguration;
+    if (slot >= 0) resident[slot] = *blocks_per_sm;
+    return cudaSuccess;
+}
+
+cudaError_t configure_mode(int mode, bool sequence, size_t smem_bytes, int *per_sm) {
+    if (sequence) {
+        return mode == 0 ? configure<0, true>(smem_bytes, per_sm)
+               : mode == 1 ? configure<1, true>(smem_bytes, per_sm) : configure<2, true>(smem_bytes, per_sm);
+    }
+    return mode == 0 ? configure<0, false>(smem_bytes, per_sm)
+           : mode == 1 ? configure<1, false>(smem_bytes, per_sm) : configure<2, false>(smem_bytes, per_sm);
 }
 
 }  // namespace
 
-void plan_decode_job(DecodeJob *job, uint32_t m_rows, uint32_t ctas, size_t *scratch_bytes, size_t *counter_bytes) {
-    const uint32_t G = job->groups;
-    const int NT = m_rows <= 8 ? 1 : 2;
-    uint32_t blocks = 0;
-    for (uint32_t s = 0; s < job->segments; ++s) {
-        job->block_begin[s] = blocks;
-        blocks += ceil_div(job->rows[s], 64);
-    }
-    for (uint32_t s = job->segments; s <= kMaxSegments; ++s) job->block_begin[s] = blocks;
-    const uint32_t units = blocks * G;
-    job->total_units = units;
-    // every row block cut into the same number of parts when all parts fit the grid
-    // Every row block cut into the same number of K parts when all parts fit the grid: one CTA then touches
-    // one row block only.  (Equal unit ranges over the whole grid balance the bytes better but make every CTA
-    // share two or three row blocks; measured 80 against 68 us per 27B layer.)
-    uint32_t parts = 0;
-    if (blocks <= ctas && getenv("Q4B_SEQUENCE_EQUAL_RANGES") == nullptr) {
-        for (uint32_t k = 1; k <= G; ++k) {
-            if (blocks * k <= ctas && (G / k >= 4 || k == 1)) parts = k;
-        }
-    }
-    job->parts = parts;
-    uint32_t max_range;
-    if (parts > 0) {
-        job->active_ctas = blocks * parts;
-        job->units_per_cta = 0;
-        job->units_extra = 0;
-        job->slots = parts;
-        job->local_blocks = 1;
-        max_range = ceil_div(G, parts);
-    } else {
-        uint32_t active = ctas;
-        const uint32_t by_work = units / 8 > 0 ? units / 8 : 1;
-        if (active > by_work) active = by_work;
-        job->active_ctas = active;
-        job->units_per_cta = units / active;
-        job->units_extra = units % active;
-        max_range = ceil_div(units, active);
-        job->slots = ceil_div(G, job->units_per_cta > 0 ? job->units_per_cta : 1) + 1;
-        job->local_blocks = (max_range - 1) / G + 2;
-    }
-    (void)max_range;
-    *scratch_bytes = (size_t)blocks * job->slots * (2 * NT * 4 * 128) * sizeof(float);
-    *counter_bytes = (size_t)blocks * sizeof(uint32_t);
-}
+uint32_t decode_max_m() { return 16; }
 
-cudaError_t sequence_geometry(uint32_t m_rows, int sm_count, uint32_t stages, uint32_t max_local_blocks,
-                              uint32_t *ctas, size_t *smem_bytes) {
-    const int NT = m_rows <= 8 ? 1 : 2;
-    if (m_rows == 0 || m_rows > 16 || stages < 2 || stages > (uint32_t)kSeqMaxStages) return cudaErrorInvalidValue;
-    const size_t bytes = 128 + (size_t)stages * 16 * kUnitBytes +
-                         (size_t)max_local_blocks * (2 * NT * 4 * 128) * sizeof(float) +
-                         ((max_local_blocks + 3u) & ~3u) * 4 + (m_rows <= 4 ? 8 * 512 * sizeof(float) : 0) + 16;
-    if (bytes > 220 * 1024) return cudaErrorInvalidValue;
-    int per_sm = 0;
-    cudaError_t status = NT == 1 ? sequence_attributes<1>(bytes, &per_sm) : sequence_attributes<2>(bytes, &per_sm);
-    if (status != cudaSuccess) return status;
-    if (per_sm < 1) return cudaErrorInvalidValue;
-    if (per_sm > 2) per_sm = 2;
-    *ctas = (uint32_t)(per_sm * sm_count);
-    *smem_bytes = bytes;
+// ---------------------------------------------------------------------------
+// Scratch that exists without any allocation call: file-scope device arrays,
+// part of the library image, held by every GPU that loads it until the process
+// exits.  In host code the names below are only stand-ins for the symbols; the
+// device addresses come from cudaGetSymbolAddress, looked up once per device
+// with that device current.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB of partial-sum slots
+constexpr size_t kStaticCounterCount = 4096;      // one arrival counter per 16-row tile of a split pair block
+static __device__ __align__(256) float q4b_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) uint32_t q4b_static_counters[kStaticCounterCount];
+
+cudaError_t decode_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
+                                  size_t *counter_bytes) {
+    static float *scratch_of[kMaxDevices];
+    static uint32_t *counters_of[kMaxDevices];
+    static std::mutex guard;  // two contexts on two threads may make their first call at the same time
+    const int device = device_slot();
+    if (device < 0) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(guard);
+    if (scratch_of[device] == nullptr) {
+        float *scratch_address = nullptr;
+        uint32_t *counter_address = nullptr;
+        cudaError_t status = cudaGetSymbolAddress(reinterpret_cast<void **>(&scratch_address), q4b_static_scratch);
+        if (status != cudaSuccess) return status;
+        status = cudaGetSymbolAddress(reinterpret_cast<void **>(&counter_address), q4b_static_counters);
+        if (status != cudaSuccess) return status;
+        counters_of[device] = counter_address;
+        scratch_of[device] = scratch_address;
+    }
+    *scratch = scratch_of[device];
+    *counters = counters_of[device];
+    *scratch_bytes = kStaticScratchBytes;
+    *counter_bytes = kStaticCounterCount * sizeof(uint32_t);
     return cudaSuccess;
 }
 
+// variant encoding (0 = heuristics): bits 0-3 CTAs per SM (at most what fits), bit 4 the fp16 form also at
+// M <= 4 (default there: the integer form), bits 8-11 an upper limit on the K parts of a pair block,
+// bit 14 no programmatic dependent launch
+cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool sequence, DecodeGeometry *geometry) {
+    if (m_rows == 0 || m_rows > decode_max_m()) return cudaErrorInvalidValue;
+    geometry->mode = mode_of(m_rows, variant);
+    geometry->smem_bytes = smem_of(geometry->mode);
+    int per_sm = 0;
+    cudaError_t status = configure_mode(geometry->mode, sequence, geometry->smem_bytes, &per_sm);
+    if (status != cudaSuccess) return status;
+    if (per_sm > 2) per_sm = 2;
+    const int wanted = variant & 0xf;
+    if (wanted >= 1 && wanted < per_sm) per_sm = wanted;
+    geometry->ctas = (uint32_t)(per_sm * sm_count);
+    geometry->threads = kDecodeThreads;
+    geometry->max_parts = (uint32_t)((variant >> 8) & 0xf);
+    return cudaSuccess;
+}
+
+void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geometry, size_t *scratch_bytes,
+                     size_t *counter_bytes) {
+    (void)m_rows;
+    const uint32_t G = job->groups;
+    uint32_t pairs = 0;
+    for (uint32_t s = 0; s < job->segments; ++s) {
+        job->pair_begin[s] = pairs;
+        pairs += job->fused ? ceil_div(job->rows[s], 64) : ceil_div(job->rows[s], 128);
+    }
+    for (uint32_t s = job->segments; s <= (uint32_t)kMaxSegments; ++s) job->pair_begin[s] = pairs;
+    // Fewer pair blocks than CTAs: cut K into equal parts so that the whole grid streams, a part no shorter
+    // than four groups.  Otherwise every CTA takes whole pair blocks in turn.
+    uint32_t parts = 1;
+    if (pairs < geometry.ctas) {
+        for (uint32_t k = 1; k <= G; ++k) {
+            if (pairs * k <= geometry.ctas && (G / k >= 4 || k == 1)) parts = k;
+        }
+    }
+    if (geometry.max_parts > 0 && parts > geometry.max_parts) parts = geometry.max_parts;
+    job->parts = parts;
+    job->units = pairs * parts;
+    const size_t vals = geometry.mode == 0 ? 2 : geometry.mode == 1 ? 4 : 8;
+    *scratch_bytes = parts > 1 ? (size_t)job->units * 8 * 32 * vals * sizeof(float) : 0;
+    *counter_bytes = parts > 1 ? (size_t)pairs * 8 * sizeof(uint32_t) : 0;
+}
+
+namespace {
+
+template <int MODE, bool SEQ>
+cudaError_t launch_kernel(const PassParams &p, uint32_t ctas, size_t smem_bytes, bool dependent_launch,
+                          cudaStream_t stream) {
+    auto kernel = decode_kernel<MODE, SEQ>;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(ctas);
+    config.blockDim = dim3(kDecodeThreads);
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    if (SEQ) {
+        // the CTAs wait on one another: all of them must be resident
+        attribute[0].id = cudaLaunchAttributeCooperative;
+        attribute[0].val.cooperative = 1;
+        config.numAttrs = 1;
+    } else {
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.numAttrs = dependent_launch ? 1 : 0;
+    }
+    config.attrs = attribute;
+    return cudaLaunchKernelEx(&config, kernel, p);
+}
+
+}  // namespace
+
+cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeometry &geometry, int variant,
+                          float *scratch, uint32_t *counters, uint32_t *status, cudaStream_t stream) {
+    PassParams p = {};
+    p.job = job;
+    p.job_count = 1;
+    p.m_rows = m_rows;
+    p.world = 1;
+    p.scratch = scratch;
+    p.counters = counters;
+    p.status = status;
+    const uint32_t ctas = job.units < geometry.ctas ? job.units : geometry.ctas;
+    const bool pdl = ((variant >> 14) & 1) == 0;
+    switch (geometry.mode) {
+        case 0: return launch_kernel<0, false>(p, ctas, geometry.smem_bytes, pdl, stream);
+        case 1: return launch_kernel<1, false>(p, ctas, geometry.smem_bytes, pdl, stream);
+        default: return launch_kernel<2, false>(p, ctas, geometry.smem_bytes, pdl, stream);
+    }
+}
+
 cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream) {
-    SeqParams p = {};
+    PassParams p = {};
     p.jobs = launch.jobs;
     p.job_count = launch.job_count;
-    p.stages = launch.stages;
     p.m_rows = launch.m_rows;
-    p.max_local_blocks = launch.max_local_blocks;
     p.world = launch.world;
-    p.rank = launch.rank;
     p.epoch = launch.epoch;
+    p.exit_count = launch.exit_count;
     p.done = launch.done;
     for (int r = 0; r < kMaxPeers; ++r) p.peer_done[r] = launch.peer_done[r];
     p.scratch = launch.scratch;
     p.counters = launch.counters;
     p.status = launch.status;
-    void *arguments[] = {&p};
-    const void *kernel = launch.m_rows <= 8 ? reinterpret_cast<const void *>(decode_sequence_kernel<1>)
-                                            : reinterpret_cast<const void *>(decode_sequence_kernel<2>);
-    // cooperative: the CTAs wait on one another, so all of them must be resident
-    return cudaLaunchCooperativeKernel(kernel, dim3(launch.ctas), dim3(288), arguments, launch.smem_bytes, stream);
+    switch (launch.geometry.mode) {
+        case 0: return launch_kernel<0, true>(p, launch.geometry.ctas, launch.geometry.smem_bytes, false, stream);
+        case 1: return launch_kernel<1, true>(p, launch.geometry.ctas, launch.geometry.smem_bytes, false, stream);
+        default: return launch_kernel<2, true>(p, launch.geometry.ctas, launch.geometry.smem_bytes, false, stream);
+    }
 }
 
 }  // namespace q4b

@@ -652,11 +652,12 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
                               (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + kTcWarpgroups * 16 * 128 * 4 + 1024;
     auto kernel = tc_gemm_kernel<BN, FUSED, BF>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[kMaxDevices];  // per instantiation and device
+    const int slot = device_slot();
+    if (slot < 0 || !configured[slot]) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (status != cudaSuccess) return status;
-        configured = true;
+        if (slot >= 0) configured[slot] = true;
     }
     unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
     // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last round

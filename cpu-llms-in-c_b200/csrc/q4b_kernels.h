@@ -2,7 +2,19 @@
 #pragma once
 #include "q4b_common.cuh"
 
+struct q4b_context;
+
 namespace q4b {
+
+// cudaFuncSetAttribute applies to one device: the launchers remember what they set per device, so that a
+// process with contexts on several GPUs configures each of them.  Returns -1 for a device beyond the table
+// (the caller then sets the attribute on every launch).
+constexpr int kMaxDevices = 64;
+inline int device_slot() {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return -1;
+    return device;
+}
 
 // ---- q4b_pack.cu ----
 // raw image planes (device) -> tile stream.  rows_total/groups describe the
@@ -19,6 +31,10 @@ cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
 // out[i][K] fp16 or fp32; rows the shard does not hold give zeros
 cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t count, uint32_t row_base, void *out,
                                int out_dtype, cudaStream_t stream);
+// y[m][slot] = sum_k w(ids[slot], k) x[m][k] for the listed rows (device ids, numbered in the whole matrix) that
+// this shard holds; m_rows <= 16
+cudaError_t launch_matmul_rows(WeightView w, const uint32_t *ids, uint32_t count, uint32_t row_base, const void *x,
+                               int x_dtype, uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, cudaStream_t stream);
 // output[b][i] = half(input[b][i] * inv_rms(b) * weight[i]), input fp16 or fp32 [batch][hidden], one block per row
 cudaError_t launch_rmsnorm(const void *input, int input_dtype, const float *weight, void *output, uint32_t hidden,
                            uint32_t batch, float epsilon, cudaStream_t stream);
@@ -29,10 +45,52 @@ cudaError_t launch_synth_meta(uint64_t seed, uint64_t stream_id, __half *meta,
 cudaError_t launch_synth_x(uint64_t seed, uint64_t stream_id, __half *x, uint64_t begin,
                            uint64_t count, cudaStream_t stream);
 
-// ---- q4b_gemv.cu ----
+// ---- q4b_decode.cu: decode GEMV / small-M GEMM, one projection per launch or a whole pass in one launch ----
 constexpr int kMaxSegments = 4;
 constexpr int kMaxPeers = 8;
-struct GemvArgs {
+constexpr uint32_t kDoneStride = 32;  // words between the completion sub-counters of a sequence (one L2 line each)
+
+// One projection as the decode kernel reads it (a kernel argument for a single launch, a row of the job table
+// in device memory for a sequence): up to kMaxSegments matrices that share x (same K), or a fused gate/up
+// pair (segment 0 = gate) with the SiLU-gate epilogue.
+struct DecodeJob {
+    const uint8_t *tiles[kMaxSegments];
+    const uint8_t *up_tiles;           // fused gate/up: the second matrix
+    void *y[kMaxSegments][kMaxPeers];  // where segment s goes on rank r (own rank included), column offset applied;
+                                       // a single launch uses rank 0 only
+    const void *x;                     // [M][K] fp16 or fp32
+    const void *residual;              // [M][ld_residual] or null; added to segment 0 only
+    uint32_t rows[kMaxSegments];
+    uint32_t ldy[kMaxSegments];
+    uint32_t pair_begin[kMaxSegments + 1];  // prefix sums of pair blocks (128 rows; 64 gate + 64 up rows when fused)
+    uint32_t groups, segments, fused;
+    int x_dtype, y_dtype, residual_dtype;
+    uint32_t ld_residual;
+    uint32_t parts, units;             // K parts per pair block; units = pair blocks x parts
+    uint32_t expected_blocks;          // 64-row blocks all ranks publish for this job per launch (sequences)
+};
+// what depends on M, the variant and the device only
+struct DecodeGeometry {
+    int mode;            // 0 integer form (M <= 4), 1 fp16 form M <= 8, 2 fp16 form M <= 16
+    uint32_t ctas;       // CTAs that are resident at once (the grid of a sequence; the limit of a single launch)
+    uint32_t threads;
+    uint32_t max_parts;  // 0: no limit on the K parts of a pair block
+    size_t smem_bytes;
+};
+struct SequenceLaunch {
+    const DecodeJob *jobs;     // device
+    uint32_t job_count, m_rows, world;
+    DecodeGeometry geometry;
+    uint32_t *epoch;           // device word, zeroed once: launches completed
+    uint32_t *exit_count;      // device word, zero between launches
+    uint32_t *done;            // device, [job_count][8] x kDoneStride words, zeroed once; counts up across launches
+    uint32_t *peer_done[kMaxPeers];
+    float *scratch;
+    uint32_t *counters;
+    uint32_t *status;
+};
+// a projection as the entry points of the C ABI describe it, before it is routed to a kernel by M
+struct ProjectionArgs {
     // up to kMaxSegments matrices that share x (same K); fused gate/up uses
     // segment 0 = gate, `up` = the second matrix, one output
     WeightView w[kMaxSegments];
@@ -42,62 +100,25 @@ struct GemvArgs {
     WeightView up;       // valid when fused_silu
     int fused_silu;
     const void *x;       // [M][K]
-    int x_dtype;         // kF16 / kF32
+    int x_dtype;         // kF16 / kF32 / kBF16
     uint32_t m_rows;
-    int y_dtype;         // kF16 / kF32
+    int y_dtype;
     const void *residual;  // [M][ld_residual] or null (segment 0 only)
     int residual_dtype;
     uint32_t ld_residual;
-    uint32_t *status;      // device-visible word that receives a code when a wait expires
-    float *scratch;        // global partial-sum slots (plan.scratch_bytes)
-    uint32_t *counters;    // zero-initialised, self-resetting (plan.counter_bytes)
 };
-// launch geometry and the scratch a launch needs, derived from the shapes alone
-struct GemvPlan {
-    uint32_t ctas, threads, stages, stage_units, total_units, blocks;
-    uint32_t local_blocks, slots, parts;
-    size_t smem_bytes, scratch_bytes, counter_bytes;
-};
-// variant: 0 = default; other values select alternatives for A/B measurements
-cudaError_t plan_gemv(const GemvArgs &args, int variant, int sm_count, GemvPlan *plan);
-cudaError_t launch_gemv(const GemvArgs &args, const GemvPlan &plan, int variant, cudaStream_t stream);
-uint32_t gemv_max_m();
-// device addresses and sizes of the library's built-in (never allocated) scratch on the current device
-cudaError_t gemv_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
-                                size_t *counter_bytes);
-
-// ---- q4b_decode.cu: job sequences in one persistent launch ----
-// One projection (a group of matrices sharing x, or a fused gate/up pair) as the
-// sequence kernel reads it from device memory.
-struct DecodeJob {
-    const uint8_t *tiles[kMaxSegments];
-    const uint8_t *up_tiles;
-    void *y[kMaxSegments][kMaxPeers];  // where segment s goes on rank r (own rank included), column offset applied
-    const void *x;                     // [M][K] fp16
-    uint32_t rows[kMaxSegments];
-    uint32_t ldy[kMaxSegments];
-    uint32_t block_begin[kMaxSegments + 1];
-    uint32_t groups, segments, fused, y_dtype;
-    uint32_t total_units, units_per_cta, units_extra, parts, active_ctas, slots, local_blocks;
-    uint32_t expected_blocks;  // row blocks all ranks publish for this job per launch (0: blocks * world)
-};
-struct SequenceLaunch {
-    const DecodeJob *jobs;     // device
-    uint32_t job_count, m_rows, stages, ctas, max_local_blocks;
-    uint32_t world, rank, epoch;
-    uint32_t *done;            // device, [job_count], zeroed once; counts up across launches
-    uint32_t *peer_done[kMaxPeers];
-    float *scratch;
-    uint32_t *counters;
-    uint32_t *status;
-    size_t smem_bytes;
-};
-// fills the partition fields of `job` for a grid of `ctas`; returns scratch needs
-void plan_decode_job(DecodeJob *job, uint32_t m_rows, uint32_t ctas, size_t *scratch_bytes, size_t *counter_bytes);
-// grid size and shared memory of the sequence kernel on the current device
-cudaError_t sequence_geometry(uint32_t m_rows, int sm_count, uint32_t stages, uint32_t max_local_blocks,
-                              uint32_t *ctas, size_t *smem_bytes);
+uint32_t decode_max_m();
+// variant: 0 = default; other values select alternatives for A/B measurements (see q4b_decode.cu)
+cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool sequence, DecodeGeometry *geometry);
+// fills pair_begin, parts and units of `job`; returns the split-K scratch it needs (0 when K is not split)
+void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geometry, size_t *scratch_bytes,
+                     size_t *counter_bytes);
+cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeometry &geometry, int variant,
+                          float *scratch, uint32_t *counters, uint32_t *status, cudaStream_t stream);
 cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream);
+// device addresses and sizes of the library's built-in (never allocated) scratch on the current device
+cudaError_t decode_static_scratch(float **scratch, uint32_t **counters, size_t *scratch_bytes,
+                                  size_t *counter_bytes);
 
 // ---- q4b_gemm.cu: tcgen05 prefill GEMM ----
 struct TcGemmArgs {
@@ -130,6 +151,10 @@ cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count
 // `expected` arrivals; a wait that expires stores a code in *status.
 cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t expected,
                                 uint32_t *status, cudaStream_t stream);
+
+// ---- q4b_api.cu: what the other host files need to know of a context ----
+int context_device(const q4b_context *context);
+void context_count_launch(q4b_context *context);  // one more kernel of this library queued (not while recording)
 
 // ---- q4b_probe.cu ----
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,

@@ -185,7 +185,7 @@ int q4b_layer_encode_mlp(q4b_context *context, const q4b_layer *layer, const voi
     if (layer != nullptr && layer->world != 1) {
         // down reads the WHOLE intermediate: with ranks, gather between the two halves
         layer_message(error_message, error_capacity,
-                      "with %u ranks call q4b_layer_encode_gate_up, gather, then q4b_layer_encode_down", layer->world);
+                      "with %u ranks call q4b_layer_encode_mlp_gathered (gate/up, gather, down, gather)", layer->world);
         return Q4B_BAD_ARGUMENT;
     }
     const int status = q4b_layer_encode_gate_up(context, layer, post_normalized_f16, batch, intermediate,
@@ -193,6 +193,57 @@ int q4b_layer_encode_mlp(q4b_context *context, const q4b_layer *layer, const voi
     if (status != Q4B_OK) return status;
     return q4b_layer_encode_down(context, layer, intermediate, intermediate_dtype, batch, residual, residual_dtype,
                                  layer_output, output_dtype, error_message, error_capacity);
+}
+
+int q4b_layer_gather(q4b_context *context, const q4b_layer *layer, q4b_comm *comm, int matrix, void *full_width,
+                     int dtype, uint32_t batch, void *staging, char *error_message, size_t error_capacity) {
+    if (layer == nullptr || comm == nullptr || full_width == nullptr || matrix < 0 || matrix >= 5 || batch == 0 ||
+        q4b_comm_world(comm) != layer->world || q4b_comm_rank(comm) != layer->rank) {
+        layer_message(error_message, error_capacity, "layer, communicator or buffer missing, or of different worlds");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const uint32_t rows = layer->rows[matrix], count = layer->count[matrix], world = layer->world;
+    if (count * world != rows || layer->begin[matrix] != layer->rank * count) {
+        layer_message(error_message, error_capacity, "the ranks' slices of matrix %d are not equal (%u rows over %u ranks)",
+                      matrix, rows, world);
+        return Q4B_BAD_ARGUMENT;
+    }
+    const size_t width = element_bytes(dtype);
+    unsigned char *base = static_cast<unsigned char *>(full_width);
+    if (batch == 1) {  // one row: every slice is already where the all-gather puts it
+        return q4b_all_gather(context, comm, base + (size_t)layer->begin[matrix] * width, base, (size_t)count * width,
+                              error_message, error_capacity);
+    }
+    if (staging == nullptr) {
+        layer_message(error_message, error_capacity, "batch > 1 needs a staging buffer");
+        return Q4B_BAD_ARGUMENT;
+    }
+    // pack this rank's columns, gather rank-major, interleave back into rows
+    unsigned char *packed = static_cast<unsigned char *>(staging);
+    unsigned char *blocks = packed + (size_t)batch * count * width;
+    int status = q4b_copy_2d(context, packed, (size_t)count * width, base + (size_t)layer->begin[matrix] * width,
+                             (size_t)rows * width, (size_t)count * width, batch, error_message, error_capacity);
+    if (status != Q4B_OK) return status;
+    return q4b_all_gather_columns(context, comm, packed, full_width, batch, count, (uint32_t)width, blocks,
+                                  error_message, error_capacity);
+}
+
+int q4b_layer_encode_mlp_gathered(q4b_context *context, const q4b_layer *layer, q4b_comm *comm,
+                                  const void *post_normalized_f16, uint32_t batch, void *intermediate,
+                                  int intermediate_dtype, const void *residual, int residual_dtype,
+                                  void *layer_output, int output_dtype, void *staging, char *error_message,
+                                  size_t error_capacity) {
+    int status = q4b_layer_encode_gate_up(context, layer, post_normalized_f16, batch, intermediate, intermediate_dtype,
+                                          error_message, error_capacity);
+    if (status != Q4B_OK) return status;
+    status = q4b_layer_gather(context, layer, comm, Q4B_MATRIX_GATE, intermediate, intermediate_dtype, batch, staging,
+                              error_message, error_capacity);
+    if (status != Q4B_OK) return status;
+    status = q4b_layer_encode_down(context, layer, intermediate, intermediate_dtype, batch, residual, residual_dtype,
+                                   layer_output, output_dtype, error_message, error_capacity);
+    if (status != Q4B_OK) return status;
+    return q4b_layer_gather(context, layer, comm, Q4B_MATRIX_DOWN, layer_output, output_dtype, batch, staging,
+                            error_message, error_capacity);
 }
 
 }  // extern "C"

@@ -220,6 +220,88 @@ cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t coun
 }
 
 // ---------------------------------------------------------------------------
+// Listed rows only: y[m][slot] = sum_k w(ids[slot], k) x[m][k] -- the draft head's extra vocabulary rows
+// (qwen38_q4_lm_head_gathered, qwen38_global.metal:68-96: one simdgroup per gathered row id, w =
+// float(scale) * q + float(bias), fp32 sum).  One warp per listed row: lane = (group phase lane / 4, quarter
+// lane % 4) reads the 16 codes of that row in each of its (group, quarter) cells and the cell's 16 activations;
+// a butterfly over the warp finishes the row.  A listed row costs 64 bytes per group (its tile partner's
+// nibbles ride along), which matters not at all for the few hundred rows such a list holds.
+// ---------------------------------------------------------------------------
+template <typename X>
+__global__ void __launch_bounds__(256)
+matmul_rows_kernel(WeightView w, const uint32_t *__restrict__ ids, uint32_t count, uint32_t row_base,
+                   const X *__restrict__ x, uint32_t m_rows, void *__restrict__ y, int y_dtype, uint32_t ldy) {
+    const uint32_t slot = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (slot >= count) return;
+    const uint32_t row = ids[slot] - row_base;  // rows outside this shard wrap to huge values
+    if (row >= w.rows) return;                  // not held here: the rank that holds it writes the slot
+    const uint32_t rt = row >> 4, within = row & 15u, gid = within & 7u, upper = within >> 3;
+    const uint32_t t = lane & 3u;
+    const size_t K = (size_t)w.groups * kGroup;
+    float acc[16];
+#pragma unroll
+    for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
+    for (uint32_t g = lane >> 2; g < w.groups; g += 8) {
+        const uint8_t *in = w.tiles + tile_offset(rt, g, w.groups);
+        const uint4 words = reinterpret_cast<const uint4 *>(in)[piece_index(gid * 4 + t)];
+        const uint2 record = reinterpret_cast<const uint2 *>(in + kTileCodeBytes)[gid];
+        const __half2 meta = *reinterpret_cast<const __half2 *>(upper ? &record.y : &record.x);
+        const float scale = __low2float(meta), bias = __high2float(meta);
+        const uint32_t word[4] = {words.x, words.y, words.z, words.w};
+        float weight[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t nibble = 4u * (c & 1) + 2u * (c >> 1) + upper;
+                weight[4 * i + c] = dequant_w32((word[i] >> (4u * nibble)) & 0xfu, scale, bias);
+            }
+        }
+        for (uint32_t m = 0; m < m_rows; ++m) {
+            const X *cell = x + (size_t)m * K + (size_t)g * kGroup + 16 * t;
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float value;
+                if constexpr (sizeof(X) == 2) value = __half2float(cell[i]);
+                else value = cell[i];
+                sum = fmaf(weight[i], value, sum);
+            }
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                if ((uint32_t)q == m) acc[q] += sum;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+        float total = acc[m];
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+        if (lane == 0 && (uint32_t)m < m_rows) {
+            const size_t at = (size_t)m * ldy + slot;
+            if (y_dtype == kF32) reinterpret_cast<float *>(y)[at] = total;
+            else reinterpret_cast<__half *>(y)[at] = __float2half_rn(total);
+        }
+    }
+}
+
+cudaError_t launch_matmul_rows(WeightView w, const uint32_t *ids, uint32_t count, uint32_t row_base, const void *x,
+                               int x_dtype, uint32_t m_rows, void *y, int y_dtype, uint32_t ldy, cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    if (m_rows == 0 || m_rows > 16) return cudaErrorInvalidValue;
+    const unsigned blocks = (count + 7) / 8;
+    if (x_dtype == kF32) {
+        matmul_rows_kernel<float><<<blocks, 256, 0, stream>>>(w, ids, count, row_base, static_cast<const float *>(x),
+                                                              m_rows, y, y_dtype, ldy);
+    } else {
+        matmul_rows_kernel<__half><<<blocks, 256, 0, stream>>>(w, ids, count, row_base, static_cast<const __half *>(x),
+                                                               m_rows, y, y_dtype, ldy);
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // RMS norm: the step that produces the fp16 x of a layer's in-projections and of the MLP
 // (qwen38_rmsnorm_f16_to_f16 / qwen38_rmsnorm_f32_to_f16, qwen38_layer.metal:21-69; one thread block per
 // activation row as in their batched forms).  Same order of operations as the reference: 256 strided partial

@@ -84,6 +84,8 @@ def library() -> ctypes.CDLL:
         "q4b_weight_unpack": (_int, [_vp, _vp, _vp, _vp, _vp] + err),
         "q4b_matmul": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, _u32, _vp, _int, _u32] + err),
         "q4b_matmul_no_alloc": (_int, [_vp, _vp, _vp, _int, _u32, _vp, _int, _u32] + err),
+        "q4b_weight_rows": (_int, [_vp, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_matmul_rows": (_int, [_vp, _vp, _vp, _u32, _vp, _int, _u32, _vp, _int, _u32] + err),
         "q4b_matmul_group": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, _int, _u32, ctypes.POINTER(_vp),
                                     _int, ctypes.POINTER(_u32)] + err),
         "q4b_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _vp, _int, _u32] + err),
@@ -102,6 +104,7 @@ def library() -> ctypes.CDLL:
         "q4b_sequence_add_matmul": (_int, [_vp, ctypes.POINTER(_vp), _int, _vp, ctypes.POINTER(_vp),
                                            ctypes.POINTER(_u32), _int] + err),
         "q4b_sequence_add_gate_up": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _int] + err),
+        "q4b_sequence_add_projection": (_int, [_vp, _vp, _vp, _int, _vp, _int, _u32, _vp, _int, _u32] + err),
         "q4b_sequence_set_peer_output": (_int, [_vp, _u32, _u32, _u32, _vp]),
         "q4b_sequence_set_job_blocks": (_int, [_vp, _u32, _u32]),
         "q4b_sequence_finalize": (_int, [_vp, _vp] + err),
@@ -112,6 +115,14 @@ def library() -> ctypes.CDLL:
         "q4b_ipc_export": (_int, [_vp, _vp, _vp] + err),
         "q4b_ipc_open": (_int, [_vp, _vp, ctypes.POINTER(_vp)] + err),
         "q4b_ipc_close": (_int, [_vp, _vp]),
+        "q4b_copy_2d": (_int, [_vp, _vp, _sz, _vp, _sz, _sz, _sz] + err),
+        "q4b_comm_unique_id": (_int, [_vp] + err),
+        "q4b_comm_create": (_int, [_vp, _u32, _u32, _vp, ctypes.POINTER(_vp)] + err),
+        "q4b_comm_world": (_u32, [_vp]),
+        "q4b_comm_rank": (_u32, [_vp]),
+        "q4b_all_gather": (_int, [_vp, _vp, _vp, _vp, _sz] + err),
+        "q4b_all_gather_columns": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp] + err),
+        "q4b_comm_free": (None, [_vp, _vp]),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
@@ -200,6 +211,13 @@ class Q4Weight:
                                                         self.context._err, _ERR))
         return c, a, (None if b is None else b.view(np.float16))
 
+    def rows_view(self, row_begin: int, row_count: int) -> "Q4Weight":
+        """Rows [row_begin, +row_count) of this weight as a weight of their own, no copy (q4b_weight_rows)."""
+        handle = _vp()
+        self.context._check(library().q4b_weight_rows(self.handle, row_begin, row_count, ctypes.byref(handle),
+                                                      self.context._err, _ERR))
+        return Q4Weight(self.context, handle.value)
+
     def free(self):
         if self.handle:
             library().q4b_weight_free(self.context.handle, self.handle)
@@ -250,6 +268,15 @@ class Q4Sequence:
         strides = (_u32 * count)(*(ldys if ldys is not None else [w.rows for w in weights]))
         self.context._check(library().q4b_sequence_add_matmul(self.handle, handles, count, x_ptr, outputs, strides,
                                                               y_dtype, self.context._err, _ERR))
+        self.jobs += 1
+        return self.jobs - 1
+
+    def add_projection(self, weight, x_ptr: int, x_dtype: int, y_ptr: int, y_dtype: int = F16, ldy=None,
+                       residual_ptr=None, residual_dtype: int = NONE, ld_residual: int = 0) -> int:
+        """One matrix with fp16 or fp32 x and an optional residual."""
+        self.context._check(library().q4b_sequence_add_projection(
+            self.handle, weight.handle, x_ptr, x_dtype, y_ptr, y_dtype, weight.rows if ldy is None else ldy,
+            residual_ptr, residual_dtype, ld_residual, self.context._err, _ERR))
         self.jobs += 1
         return self.jobs - 1
 
@@ -391,6 +418,12 @@ class Q4Context:
                                          weight.rows if ldy is None else ldy, residual_ptr, residual_dtype,
                                          ld_residual, self._err, _ERR))
 
+    def matmul_rows(self, weight: Q4Weight, row_ids_ptr: int, count: int, x_ptr: int, x_dtype: int, m_rows: int,
+                    y_ptr: int, y_dtype: int = F32, ldy: int | None = None):
+        """Listed rows of the matrix only (q4b_matmul_rows): y[m][slot] for row_ids[slot]."""
+        self._check(library().q4b_matmul_rows(self.handle, weight.handle, row_ids_ptr, count, x_ptr, x_dtype, m_rows,
+                                              y_ptr, y_dtype, count if ldy is None else ldy, self._err, _ERR))
+
     def matmul_no_alloc(self, weight: Q4Weight, x_ptr: int, x_dtype: int, m_rows: int, y_ptr: int,
                         y_dtype: int = F16, ldy: int | None = None):
         """q4b_matmul with the library's built-in scratch array: allocates nothing."""
@@ -510,3 +543,35 @@ class Q4Barrier:
             library().q4b_barrier_free(self.context.handle, self.handle)
             self.handle = None
 
+
+
+class Q4Comm:
+    """NCCL communicator of the column-parallel ranks (q4b_comm_*).  `exchange(payload_bytes) -> list of every
+    rank's payload` is any out-of-band all-gather of small byte strings the launcher has (a process group, a
+    file, a socket): rank 0 makes the id, everybody gets it."""
+
+    def __init__(self, context: Q4Context, world: int, rank: int, exchange):
+        self.context, self.world, self.rank = context, world, rank
+        unique = ctypes.create_string_buffer(128)
+        if rank == 0:
+            context._check(library().q4b_comm_unique_id(unique, context._err, _ERR))
+        unique = ctypes.create_string_buffer(exchange(unique.raw)[0], 128)
+        handle = _vp()
+        context._check(library().q4b_comm_create(context.handle, world, rank, unique, ctypes.byref(handle),
+                                                 context._err, _ERR))
+        self.handle = handle
+
+    def all_gather(self, slice_ptr: int, gathered_ptr: int, bytes_per_rank: int):
+        self.context._check(library().q4b_all_gather(self.context.handle, self.handle, slice_ptr, gathered_ptr,
+                                                     bytes_per_rank, self.context._err, _ERR))
+
+    def all_gather_columns(self, slice_ptr: int, full_ptr: int, m_rows: int, slice_columns: int, element_bytes: int,
+                           staging_ptr: int | None):
+        self.context._check(library().q4b_all_gather_columns(self.context.handle, self.handle, slice_ptr, full_ptr,
+                                                             m_rows, slice_columns, element_bytes, staging_ptr,
+                                                             self.context._err, _ERR))
+
+    def free(self):
+        if self.handle:
+            library().q4b_comm_free(self.context.handle, self.handle)
+            self.handle = None

@@ -1,4 +1,4 @@
-"""A stack of Q4 layers on one rank of a column-parallel job (BASELINE configs[4]).
+"""A stack of Q4 layers on one rank of a column-parallel job.
 
 Every projection of every layer is split by output rows over `world` ranks;
 each rank owns its slice's tile stream, computes Y[:, n0:n1] from the full x and
@@ -11,10 +11,11 @@ Two gather paths:
               only when all ranks have published the previous one; M > 16: the
               tensor-core GEMM pushes (q4b_context_push_outputs) and a one-thread
               barrier kernel follows every projection group (q4b_barrier_queue);
-  * "nccl"  : torch.distributed all_gather_into_tensor per gather point, queued
-              on the context's stream (the baseline and the cross-check).
-With world == 1 neither runs.  torch is imported only when world > 1 (process
-group for the handle exchange, NCCL for the baseline).
+  * "nccl"  : q4b_all_gather_columns (ncclAllGather + interleave) per gather
+              point, queued on the context's stream (the baseline and the
+              cross-check).
+With world == 1 neither runs.  The caller's process group (world > 1) only
+carries handles and the communicator's id between the ranks.
 """
 from __future__ import annotations
 
@@ -22,16 +23,23 @@ import ctypes
 
 import numpy as np
 
-from .host import F16, Q4Barrier, Q4Context, Q4Sequence, library
+from .host import F16, Q4Barrier, Q4Comm, Q4Context, Q4Sequence, library
 from .layer import Q4Layer, slice_of
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on the 27B gate/up pair at M = 1
+NCU_GATE_UP_TRAFFIC_BYTES = None
 
 
 class ShardedLayerStack:
     def __init__(self, ctx: Q4Context, layer_set, n_layers: int, m_rows: int, rank: int = 0, world: int = 1,
-                 dist=None, gather: str = "push", mode: str = "graph"):
+                 dist=None, gather: str = "push", mode: str = "graph", layers=None):
         self.ctx, self.layer_set, self.n_layers, self.m = ctx, tuple(layer_set), n_layers, m_rows
         self.rank, self.world, self.dist, self.gather = rank, world, dist, gather
-        self.layers = [Q4Layer(ctx, layer_set, seed, rank, world) for seed in range(n_layers)]
+        # weights do not depend on M: a second stack (another M) may share the first one's layers
+        self.owns_layers = layers is None
+        self.layers = layers if layers is not None else [Q4Layer(ctx, layer_set, seed, rank, world)
+                                                         for seed in range(n_layers)]
         self.ks = sorted({p.k for p in self.layer_set})
         self.graph = None
         self.sequence = None
@@ -59,28 +67,31 @@ class ShardedLayerStack:
         self.y_layer_bytes = offset
         self.h2d_bytes_per_step = self.x_layer_bytes * n_layers
         self.d2h_bytes_per_step = self.y_layer_bytes * n_layers
-        self._torch = None
+        self.comm = None
         self.barrier = None
         if world > 1 and gather == "push" and m_rows <= 16:
             self._setup_push()
         elif world > 1 and gather == "push":
             self._setup_push_gemm()
         elif world > 1:
-            import torch
-            self._torch = torch
             self.gather = "nccl"
-            self.stream = torch.cuda.ExternalStream(ctx.stream)
-            self.y_torch = torch.zeros(self.y_layer_bytes * n_layers // 2, dtype=torch.float16, device="cuda")
-            self.y_base = self.y_torch.data_ptr()
+            # the process group only carries the communicator's id; the gathers themselves are q4b_all_gather*
+            def exchange(payload: bytes):
+                everyone = [None] * world
+                dist.all_gather_object(everyone, payload)
+                return everyone
+            self.comm = Q4Comm(ctx, world, rank, exchange)
+            self.y_all = ctx.alloc(self.y_layer_bytes * n_layers)
+            self.y_base = self.y_all.ptr
             # this rank's slices, one contiguous block per layer: [projection][M][n_local]
             self.local_offsets, offset = {}, 0
             for p in self.layer_set:
                 self.local_offsets[p.name] = offset
                 offset += m_rows * slice_of(p.n, rank, world)[1] * 2
             self.local_layer_bytes = offset
-            self.local_torch = torch.zeros(offset * n_layers // 2, dtype=torch.float16, device="cuda")
-            self.local_base = self.local_torch.data_ptr()
-            self.staging = torch.zeros(max(m_rows * p.n for p in self.layer_set), dtype=torch.float16, device="cuda")
+            self.local_all = ctx.alloc(offset * n_layers)
+            self.local_base = self.local_all.ptr
+            self.staging = ctx.alloc(max(m_rows * p.n for p in self.layer_set) * 2)
         else:
             self.y_all = ctx.alloc(self.y_layer_bytes * n_layers)
             self.y_base = self.y_all.ptr
@@ -184,25 +195,15 @@ class ShardedLayerStack:
             layer.forward(self._x_ptrs(index), {p.name: base + self.y_offsets[p.name] for p in self.layer_set}, self.m)
 
     def _queue_sharded_nccl(self):
-        torch, dist = self._torch, self.dist
-        with torch.cuda.stream(self.stream):
-            for index, layer in enumerate(self.layers):
-                local = self.local_base + index * self.local_layer_bytes
-                layer.forward(self._x_ptrs(index), {p.name: local + self.local_offsets[p.name] for p in self.layer_set},
-                              self.m)
-                for p in self.layer_set:
-                    n_local = slice_of(p.n, self.rank, self.world)[1]
-                    start = (index * self.local_layer_bytes + self.local_offsets[p.name]) // 2
-                    piece = self.local_torch[start:start + self.m * n_local]
-                    begin = (index * self.y_layer_bytes + self.y_offsets[p.name]) // 2
-                    full = self.y_torch[begin:begin + self.m * p.n]
-                    if self.m == 1:
-                        dist.all_gather_into_tensor(full, piece)
-                    else:
-                        staging = self.staging[:self.m * p.n]
-                        dist.all_gather_into_tensor(staging, piece)
-                        full.view(self.m, self.world, n_local).copy_(
-                            staging.view(self.world, self.m, n_local).permute(1, 0, 2))
+        for index, layer in enumerate(self.layers):
+            local = self.local_base + index * self.local_layer_bytes
+            layer.forward(self._x_ptrs(index), {p.name: local + self.local_offsets[p.name] for p in self.layer_set},
+                          self.m)
+            for p in self.layer_set:
+                n_local = slice_of(p.n, self.rank, self.world)[1]
+                piece = local + self.local_offsets[p.name]
+                full = self.y_base + index * self.y_layer_bytes + self.y_offsets[p.name]
+                self.comm.all_gather_columns(piece, full, self.m, n_local, 2, self.staging.ptr)
 
     def step(self):
         """One pass over all layers, queued on the context stream."""
@@ -244,13 +245,30 @@ class ShardedLayerStack:
 
     def dominant_kernel_pass(self):
         """The fused gate/up kernel alone, once per layer (distinct weights)."""
-        fused = next(p for p in self.layer_set if p.fused)
+        self.projection_pass(next(p.name for p in self.layer_set if p.fused))
+
+    def projection_pass(self, name: str):
+        """One launch group of the layer alone (the group's first member names it), once per layer: this rank's
+        slice, outputs where the whole pass puts them, no gather."""
         for index, layer in enumerate(self.layers):
-            gate, up = layer.weights[fused.name]
-            out = (self.local_base + index * self.local_layer_bytes + self.local_offsets[fused.name]
-                   if self.world > 1 and self.gather == "nccl"
-                   else self.y_base + index * self.y_layer_bytes + self.y_offsets[fused.name])
-            self.ctx.gate_up_silu(gate, up, self._x_ptrs(index)[fused.k], F16, self.m, out, F16)
+            kind, members = next((k, ms) for k, ms in layer.launch_plan() if ms[0].name == name)
+            outs = []
+            for p in members:
+                if self.world > 1 and self.gather == "nccl":
+                    outs.append(self.local_base + index * self.local_layer_bytes + self.local_offsets[p.name])
+                else:
+                    outs.append(self.y_base + index * self.y_layer_bytes + self.y_offsets[p.name] +
+                                layer.slices[p.name][0] * 2)
+            wide = self.world > 1 and self.gather != "nccl"
+            strides = [p.n if wide else layer.slices[p.name][1] for p in members]
+            x = self._x_ptrs(index)[members[0].k]
+            if kind == "group":
+                self.ctx.matmul_group([layer.weights[p.name][0] for p in members], x, F16, self.m, outs, F16, strides)
+            elif kind == "fused":
+                gate, up = layer.weights[name]
+                self.ctx.gate_up_silu(gate, up, x, F16, self.m, outs[0], F16, strides[0])
+            else:
+                self.ctx.matmul(layer.weights[name][0], x, F16, self.m, outs[0], F16, strides[0])
 
     def outputs(self, index: int) -> dict[str, np.ndarray]:
         """Host copies of layer `index`'s gathered outputs, for checks."""
@@ -266,15 +284,13 @@ class ShardedLayerStack:
         return result
 
     def ncu_traffic_bytes(self):
-        """DRAM bytes (read + written) per launch of the dominant kernel, from the
-        profiler capture summarised in profiles/gemv_kernel_gate_up_27b_m1.md:
-        100.33 MB read + 3.59 MB written for the whole 27B gate/up pair at M = 1.
-        Traffic is the weight stream, so a rank's slice moves 1/world of it; no
-        capture exists for other shapes or M."""
+        """DRAM bytes (read + written) per launch of the dominant kernel (fused gate/up, 5120 -> 17408, M = 1),
+        from the profiler capture summarised under profiles/; a rank's slice moves 1/world of the weight
+        stream.  None where no capture exists (other shapes, other M)."""
         fused = next(p for p in self.layer_set if p.fused)
-        if (fused.k, fused.n) != (5120, 17408) or self.m != 1:
+        if (fused.k, fused.n) != (5120, 17408) or self.m != 1 or NCU_GATE_UP_TRAFFIC_BYTES is None:
             return None
-        return 103.92e6 / self.world
+        return NCU_GATE_UP_TRAFFIC_BYTES / self.world
 
     def free(self):
         if self.world > 1 and self.gather == "push":
@@ -284,8 +300,11 @@ class ShardedLayerStack:
                 self.ctx.ipc_close(pointer)
             if self.barrier is not None:
                 self.barrier.free()
-        for layer in self.layers:
-            layer.free()
+        if self.comm is not None:
+            self.comm.free()
+        if self.owns_layers:
+            for layer in self.layers:
+                layer.free()
         if self.graph is not None:
             self.graph.free()
         if self.sequence is not None:

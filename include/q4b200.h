@@ -63,6 +63,9 @@ int q4b_copy_to_device(q4b_context *context, void *device_destination, const voi
                        size_t bytes, char *error_message, size_t error_capacity);
 int q4b_copy_to_host(q4b_context *context, void *host_destination, const void *device_source,
                      size_t bytes, char *error_message, size_t error_capacity);
+/* device to device, `rows` rows of `row_bytes` bytes with the given pitches (cudaMemcpy2DAsync on the stream) */
+int q4b_copy_2d(q4b_context *context, void *destination, size_t destination_pitch, const void *source,
+                size_t source_pitch, size_t row_bytes, size_t rows, char *error_message, size_t error_capacity);
 
 /* ---- weight-image loader: replaces mapped_buffer / load_*_layer
  * (qwen38_m3_decode.m:398-407, :500-625).  Takes the two image segments of one
@@ -136,6 +139,27 @@ int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *c
  * aligned; asynchronous.  The kernel is chosen by M: the decode kernel for
  * M <= 16, the tcgen05 GEMM above.
  *
+ * How the decode kernel takes x.  At M <= 4 it multiplies on the integer tensor
+ * pipe: every 64-column group of an activation row becomes two signed 8-bit
+ * digits per value with one power-of-two step for the group (15 bits relative to
+ * the group's largest |x|; fp16 itself carries 11 per value), the sums of
+ * code x digit are exact integers, and scale, step and bias are applied per group
+ * in fp32.  Measured max|y - ref| / max|ref| = 3e-5 .. 8e-5 on fp32 outputs, far
+ * inside 2e-3 (an fp16 output rounds at 5e-4).  At M = 5..16 the codes meet x as
+ * fp16 on the tensor pipe with fp32 accumulation (1e-6 on fp32 outputs).  Either
+ * way a row's result does not depend on M (within the same form) or on the other
+ * rows, nor on timing.  Bit 4 of q4b_context_set_variant (or Q4B_VARIANT) keeps
+ * the fp16 form at M <= 4 too.
+ * fp32 x (the reference's second projections multiply in fp32,
+ * qwen38_m3_layer.m:375-393) is not narrowed to fp16's range: each group is
+ * scaled by the power of two of its largest magnitude before it is cut into
+ * digits (M <= 4) or rounded to fp16 (M = 5..16: 11 bits per value relative to
+ * the value itself), so magnitudes up to 2^100 are served with the same relative
+ * accuracy.  The tensor-core GEMM (M > 16) does round fp32 x to fp16 as it is:
+ * there |x| above 65504 overflows.
+ * A group that holds an infinity or a NaN (or, for fp32 x, a magnitude of 2^100
+ * or more) makes every output of that activation row NaN.
+ *
  * bf16 activations (x_dtype = Q4B_BF16) select the arithmetic of the H3
  * projections (minimax_h3_q4_gemm_bf16_activation, minimax_h3_attention.metal:
  * 512-592; CPU check benchmarks/minimax_h3_m3_real_gemm.c:25-42): every weight
@@ -161,13 +185,20 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
  * cudaMalloc and cudaFree cause) would stall other streams mid-token, or that
  * must give the same latency on the first token as on the thousandth.  This
  * variant runs the same kernel with its scratch in an array that is part of the
- * library image itself: 4 MiB of partial sums plus 4096 arrival counters, held
+ * library image itself: 2 MiB of partial sums plus 4096 arrival counters, held
  * by every GPU that loads the library until the process exits.  It calls no
  * cudaMalloc, cudaFree or other allocating routine.
  *
  * Limits and rules:
- *   - shapes whose split-K scratch exceeds the array are refused with status 1
- *     and a message that states both sizes (all BASELINE shapes fit);
+ *   - only a matrix with fewer 128-row blocks than the GPU runs thread blocks at
+ *     once (296 on a B200, i.e. up to about 37,000 rows) has its K range split and
+ *     uses the scratch at all; larger matrices (the 248,320-row lm_head among
+ *     them) need none and are served as they are.  A split matrix needs at most
+ *     2 KB (M <= 4), 4 KB (M <= 8) or 8 KB (M <= 16) per resident thread block:
+ *     everything up to M = 8 fits on a B200 (at most 1.2 MB); at M = 9..16 a
+ *     matrix cut into more than 256 pieces (17408 -> 5120 is cut into 280) needs
+ *     up to 2.4 MB and is refused with status 1 and a message that states both
+ *     sizes: use q4b_matmul for it;
  *   - no residual input; otherwise the arguments of q4b_matmul;
  *   - the first call on a device looks the array's device address up (once per
  *     device); make that first call before any stream capture begins;
@@ -178,6 +209,22 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
 int q4b_matmul_no_alloc(q4b_context *context, const q4b_weight *weight, const void *x, int x_dtype,
                         uint32_t m_rows, void *y, int y_dtype, uint32_t ldy,
                         char *error_message, size_t error_capacity);
+/* The restricted head of the draft passes (qwen38_m3_decode.m:1847-1866): the first
+ * `draft_vocab` rows of the lm_head as an ordinary matmul, then the listed extra
+ * rows after them.
+ * q4b_weight_rows: a handle on rows [row_begin, row_begin + row_count) of a loaded
+ * weight, without a copy (row_begin a multiple of 128); usable wherever a weight
+ * is, freed with q4b_weight_free before the weight it was taken from.
+ * q4b_matmul_rows replaces qwen38_q4_lm_head_gathered (qwen38_global.metal:68-96):
+ * y[m][slot] = sum_k w(row_ids[slot], k) x[m][k] for `count` row ids in DEVICE
+ * memory, numbered in the whole matrix; 1 <= m_rows <= 16; w = scale * q + bias in
+ * fp32 as there.  The reference writes logits[base + slot]: pass y + base.  Ids of
+ * rows another rank's shard holds leave their slot untouched. */
+int q4b_weight_rows(const q4b_weight *weight, uint32_t row_begin, uint32_t row_count, q4b_weight **rows,
+                    char *error_message, size_t error_capacity);
+int q4b_matmul_rows(q4b_context *context, const q4b_weight *weight, const uint32_t *row_ids, uint32_t count,
+                    const void *x, int x_dtype, uint32_t m_rows, void *y, int y_dtype, uint32_t ldy,
+                    char *error_message, size_t error_capacity);
 /* Up to 4 matrices that share x in one launch, e.g. q/k/v, which the reference
  * fuses into one matrix (qwen38_attention.metal:4-8). */
 int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int count,
@@ -186,17 +233,7 @@ int q4b_matmul_group(q4b_context *context, const q4b_weight *const *weights, int
 /* Fused gate/up with SiLU-gate epilogue: out = silu(gate x) * (up x), replaces
  * qwen38_q4_gate_up_silu (qwen38_q4.metal:129-151, qwen38_m3_decode.m:643-651)
  * and the prefill pair + qwen38_prefill_silu_mul (:1019-1033).
- *
- * At M <= 4 with fp16 x the kernel multiplies on the integer tensor pipe: every
- * 64-column group of an activation row is taken as two signed 8-bit digits per
- * value with one power-of-two step for the group (15 bits relative to the group's
- * largest |x|; fp16 itself carries 11 per value), the sums of code x digit are
- * exact integers, scale, step and bias are applied per group in fp32.  Measured
- * max|y - ref| / max|ref| = 3e-5 .. 8e-5 on fp32 outputs (the fp16 form of the
- * other kernels: 1e-6; both far inside 2e-3, and an fp16 output rounds at 5e-4).
- * A row's result does not depend on M or on the other rows.  Infinite or NaN
- * activations give undefined results in this form.  Bit 4 of
- * q4b_context_set_variant (or Q4B_VARIANT) keeps the fp16 form here too. */
+ * Activations are taken as q4b_matmul takes them (integer form at M <= 4). */
 int q4b_gate_up_silu(q4b_context *context, const q4b_weight *gate, const q4b_weight *up,
                      const void *x, int x_dtype, uint32_t m_rows, void *y, int y_dtype,
                      uint32_t ldy, char *error_message, size_t error_capacity);
@@ -226,11 +263,17 @@ int q4b_sync(q4b_context *context, double *device_ms, char *error_message, size_
  * encode_delta / encode_attention / encode_mlp back to back).  A sequence is the
  * same idea for the Q4 matmuls: jobs are added in execution order, each either a
  * group of 1..4 matrices that share x (q4b_matmul_group) or a fused gate/up pair
- * (q4b_gate_up_silu); job j may read what job j-1 wrote.  All pointers are
- * DEVICE pointers, x is fp16, 1 <= m_rows <= 16.  q4b_sequence_finalize plans
- * the work split and allocates the sequence's own scratch (synchronous, never
- * while recording); q4b_sequence_launch queues one cooperative kernel on the
- * context's stream and may be recorded into a graph.
+ * (q4b_gate_up_silu); job j may read what job j-1 wrote (the kernel treats
+ * every job as depending on the one before it; the next job's weights are
+ * already streaming while it waits).  All pointers are DEVICE pointers,
+ * 1 <= m_rows <= 16; q4b_sequence_add_matmul and _add_gate_up take fp16 x,
+ * q4b_sequence_add_projection one matrix with fp16 or fp32 x and an optional
+ * residual (the second projections, qwen38_layer.metal:193-255).
+ * q4b_sequence_finalize plans the work split and allocates the sequence's own
+ * scratch (synchronous, never while recording); q4b_sequence_launch queues one
+ * cooperative kernel on the context's stream.  The count of launches lives in
+ * device memory and advances when a launch ends, so a launch recorded into a
+ * graph (q4b_graph_begin) replays correctly.
  *
  * Column-parallel ranks (one process per GPU): create with (world, rank), give
  * every job the slice this rank owns, and with q4b_sequence_set_peer_output name
@@ -249,6 +292,9 @@ int q4b_sequence_add_matmul(q4b_sequence *sequence, const q4b_weight *const *wei
 int q4b_sequence_add_gate_up(q4b_sequence *sequence, const q4b_weight *gate, const q4b_weight *up,
                              const void *x, void *y, uint32_t ldy, int y_dtype,
                              char *error_message, size_t error_capacity);
+int q4b_sequence_add_projection(q4b_sequence *sequence, const q4b_weight *weight, const void *x, int x_dtype,
+                                void *y, int y_dtype, uint32_t ldy, const void *residual, int residual_dtype,
+                                uint32_t ld_residual, char *error_message, size_t error_capacity);
 int q4b_sequence_set_peer_output(q4b_sequence *sequence, uint32_t job, uint32_t segment,
                                  uint32_t peer_rank, void *peer_y);
 /* Ranks whose slices differ in size: the number of 64-row blocks (summed over the
@@ -300,6 +346,36 @@ int q4b_ipc_export(q4b_context *context, void *device_pointer, void *handle_64_b
 int q4b_ipc_open(q4b_context *context, const void *handle_64_bytes, void **peer_pointer,
                  char *error_message, size_t error_capacity);
 int q4b_ipc_close(q4b_context *context, void *peer_pointer);
+
+/* ---- NCCL all-gather of the output slices over NVLink (the reference is
+ * single-device and has no collective; this is the plain form of the gather that
+ * the sequences and q4b_context_push_outputs fuse into the producing kernels, kept
+ * as their baseline and cross-check).  One process per GPU: one rank calls
+ * q4b_comm_unique_id and hands the 128 bytes to the others by any means; every
+ * rank then calls q4b_comm_create (collective: returns when all have).  NCCL is
+ * loaded at run time (libnccl.so.2) by the first of these calls; status 3 when
+ * it cannot be.
+ *
+ * q4b_all_gather: ncclAllGather of `bytes_per_rank` bytes on the context's
+ * stream; `gathered` holds world x bytes_per_rank, rank-major; in place when
+ * slice == gathered + rank * bytes_per_rank.  Asynchronous.
+ * q4b_all_gather_columns: this rank's [m_rows][slice_columns] block (dense) into
+ * the whole [m_rows][world * slice_columns] row-major matrix every rank needs
+ * next.  m_rows = 1 is the plain all-gather; above that NCCL's rank-major blocks
+ * land in `staging` (world x m_rows x slice bytes, device) and a copy kernel
+ * interleaves them.  All ranks pass equal slices. */
+typedef struct q4b_comm q4b_comm;
+int q4b_comm_unique_id(void *id_128_bytes, char *error_message, size_t error_capacity);
+int q4b_comm_create(q4b_context *context, uint32_t world, uint32_t rank, const void *id_128_bytes,
+                    q4b_comm **comm, char *error_message, size_t error_capacity);
+uint32_t q4b_comm_world(const q4b_comm *comm);
+uint32_t q4b_comm_rank(const q4b_comm *comm);
+int q4b_all_gather(q4b_context *context, q4b_comm *comm, const void *slice, void *gathered,
+                   size_t bytes_per_rank, char *error_message, size_t error_capacity);
+int q4b_all_gather_columns(q4b_context *context, q4b_comm *comm, const void *slice, void *full,
+                           uint32_t m_rows, uint32_t slice_columns, uint32_t element_bytes, void *staging,
+                           char *error_message, size_t error_capacity);
+void q4b_comm_free(q4b_context *context, q4b_comm *comm);
 
 /* ---- layer-image files: replaces map_file, validate_delta_header,
  * validate_attention_header, load_delta_layer and load_attention_layer
@@ -370,7 +446,13 @@ void q4b_image_close(q4b_image *image);
  * leaves the rest to the other ranks (gather is the caller's; with world = 1 the
  * slice is everything).  Inputs: fp16, except where a dtype is passed (the
  * reference feeds fp32 to the second projections, qwen38_layer.metal:193-255).
- * q4b_layer_encode_mlp runs both halves and therefore needs world = 1. */
+ * q4b_layer_encode_mlp runs both halves and therefore needs world = 1;
+ * q4b_layer_encode_mlp_gathered is the same for world > 1: gate/up on this rank's
+ * rows, q4b_layer_gather of the intermediate, down, gather of the output, all
+ * queued on the context's stream.  q4b_layer_gather completes a full-width
+ * [batch, rows] buffer of which every rank has written its own columns (NCCL
+ * all-gather; equal slices on all ranks; batch > 1 needs `staging`, device
+ * memory of (world + 1) x batch x slice bytes). */
 typedef struct q4b_layer q4b_layer;
 void q4b_layer_slice(uint32_t rows, uint32_t rank, uint32_t world, uint32_t *row_begin, uint32_t *row_count);
 int q4b_layer_load(q4b_context *context, const q4b_image *image, uint32_t rank, uint32_t world,
@@ -396,6 +478,14 @@ int q4b_layer_encode_mlp(q4b_context *context, const q4b_layer *layer, const voi
                          uint32_t batch, void *intermediate, int intermediate_dtype, const void *residual,
                          int residual_dtype, void *layer_output, int output_dtype,
                          char *error_message, size_t error_capacity);
+
+int q4b_layer_gather(q4b_context *context, const q4b_layer *layer, q4b_comm *comm, int matrix, void *full_width,
+                     int dtype, uint32_t batch, void *staging, char *error_message, size_t error_capacity);
+int q4b_layer_encode_mlp_gathered(q4b_context *context, const q4b_layer *layer, q4b_comm *comm,
+                                  const void *post_normalized_f16, uint32_t batch, void *intermediate,
+                                  int intermediate_dtype, const void *residual, int residual_dtype,
+                                  void *layer_output, int output_dtype, void *staging,
+                                  char *error_message, size_t error_capacity);
 
 /* ---- read-bandwidth probe: the role of the reference's device-memory probe
  * (models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-49):

@@ -2,9 +2,10 @@
 
 Outputs: max|y - ref| / max|ref| <= 2e-3 against the oracle's double sum on
 sampled weight rows (the oracle is a scalar loop); the multiplied weights are the
-bit-exact W16 values (gate in test_gpu_parity.py).  At BASELINE's full sizes the
-check is a property: the GEMM must agree with the small-M kernel on sampled
-activation rows.
+bit-exact W16 values (gate in test_gpu_parity.py).  At the full sizes of the 27B
+layer set (M up to 8192) the oracle runs on sampled weight rows x sampled
+activation rows, the edges of the first and last weight block and activation
+block among them.
 """
 import numpy as np
 import pytest
@@ -120,3 +121,57 @@ def test_gemm_grouped_launch(q4b, orc, ctx):
     assert ctx.launches - before == 1
     for n, out, ref in zip(shapes, outs, refs):
         assert_close(out.download(np.float16, (m, n)), ref, f"group member {n}")
+
+
+def sampled(count, rng, picks=24):
+    edges = [0, 1, 63, 64, 127, 128, 255, 256, count - 257, count - 256, count - 129, count - 128, count - 65,
+             count - 64, count - 2, count - 1]
+    return np.unique(np.concatenate([np.array([e for e in edges if 0 <= e < count]), rng.integers(0, count, picks)]))
+
+
+# the 27B layer set at the prefill sizes: every weight block and every activation block is hit by the
+# samples' edges; whole outputs must be finite
+@pytest.mark.parametrize("name,k,n,m", [("q", 5120, 6144, 8192), ("k", 5120, 1024, 512), ("k", 5120, 1024, 8192),
+                                        ("o", 6144, 5120, 8192), ("down", 17408, 5120, 8192)])
+def test_gemm_27b_shapes_on_sampled_rows(q4b, orc, ctx, name, k, n, m):
+    groups = k // 64
+    seed, projection = 31, 2
+    weight = ctx.synth_weight(seed, projection, n, groups)
+    dx = ctx.synth_x(seed, 0, m, k)
+    dy = ctx.alloc(m * n * 2)
+    ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    assert np.isfinite(y.astype(np.float32)).all()
+    rng = np.random.default_rng(m + n)
+    rows, acts = sampled(n, rng), sampled(m, rng, 8)
+    x = dx.download(np.float16, (m, k))[acts]
+    quants, meta = orc.synth_weight_rows(seed, projection, groups, rows)
+    _, ref = orc.matmul(quants, meta, groups, x, want32=False)
+    scale = float(np.max(np.abs(y.astype(np.float32))))
+    error = float(np.max(np.abs(y[np.ix_(acts, rows)].astype(np.float64) - ref))) / scale
+    assert error <= 2e-3, f"{name} M={m}: {error:.3e}"
+    weight.free()
+
+
+@pytest.mark.parametrize("m", [512, 2048, 8192])
+def test_gemm_fused_gate_up_full_width(q4b, orc, ctx, m):
+    k, n = 5120, 17408
+    groups = k // 64
+    seed = 32
+    gate, up = ctx.synth_weight(seed, 4, n, groups), ctx.synth_weight(seed, 5, n, groups)
+    dx = ctx.synth_x(seed, 0, m, k)
+    dy = ctx.alloc(m * n * 2)
+    ctx.gate_up_silu(gate, up, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    assert np.isfinite(y.astype(np.float32)).all()
+    rng = np.random.default_rng(m)
+    rows, acts = sampled(n, rng), sampled(m, rng, 8)
+    x = dx.download(np.float16, (m, k))[acts]
+    gq, gm = orc.synth_weight_rows(seed, 4, groups, rows)
+    uq, um = orc.synth_weight_rows(seed, 5, groups, rows)
+    _, ref = orc.gate_up_silu(gq, gm, uq, um, groups, x, want32=False)
+    scale = float(np.max(np.abs(y.astype(np.float32))))
+    error = float(np.max(np.abs(y[np.ix_(acts, rows)].astype(np.float64) - ref))) / scale
+    assert error <= 2e-3, f"fused gate/up M={m}: {error:.3e}"
+    gate.free()
+    up.free()

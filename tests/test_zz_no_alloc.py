@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 def test_no_alloc_entry_point_matches_matmul_twice_in_a_row(q4b, orc):
     with q4b.Q4Context(0) as ctx:
         # shapes whose K range is split over thread blocks (they use the scratch) and one that is not
-        for seed, (n, k, m) in enumerate([(1024, 5120, 1), (6144, 5120, 4), (5120, 17408, 1), (128, 64, 3)]):
+        for seed, (n, k, m) in enumerate([(1024, 5120, 1), (6144, 5120, 4), (5120, 17408, 1), (128, 64, 3), (1024, 2048, 7)]):
             quants, meta = orc.synth_weight(seed, 0, n, k // 64)
             weight = ctx.upload(quants, meta, n, k // 64)
             x = orc.synth_x(seed, 0, m, k)
@@ -40,13 +40,22 @@ def test_no_alloc_entry_point_matches_matmul_twice_in_a_row(q4b, orc):
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit(q4b, orc):
     with q4b.Q4Context(0) as ctx:
-        # 4096 counters cover 4096 row blocks of 64 rows: 300,000 rows need more
+        # 17408 -> 5120 has 40 blocks of 128 rows, so its K range is cut into 7 parts per block: 280 pieces.
+        # At M = 16 a piece parks 8 KB of sums: 2.3 MB, more than the 2 MiB the library carries.
+        n, k, m = 5120, 17408, 16
+        weight = ctx.synth_weight(0, 0, n, k // 64)
+        dx = ctx.synth_x(0, 0, m, k)
+        dy = ctx.alloc(m * n * 2)
+        with pytest.raises(q4b.Q4Error) as info:
+            ctx.matmul_no_alloc(weight, dx.ptr, q4b.F16, m, dy.ptr)
+        assert info.value.status == 1 and "built-in scratch" in info.value.message
+        ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)  # the allocating entry point takes it
+        ctx.matmul_no_alloc(weight, dx.ptr, q4b.F16, 4, dy.ptr)  # and at M = 4 it fits
+        ctx.sync()
+        # a matrix with more 128-row blocks than resident thread blocks needs no scratch at all
         n, k = 300_000, 64
         weight = ctx.synth_weight(0, 0, n, 1)
         dx = ctx.synth_x(0, 0, 1, k)
         dy = ctx.alloc(n * 2)
-        with pytest.raises(q4b.Q4Error) as info:
-            ctx.matmul_no_alloc(weight, dx.ptr, q4b.F16, 1, dy.ptr)
-        assert info.value.status == 1 and "built-in scratch" in info.value.message
-        ctx.matmul(weight, dx.ptr, q4b.F16, 1, dy.ptr)  # the allocating entry point takes it
+        ctx.matmul_no_alloc(weight, dx.ptr, q4b.F16, 1, dy.ptr)
         ctx.sync()
