@@ -373,7 +373,27 @@ def run_ours(args):
                 "frac_of_8TBs": dominant["gbs"] / 8000.0, "us_per_launch": dominant["us_per_launch"],
                 "traffic": model.ncu_traffic_bytes()}
 
-    extras = {"mode": mode, "ms_per_step_by_mode": modes, "per_projection": per_projection,
+    # ---- where the persistent launch spends its time, as one consumer warp per thread block sees it ----
+    phases = None
+    if model.sequence is not None:
+        model.mode = "sequence"
+        model.sequence.profile()          # clocks on
+        for _ in range(3):
+            model.step()
+        ticks = model.sequence.profile()  # [thread blocks, 6] SM clock ticks of the three launches
+        total = np.maximum(ticks[:, 5].astype(np.float64), 1.0)
+        names = model.sequence.PROFILE_PHASES
+        sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+        phases = {"share_of_launch_median_over_thread_blocks":
+                      {name: float(np.median(ticks[:, i] / total)) for i, name in enumerate(names[:5])},
+                  "us_per_layer_median_over_thread_blocks":
+                      {name: float(np.median(ticks[:, i])) / 3 / LAYERS / sm_mhz for i, name in enumerate(names)},
+                  "note": "SM clock ticks x sampled median SM MHz; dependency = waiting for the previous projection's "
+                          "outputs, entries = activations into tensor-pipe operands, weights = waiting for HBM, "
+                          "tiles = multiplying, finish = split sums, epilogue, publishing"}
+        model.mode = mode
+
+    extras = {"mode": mode, "ms_per_step_by_mode": modes, "per_projection": per_projection, "sequence_phases": phases,
               "whole_step_frac_of_measured_hbm": value / world / peaks["hbm_gbs"],
               "whole_step_frac_of_8TBs": value / world / 8000.0, "us_per_layer": ms_per_step * 1e3 / LAYERS,
               "tflops": layer_flops * LAYERS / (ms_per_step * 1e-3) / 1e12}
@@ -387,6 +407,7 @@ def run_ours(args):
         if world == 1:
             extras["prefill_gemm"] = prefill_gemm(q4b, orc, ctx, model, peaks, parity)
             extras["h3_bf16_gemm"] = h3_bf16_gemm(q4b, ctx, peaks)
+            extras["h3_f16_large_m"] = h3_large_m(q4b, ctx, peaks)
         else:
             extras["prefill_gemm"] = sharded_prefill(q4b, sharded, orc, ctx, rank, world, dist, peaks, barrier,
                                                      max_over_ranks, args.gather, parity)
@@ -554,6 +575,38 @@ def h3_bf16_gemm(q4b, ctx, peaks, blocks=2, m=2048):
     return {"m_rows": m, "ms_per_block": ms, "tflops": tflops, "dtype": "u4*bf16->f32->bf16",
             "frac_of_measured_bf16_burst": tflops / peaks["bf16_tflops"],
             "frac_of_measured_bf16_sustained": tflops / peaks["bf16_tflops_sustained"]}
+
+
+def h3_large_m(q4b, ctx, peaks):
+    """The reference's largest measured affine-Q4 GEMM: 5376 -> 14336, fp16 in and out, M = 15,485 and its
+    4,646-row sample (models/minimax-h3/targets/apple-m3-pro/README.md:722-726: 618.2 ms = 3.861 TFLOP/s and
+    194.6 ms = 3.680 TFLOP/s on an M3 Pro).  Three weight sets in turn; TFLOP/s = 2*M*N*K over device time."""
+    n, k = 14336, 5376
+    weights = [ctx.synth_weight(200 + index, 0, n, k // 64) for index in range(3)]
+    results = []
+    for m in (4646, 15485):
+        x = ctx.synth_x(m, 0, m, k)
+        y = ctx.alloc(m * n * 2)
+
+        def run():
+            for weight in weights:
+                ctx.matmul(weight, x.ptr, q4b.F16, m, y.ptr)
+        run()
+        ctx.sync()
+        reps = 3
+        ctx.timer_start()
+        for _ in range(reps):
+            run()
+        ms = ctx.sync(timed=True) / (reps * len(weights))
+        tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        results.append({"m_rows": m, "ms": ms, "tflops": tflops,
+                        "frac_of_measured_bf16_burst": tflops / peaks["bf16_tflops"],
+                        "reference_m3_pro_ms": 618.205 if m == 15485 else 194.602})
+        x.free()
+        y.free()
+    for weight in weights:
+        weight.free()
+    return results
 
 
 def sharded_prefill(q4b, sharded, orc, ctx, rank, world, dist, peaks, barrier, max_over_ranks, gather, parity,

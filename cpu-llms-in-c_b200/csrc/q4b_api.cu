@@ -57,6 +57,7 @@ struct q4b_sequence {
     uint32_t *peer_done[kMaxPeers];
     float *scratch;
     uint32_t *counters;
+    unsigned long long *profile;  // optional phase clocks, [ctas][kProfileSlots]
     SequenceLaunch launch;
 };
 
@@ -368,8 +369,23 @@ int run_projection(q4b_context *context, ProjectionArgs args, char *error_messag
     const uint32_t total = args.m_rows;
     const size_t K = (size_t)args.w[0].groups * kGroup;
     // variant bit 15 keeps large M on the small-M kernel (row blocks of 16), for A/B runs
-    if (total > limit && !built_in_scratch && ((context->variant >> 15) & 1) == 0) {
+    if (total > limit && !built_in_scratch && ((context->variant >> 15) & 1) == 0 && args.w[0].kind == kQ4) {
         return run_tensor_core(context, args, error_message, error_capacity);
+    }
+    if (args.w[0].kind == kQ8) {
+        // the affine-Q8 sibling exists as a GEMM only (as in the reference): the tensor-core kernel at every M
+        if (built_in_scratch || args.fused_silu || args.segments != 1 || args.x_dtype == kBF16) {
+            set_error(error_message, error_capacity,
+                      "affine-Q8 weights: one matrix per call through q4b_matmul, fp16 or fp32 activations");
+            return Q4B_BAD_ARGUMENT;
+        }
+        return run_tensor_core(context, args, error_message, error_capacity);
+    }
+    for (int s = 0; s < args.segments; ++s) {
+        if (args.w[s].kind != kQ4 || (args.fused_silu && args.up.kind != kQ4)) {
+            set_error(error_message, error_capacity, "affine-Q8 weights cannot share a call with Q4 weights");
+            return Q4B_BAD_ARGUMENT;
+        }
     }
     if (args.x_dtype == kBF16) {
         // the small-M kernel multiplies fp16 or integer digits; bf16 activations go to the tensor-core kernel at every M
@@ -594,6 +610,22 @@ int q4b_weight_upload(q4b_context *context, const void *quants, const void *meta
                          row_count, weight, error_message, error_capacity);
 }
 
+uint64_t q4b_planes_narrowed(const void *scales, const void *biases, int meta_dtype, uint64_t values_per_plane) {
+    if (meta_dtype != Q4B_BF16 || scales == nullptr || biases == nullptr) return 0;  // fp16 planes are taken as they are
+    uint64_t changed = 0;
+    for (int plane = 0; plane < 2; ++plane) {
+        const uint16_t *values = static_cast<const uint16_t *>(plane == 0 ? scales : biases);
+        for (uint64_t i = 0; i < values_per_plane; ++i) {
+            const uint32_t bits = (uint32_t)values[i] << 16;
+            float value;
+            memcpy(&value, &bits, sizeof(value));
+            const float back = __half2float(__float2half_rn(value));
+            if (!(back == value) && value == value) ++changed;  // NaN stays NaN: not counted
+        }
+    }
+    return changed;
+}
+
 int q4b_weight_upload_planes(q4b_context *context, const void *quants, const void *scales,
                              const void *biases, int meta_dtype, uint32_t rows, uint32_t groups_per_row,
                              uint32_t row_begin, uint32_t row_count, q4b_weight **weight,
@@ -604,6 +636,74 @@ int q4b_weight_upload_planes(q4b_context *context, const void *quants, const voi
     }
     return upload_common(context, quants, scales, biases, meta_dtype, rows, groups_per_row, row_begin,
                          row_count, weight, error_message, error_capacity);
+}
+
+int q4b_weight_upload_q8(q4b_context *context, const void *quants, const void *scales_bf16, const void *biases_bf16,
+                         uint32_t rows, uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                         q4b_weight **weight, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (weight == nullptr || quants == nullptr || scales_bf16 == nullptr || biases_bf16 == nullptr) {
+        set_error(error_message, error_capacity, "NULL plane or output pointer");
+        return Q4B_BAD_ARGUMENT;
+    }
+    *weight = nullptr;
+    code = validate_shape(rows, groups_per_row, row_begin, row_count, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (context->capturing) {
+        set_error(error_message, error_capacity, "weights cannot be loaded while recording a graph");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const size_t blocks = (size_t)row_count * groups_per_row;  // (row, group) cells of the slice
+    const size_t quant_bytes = blocks * kGroup, plane_bytes = blocks * 2;
+    const uint64_t stream_bytes = (uint64_t)ceil_div(row_count, kQ8Rows) * groups_per_row * kQ8TileBytes;
+    uint8_t *staging = nullptr, *tiles = nullptr;
+    cudaError_t status = cudaMalloc(&staging, quant_bytes + 2 * plane_bytes + 64);
+    if (status == cudaSuccess) status = cudaMalloc(&tiles, stream_bytes);
+    if (status != cudaSuccess) {
+        cudaFree(staging);
+        set_error(error_message, error_capacity, "cudaMalloc of the Q8 weight image: %s", cudaGetErrorString(status));
+        return Q4B_LOAD_FAILURE;
+    }
+    uint8_t *device_quants = staging;
+    uint8_t *device_scales = staging + ((quant_bytes + 15) & ~(size_t)15);
+    uint8_t *device_biases = device_scales + ((plane_bytes + 15) & ~(size_t)15);
+    const size_t first = (size_t)row_begin * groups_per_row;  // only the slice's bytes cross PCIe
+    status = cudaMemcpyAsync(device_quants, static_cast<const uint8_t *>(quants) + first * kGroup, quant_bytes,
+                             cudaMemcpyHostToDevice, context->stream);
+    if (status == cudaSuccess)
+        status = cudaMemcpyAsync(device_scales, static_cast<const uint8_t *>(scales_bf16) + first * 2, plane_bytes,
+                                 cudaMemcpyHostToDevice, context->stream);
+    if (status == cudaSuccess)
+        status = cudaMemcpyAsync(device_biases, static_cast<const uint8_t *>(biases_bf16) + first * 2, plane_bytes,
+                                 cudaMemcpyHostToDevice, context->stream);
+    if (status == cudaSuccess)
+        status = launch_repack_q8(device_quants, reinterpret_cast<const uint16_t *>(device_scales),
+                                  reinterpret_cast<const uint16_t *>(device_biases), groups_per_row, 0, row_count, tiles,
+                                  context->stream);
+    ++context->launches;
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    cudaFree(staging);
+    if (status != cudaSuccess) {
+        cudaFree(tiles);
+        return device_failure(error_message, error_capacity, "Q8 repack", status);
+    }
+    q4b_weight *result = new (std::nothrow) q4b_weight();
+    if (result == nullptr) {
+        cudaFree(tiles);
+        return Q4B_LOAD_FAILURE;
+    }
+    result->view.tiles = tiles;
+    result->view.rows = row_count;
+    result->view.groups = groups_per_row;
+    result->view.row_tiles = ceil_div(row_count, kTileRows);
+    result->view.kind = kQ8;
+    result->device_bytes = stream_bytes;
+    result->rows_total = rows;
+    result->row_begin = row_begin;
+    result->device = context->device;
+    *weight = result;
+    return Q4B_OK;
 }
 
 int q4b_weight_from_device(q4b_context *context, const void *device_quants, const void *device_meta,
@@ -686,7 +786,7 @@ void q4b_weight_free(q4b_context *context, q4b_weight *weight) {
 
 int q4b_weight_rows(const q4b_weight *weight, uint32_t row_begin, uint32_t row_count, q4b_weight **rows,
                     char *error_message, size_t error_capacity) {
-    if (weight == nullptr || rows == nullptr || row_count == 0 || row_begin % 128 != 0 ||
+    if (weight == nullptr || rows == nullptr || row_count == 0 || row_begin % 128 != 0 || weight->view.kind != kQ4 ||
         row_begin >= weight->view.rows || row_count > weight->view.rows - row_begin) {
         set_error(error_message, error_capacity,
                   "a row range starts at a multiple of 128 rows and lies inside the weight");
@@ -710,7 +810,7 @@ int q4b_matmul_rows(q4b_context *context, const q4b_weight *weight, const uint32
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
     if (weight == nullptr || row_ids == nullptr || x == nullptr || y == nullptr || weight->device != context->device ||
-        m_rows == 0 || m_rows > 16 || ldy < count || !valid_activation_dtype(x_dtype) ||
+        weight->view.kind != kQ4 || m_rows == 0 || m_rows > 16 || ldy < count || !valid_activation_dtype(x_dtype) ||
         !valid_activation_dtype(y_dtype) || !aligned16(x)) {
         set_error(error_message, error_capacity,
                   "weight, row list, x or y missing; 1..16 activation rows, fp16 or fp32, ldy >= count, x 16-byte aligned");
@@ -822,7 +922,7 @@ int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, cons
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
     if (embedding == nullptr || rows == nullptr || out == nullptr || !valid_activation_dtype(out_dtype) ||
-        embedding->device != context->device || !aligned16(out)) {
+        embedding->device != context->device || !aligned16(out) || embedding->view.kind != kQ4) {
         set_error(error_message, error_capacity, "embedding, row list or output missing, or not fp16/fp32 16-byte aligned");
         return Q4B_BAD_ARGUMENT;
     }
@@ -867,7 +967,9 @@ int q4b_weight_unpack(q4b_context *context, const q4b_weight *weight, uint8_t *c
     if (status == cudaSuccess && w32 != nullptr) status = cudaMalloc(&device_w32, elements * 4);
     if (status == cudaSuccess && w16 != nullptr) status = cudaMalloc(&device_w16, elements * 2);
     if (status == cudaSuccess) {
-        status = launch_unpack(weight->view, device_codes, device_w32, device_w16, context->stream);
+        status = weight->view.kind == kQ8
+                     ? launch_unpack_q8(weight->view, device_codes, device_w32, device_w16, context->stream)
+                     : launch_unpack(weight->view, device_codes, device_w32, device_w16, context->stream);
         ++context->launches;
     }
     if (status == cudaSuccess && codes != nullptr)
@@ -1122,8 +1224,10 @@ static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights
     DecodeJob job = {};
     for (int s = 0; s < count; ++s) {
         if (weights[s] == nullptr || y[s] == nullptr || weights[s]->device != sequence->device ||
-            weights[s]->view.groups != weights[0]->view.groups || ldy[s] < weights[s]->view.rows) {
-            set_error(error_message, error_capacity, "matrices of a job must live on the context's device, share K and fit ldy");
+            weights[s]->view.groups != weights[0]->view.groups || ldy[s] < weights[s]->view.rows ||
+            weights[s]->view.kind != kQ4) {
+            set_error(error_message, error_capacity,
+                      "matrices of a job must be Q4, live on the context's device, share K and fit ldy");
             return Q4B_BAD_ARGUMENT;
         }
         job.tiles[s] = weights[s]->view.tiles;
@@ -1132,8 +1236,9 @@ static int sequence_add(q4b_sequence *sequence, const q4b_weight *const *weights
         job.y[s][sequence->rank] = y[s];
     }
     if (up != nullptr) {
-        if (count != 1 || up->view.rows != weights[0]->view.rows || up->view.groups != weights[0]->view.groups) {
-            set_error(error_message, error_capacity, "gate and up must have the same shape");
+        if (count != 1 || up->view.rows != weights[0]->view.rows || up->view.groups != weights[0]->view.groups ||
+            up->view.kind != kQ4) {
+            set_error(error_message, error_capacity, "gate and up must be Q4 matrices of the same shape");
             return Q4B_BAD_ARGUMENT;
         }
         job.up_tiles = up->view.tiles;
@@ -1278,12 +1383,43 @@ int q4b_sequence_launch(q4b_context *context, q4b_sequence *sequence, char *erro
     return Q4B_OK;
 }
 
+int q4b_sequence_profile(q4b_context *context, q4b_sequence *sequence, uint64_t *clocks, uint32_t capacity,
+                         uint32_t *thread_blocks, char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (sequence == nullptr || !sequence->finalized || context->capturing) {
+        set_error(error_message, error_capacity, "the sequence is not finalized, or a graph is being recorded");
+        return Q4B_BAD_ARGUMENT;
+    }
+    const uint32_t ctas = sequence->launch.geometry.ctas;
+    const size_t bytes = (size_t)ctas * kProfileSlots * sizeof(unsigned long long);
+    if (thread_blocks != nullptr) *thread_blocks = ctas;
+    Q4B_CUDA(cudaStreamSynchronize(context->stream), "stream synchronize");
+    if (sequence->profile == nullptr) {  // first call: switch the clocks on
+        Q4B_CUDA(cudaMalloc(&sequence->profile, bytes), "cudaMalloc of the profile");
+        Q4B_CUDA(cudaMemset(sequence->profile, 0, bytes), "profile reset");
+        sequence->launch.profile = sequence->profile;
+        return Q4B_OK;
+    }
+    if (clocks != nullptr) {
+        if (capacity < ctas * kProfileSlots) {
+            set_error(error_message, error_capacity, "the buffer holds %u values, the profile has %u", capacity,
+                      ctas * kProfileSlots);
+            return Q4B_BAD_ARGUMENT;
+        }
+        Q4B_CUDA(cudaMemcpy(clocks, sequence->profile, bytes, cudaMemcpyDeviceToHost), "profile read");
+    }
+    Q4B_CUDA(cudaMemset(sequence->profile, 0, bytes), "profile reset");
+    return Q4B_OK;
+}
+
 void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence) {
     if (sequence == nullptr) return;
     if (context != nullptr) {
         cudaSetDevice(context->device);
         cudaStreamSynchronize(context->stream);
     }
+    cudaFree(sequence->profile);
     cudaFree(sequence->device_jobs);
     cudaFree(sequence->done);
     cudaFree(sequence->scratch);

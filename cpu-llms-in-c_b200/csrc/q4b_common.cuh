@@ -52,12 +52,29 @@ constexpr int kUnitBytes = kBlockTiles * kTileBytes;  // one block x one group: 
 
 enum DType : int { kF16 = 0, kF32 = 1, kBF16 = 2, kNone = -1 };
 
+enum WeightKind : uint32_t { kQ4 = 0, kQ8 = 1 };
+
 struct WeightView {
     const uint8_t *tiles;  // tile stream
     uint32_t rows;         // logical rows held (N of this shard)
     uint32_t groups;       // G = K / 64
     uint32_t row_tiles;    // ceil(rows / 16)
+    uint32_t kind;         // kQ4: the 576-byte tiles above; kQ8: the affine-Q8 stream below
 };
+
+// Affine Q8 (minimax_h3_q8_gemm_bf16_meta, minimax_h3_attention.metal:594-676): one code BYTE per weight,
+// 64 per group, bf16 scale and bias per (row, group), w = half(float(scale) * q + float(bias)).  Stream of
+// 8704-byte tiles of 128 rows x one group, ordered [128-row block][group]:
+//   [0, 8192)     row r's 64 code bytes as four 16-byte pieces, piece p (columns 16 p .. 16 p + 15) at index
+//                 4 r + ((p + r / 2) & 3): a warp whose lanes read piece p of 32 consecutive rows then touches
+//                 every bank group four times, the minimum for 512 bytes
+//   [8192, 8704)  128 records {bf16 scale, bf16 bias}, kept as bf16
+constexpr int kQ8Rows = 128;
+constexpr int kQ8CodeBytes = kQ8Rows * kGroup;          // 8192
+constexpr int kQ8TileBytes = kQ8CodeBytes + kQ8Rows * 4;  // 8704
+__host__ __device__ inline uint32_t q8_piece_index(uint32_t row, uint32_t piece) {
+    return 4u * row + ((piece + (row >> 1)) & 3u);
+}
 
 __host__ __device__ inline uint32_t ceil_div(uint32_t a, uint32_t b) {
     return (a + b - 1) / b;

@@ -13,7 +13,7 @@
 // HBM bound: every weight byte is read once.  Work is cut into units: one "pair
 // block" (128 output rows = two 64-row blocks of the tile stream, or 64 gate rows
 // and the same 64 up rows when fused) times one contiguous range of K groups.  A
-// CTA has three kinds of warps:
+// CTA has two kinds of warps:
 //
 //   * warp 8, the weight producer: one thread streams the CTA's units -- job after
 //     job in a sequence, never draining -- through a shared-memory ring with bulk
@@ -22,29 +22,31 @@
 //     the consumers across job boundaries and kernel boundaries (programmatic
 //     dependent launch): the wait for the previous projection's output is hidden
 //     behind loads that are needed anyway.
-//   * warp 9, the activation loader: turns x, group by group, into the B operands
-//     the consumers feed to the tensor pipe and parks them in a small ring of its
-//     own.  For M <= 4 that is the integer form: two signed 8-bit digits per value
-//     with one power-of-two step per (group, activation row), 15 bits relative to
-//     the group's largest value (fp16 itself carries 11 per value), so the codes go
-//     to the tensor pipe as bytes (mma.sync m16n8k32 u8 x s8, exact s32 sums).  For
-//     M = 5..16 it is the fp16 form (codes as fp16 subnormal bit patterns,
-//     m16n8k16, fp32 accumulate).  fp32 activations are scaled per group by a power
-//     of two first, so their magnitude does not matter.  In a sequence this warp
-//     is also the one that waits for the previous job's outputs.
-//   * warps 0..7, the consumers: warp w owns ONE 16-row tile of the pair block
-//     (tile w & 3 of block w >> 2) and walks the unit's groups with it, so a row's
-//     sum lives in one lane from the first group to the last: no reduction inside
-//     the CTA, no barrier between units.  Per group: y += (s * step) * (q . x')
-//     + b * sum(x) in fp32, the reference's arithmetic re-associated per group.
+//   * warps 0..7, the consumers.  Warp w owns ONE 16-row tile of the pair block
+//     (tile w & 3 of block w >> 2) and multiplies it with every group of the
+//     unit, so a row's sum lives in one lane from the first group to the last: no
+//     reduction inside the CTA, no barrier among the consumers.  Per group:
+//     y += (s * step) * (q . x') + b * sum(x) in fp32, the reference's arithmetic
+//     re-associated per group.  The activations reach the tensor pipe as "entries"
+//     in shared memory, eight per ring stage, which the same warps make in turn,
+//     two stages ahead of their use (three sets, mbarrier hand-over).  For M <= 4
+//     an entry is the integer form: two signed 8-bit digits per value with one
+//     power-of-two step per (group, activation row), 15 bits relative to the
+//     group's largest value (fp16 itself carries 11 per value), so the codes go
+//     to the tensor pipe as bytes (mma.sync m16n8k32 u8 x s8, exact s32 sums); one
+//     pass of a warp serves four groups at M = 1, two at M = 2.  For M = 5..16 it
+//     is the fp16 form (codes as fp16 subnormal bit patterns, m16n8k16, fp32
+//     accumulate).  fp32 activations are scaled per group by a power of two
+//     first, so their magnitude does not matter.  In a sequence the consumers are
+//     also the ones that wait for the previous job's outputs.
 //
 // Units that share a pair block (K split over CTAs when a job has fewer pair
 // blocks than the grid has CTAs) park their sums in global slots; the last warp
 // to arrive for a tile adds the slots in part order -- results do not depend on
 // timing -- applies the epilogue (SiLU gate, residual) and stores y, on every
 // rank's copy when the ranks of a column-parallel job share outputs.  In a
-// sequence it then advances the job's completion counters; the loaders of the next
-// job start when every tile of every rank has been counted.
+// sequence it then advances the job's completion counters; the next job's
+// consumers start when every tile of every rank has been counted.
 //
 // Every wait is bounded.  The first wait that expires sets a CTA-wide flag and a
 // code in the status word; from then on no wait in that CTA waits, every role
@@ -59,36 +61,45 @@ namespace q4b {
 namespace {
 
 constexpr int kConsumers = 8;                 // consumer warps
-constexpr int kProducerWarp = 8, kLoaderWarp = 9;  // loader warps: 9 and 10, one per slot of the activation ring
-constexpr int kLoaders = 2;
-constexpr int kDecodeThreads = 32 * (kConsumers + 1 + kLoaders);
+constexpr int kProducerWarp = 8;
+constexpr int kDecodeThreads = 32 * (kConsumers + 1);
 constexpr uint32_t kStageGroups = 8;          // groups per ring stage, both blocks of the pair
 constexpr uint32_t kStageBytes = 2 * kStageGroups * kUnitBytes;  // 36,864
-constexpr uint32_t kChunkGroups = 4;          // groups per hand-over of activations
-constexpr uint32_t kChunks = 2;
+constexpr uint32_t kEntrySets = 3;            // sets of eight entries: they are made two stages ahead of their use
+constexpr uint32_t kMaxSharedBytes = 115712;  // what lets two CTAs share an SM (228 KB less 1 KB per CTA)
 constexpr long long kWaitLimitCycles = 4000000000ll;  // every wait gives up after ~2 s of SM clocks
+// phases of a consumer's time (see SequenceLaunch::profile): waiting for the previous job's outputs, making and
+// waiting for activation entries, waiting for weights, multiplying, finishing units; the whole launch
+enum ProfileSlot { kProfileDependency = 0, kProfileEntries, kProfileWeights, kProfileTiles, kProfileFinish, kProfileTotal };
 
 // MODE 0: integer form, M <= 4.  MODE 1 / 2: fp16 form, M <= 8 / M <= 16.
+// An "entry" is what one group's activations take in shared memory once they are B operands.
 template <int MODE> struct Form;
 template <> struct Form<0> {
-    static constexpr int NT = 1, VALS = 2, STAGES = 3;
-    static constexpr uint32_t XGROUP = 544;   // 512 B of digit fragments + 4 x {step, sum}
+    static constexpr int NT = 1, VALS = 2, SUM_UNROLL = 8;
     static constexpr uint32_t XCHG_VALS = 1;  // values per lane handed from an up warp to its gate warp at a time
+    // per activation row: 128 B of digit fragments (lanes 0 .. 8 M - 1), then {step, sum} per row; entries
+    // are read with 16-byte loads, so their size is a multiple of 16
+    __host__ __device__ static constexpr uint32_t entry_bytes(uint32_t m_rows) { return (136 * m_rows + 15) / 16 * 16; }
 };
 template <> struct Form<1> {
-    static constexpr int NT = 1, VALS = 4, STAGES = 2;
-    static constexpr uint32_t XGROUP = 1088;  // 1024 B of fp16 fragments + 8 x {step, sum}
+    static constexpr int NT = 1, VALS = 4, SUM_UNROLL = 4;
     static constexpr uint32_t XCHG_VALS = 4;
+    __host__ __device__ static constexpr uint32_t entry_bytes(uint32_t) { return 1088; }  // 1024 B of fp16 fragments + 8 x {step, sum}
 };
 template <> struct Form<2> {
-    static constexpr int NT = 2, VALS = 8, STAGES = 2;
-    static constexpr uint32_t XGROUP = 2176;
+    static constexpr int NT = 2, VALS = 8, SUM_UNROLL = 2;
     static constexpr uint32_t XCHG_VALS = 8;
+    __host__ __device__ static constexpr uint32_t entry_bytes(uint32_t) { return 2176; }
 };
 
-template <int MODE> constexpr uint32_t smem_bytes_of() {
-    return 128 + Form<MODE>::STAGES * kStageBytes + kChunks * kChunkGroups * Form<MODE>::XGROUP +
-           4 * 32 * Form<MODE>::XCHG_VALS * 4;
+// shared memory of a CTA: barriers and flags, the weight ring, three sets of eight entries, the exchange buffer
+// of fused gate/up.  Three ring stages when two CTAs then still share an SM, else two.
+template <int MODE> uint32_t smem_bytes_of(uint32_t m_rows, uint32_t *stages) {
+    const uint32_t fixed = 128 + kEntrySets * kStageGroups * Form<MODE>::entry_bytes(m_rows) +
+                           4 * 32 * Form<MODE>::XCHG_VALS * 4 + 64;  // the last 64: the optional phase clocks
+    *stages = fixed + 3 * kStageBytes <= kMaxSharedBytes ? 3u : 2u;
+    return fixed + *stages * kStageBytes;
 }
 
 struct PassParams {
@@ -97,6 +108,7 @@ struct PassParams {
     uint32_t job_count;
     uint32_t m_rows;
     uint32_t world;
+    uint32_t stages;                 // ring stages (2 or 3)
     uint32_t *epoch;                 // sequence: launches completed so far (device word)
     uint32_t *exit_count;            // sequence: CTAs of this launch that have finished
     uint32_t *done;                  // sequence: [job][8] completion counters, kDoneStride words apart
@@ -104,6 +116,7 @@ struct PassParams {
     float *scratch;
     uint32_t *counters;
     uint32_t *status;
+    unsigned long long *profile;     // optional: [CTA][kProfileSlots] SM clocks by phase, added up by consumer warp 0
 };
 
 // ---------------------------------------------------------------------------
@@ -207,49 +220,8 @@ __device__ inline Unit unit_of(const DecodeJob &job, uint32_t index) {
 }
 
 // ---------------------------------------------------------------------------
-// the activation loaders' work (all 32 lanes of a loader warp)
+// activations of one group -> B operands in shared memory (all 32 lanes of one consumer warp)
 // ---------------------------------------------------------------------------
-// Where a loader stands in the CTA's work: job, unit, first group of the next chunk, chunks so far.
-struct Cursor {
-    uint32_t j, index, g, xi;
-    Unit u;
-    bool have_unit, valid;
-};
-
-template <bool SEQ>
-__device__ inline void cursor_settle(Cursor &c, const PassParams &p, uint32_t job_count, uint32_t cta, uint32_t ctas) {
-    for (;;) {
-        if (c.j >= job_count) {
-            c.valid = false;
-            return;
-        }
-        const DecodeJob &job = SEQ ? p.jobs[c.j] : p.job;
-        if (c.index < job.units) {
-            if (!c.have_unit) {
-                c.u = unit_of(job, c.index);
-                c.g = c.u.g0;
-                c.have_unit = true;
-            }
-            if (c.g < c.u.g1) {
-                c.valid = true;
-                return;
-            }
-            c.index += ctas;
-            c.have_unit = false;
-        } else {
-            ++c.j;
-            c.index = cta;
-            c.have_unit = false;
-        }
-    }
-}
-template <bool SEQ>
-__device__ inline void cursor_advance(Cursor &c, const PassParams &p, uint32_t job_count, uint32_t cta, uint32_t ctas) {
-    c.g += kChunkGroups;
-    ++c.xi;
-    cursor_settle<SEQ>(c, p, job_count, cta, ctas);
-}
-
 // 16 consecutive fp16 activations of this lane in one group (8 registers), zeros when not `live`
 __device__ inline void fetch_x16(const void *x, size_t element, bool live, uint32_t raw[8]) {
     uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
@@ -271,11 +243,12 @@ __device__ inline void fetch_x32(const void *x, size_t element, bool live, float
 }
 
 // Integer form.  Lane (gid, t): activation row m = gid >> 1, digit gid & 1 (0 high, 1 low), the 16 columns
-// 16 t .. 16 t + 15 of the group -- the columns this lane's code words cover in a tile.  A slot receives:
-//   [lane * 16, +16)  the four B registers of the two m16n8k32 MMAs of a tile (column n = 2 m + digit),
-//                     bytes of register i in the order of the code bytes of word i: columns 4i, 4i+2, 4i+1, 4i+3
-//   [512 + 8 m, +8)   {step, sum}: one unit of the low digit as a float, and the sum of the group's 64 values
-//                     as the digits represent them (exact)
+// 16 t .. 16 t + 15 of the group -- the columns this lane's code words cover in a tile.  An entry receives:
+//   [lane * 16, +16)    for lanes 0 .. 8 M - 1: the four B registers of the two m16n8k32 MMAs of a tile
+//                       (column n = 2 m + digit), bytes of register i in the order of the code bytes of word i:
+//                       columns 4i, 4i+2, 4i+1, 4i+3; the other lanes' registers are zero and are not stored
+//   [128 M + 8 m, +8)   {step, sum}: one unit of the low digit as a float, and the sum of the group's 64 values
+//                       as the digits represent them (exact)
 // A group whose largest magnitude is infinite, NaN (or, for fp32 input, 2^100 or more) gets step = NaN, so
 // that every output row of that activation row comes out NaN as the reference's arithmetic would have it.
 //
@@ -344,79 +317,82 @@ __device__ inline void digits_of_f32(const float v[16], bool low_digit, uint32_t
         b[i] = word;
     }
 }
-__device__ inline void store_digits(const uint32_t b[4], float step_here, uint8_t *slot, int lane, bool live) {
+// One pass of a warp makes the entries of P = 4 >> shift consecutive groups, shift = 0, 1, 2 for M = 1, 2, 3..4:
+// the eight (activation row, digit) columns of the B operand are four "slots" of two digits, and with fewer than
+// four activation rows the spare slots take the same rows of the following groups.  Lane (gid, t): slot gid >> 1
+// = (group q = slot >> shift of the pass, activation row m = slot & (2^shift - 1)), digit gid & 1.
+struct Pass {
+    uint32_t q, m;      // this lane's group of the pass and activation row
+    bool live;          // that group and row exist
+};
+__device__ inline Pass pass_of(int lane, uint32_t shift, uint32_t count, uint32_t m_rows) {
+    const uint32_t slot = (uint32_t)lane >> 3;
+    Pass pass;
+    pass.q = slot >> shift;
+    pass.m = slot & ((1u << shift) - 1u);
+    pass.live = pass.q < count && pass.m < m_rows;
+    return pass;
+}
+// digits in hand (b, step_here): the sums of the pass's groups on the tensor pipe, then everything to the entries
+__device__ inline void pass_store(const uint32_t b[4], float step_here, const Pass &pass, uint32_t shift, uint32_t count,
+                                  uint32_t m_rows, uint8_t *first_entry, uint32_t entry_bytes, int lane) {
     const int gid = lane >> 2, t = lane & 3;
-    // as the owner of accumulator column pair t this lane reports activation row t: its step sits in lane 8 t
+    // accumulator column pair t belongs to slot t, whose step sits in lane 8 t
     const float step = __shfl_sync(0xffffffffu, step_here, 8 * t);
-    // the group's sum of x, exact: a row of ones against the digits
+    // the sum of a group's 64 values, exact: a row of ones against the digits
     const uint32_t ones[4] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
     int s[4];
     mma_16832_u8s8(s, ones, b[0], b[1], true);
     mma_16832_u8s8(s, ones, b[2], b[3], false);
-    if (live) {
-        *reinterpret_cast<uint4 *>(slot + lane * 16) = make_uint4(b[0], b[1], b[2], b[3]);
-        if (gid == 0) {
-            const float sum = step * (float)(s[0] * 256 + s[1]);
-            *reinterpret_cast<float2 *>(slot + 512 + t * 8) = make_float2(step, sum);
-        }
+    if (pass.live) {
+        *reinterpret_cast<uint4 *>(first_entry + pass.q * entry_bytes + (pass.m * 8 + (gid & 1) * 4 + t) * 16) =
+            make_uint4(b[0], b[1], b[2], b[3]);
+    }
+    const uint32_t q = (uint32_t)t >> shift, m = (uint32_t)t & ((1u << shift) - 1u);
+    if (gid == 0 && q < count && m < m_rows) {
+        const float sum = step * (float)(s[0] * 256 + s[1]);
+        *reinterpret_cast<float2 *>(first_entry + q * entry_bytes + 128 * m_rows + m * 8) = make_float2(step, sum);
     }
 }
-
-// One chunk of the integer form from registers fetched earlier (fp16 x): the four groups advance together,
-// stage by stage, so that their dependency chains overlap.
-__device__ inline void digitize_chunk_f16(const uint32_t raw[kChunkGroups][8], uint32_t count, uint8_t *chunk,
-                                          int lane) {
+// the whole pass for groups [group, group + count): fp16 x from `raw` (fetched earlier by pass_fetch), fp32 x from memory
+__device__ inline void pass_fetch(const DecodeJob &job, size_t K, uint32_t group, const Pass &pass, int lane,
+                                  uint32_t raw[8]) {
+    fetch_x16(job.x, (size_t)pass.m * K + (size_t)(group + pass.q) * kGroup + 16 * (lane & 3), pass.live, raw);
+}
+__device__ inline void pass_finish(const DecodeJob &job, size_t K, uint32_t group, const Pass &pass, uint32_t shift,
+                                   uint32_t count, uint32_t m_rows, const uint32_t raw[8], uint8_t *first_entry,
+                                   uint32_t entry_bytes, int lane) {
     const bool low_digit = ((lane >> 2) & 1) != 0;
-    uint32_t b[kChunkGroups][4];
-    float step[kChunkGroups];
-#pragma unroll
-    for (uint32_t q = 0; q < kChunkGroups; ++q) digits_of_f16(raw[q], low_digit, b[q], step[q]);
-#pragma unroll
-    for (uint32_t q = 0; q < kChunkGroups; ++q) store_digits(b[q], step[q], chunk + q * Form<0>::XGROUP, lane, q < count);
-}
-// the same from fp32 x, loads included (no prefetch: twice the registers)
-__device__ inline void digitize_chunk_f32(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t g, uint32_t count,
-                                          uint8_t *chunk, int lane) {
-    const int gid = lane >> 2, t = lane & 3;
-    const uint32_t m = (uint32_t)gid >> 1;
-    const bool low_digit = (gid & 1) != 0;
-#pragma unroll
-    for (uint32_t half = 0; half < kChunkGroups; half += 2) {
-        float v[2][16];
-        uint32_t b[2][4];
-        float step[2];
-#pragma unroll
-        for (uint32_t q = 0; q < 2; ++q) {
-            fetch_x32(job.x, (size_t)m * K + (size_t)(g + half + q) * kGroup + 16 * t, m < m_rows && half + q < count, v[q]);
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < 2; ++q) digits_of_f32(v[q], low_digit, b[q], step[q]);
-#pragma unroll
-        for (uint32_t q = 0; q < 2; ++q) {
-            store_digits(b[q], step[q], chunk + (half + q) * Form<0>::XGROUP, lane, half + q < count);
-        }
+    uint32_t b[4];
+    float step_here;
+    if (job.x_dtype == kF32) {
+        float v[16];
+        fetch_x32(job.x, (size_t)pass.m * K + (size_t)(group + pass.q) * kGroup + 16 * (lane & 3), pass.live, v);
+        digits_of_f32(v, low_digit, b, step_here);
+    } else {
+        digits_of_f16(raw, low_digit, b, step_here);
     }
+    pass_store(b, step_here, pass, shift, count, m_rows, first_entry, entry_bytes, lane);
 }
 
-// fp16 form.  Lane (gid, t), column tile n: activation row m = 8 n + gid, columns 16 t .. 16 t + 15.  A slot gets:
+// fp16 form.  Lane (gid, t), column tile n: activation row m = 8 n + gid, columns 16 t .. 16 t + 15.  An entry gets:
 //   [n * 1024 + lane * 32, +32)           the eight B registers of the four m16n8k16 MMAs of a tile
 //   [NT * 1024 + 8 (8 n + m'), +8)        {step, step * sum} of activation row 8 n + m'
 // fp16 input passes through unchanged (step = 1); fp32 input is scaled by the power of two that brings the
 // group's largest magnitude into [1, 2) and then rounded to fp16, the power going into step.
+// `held` (fp16 input only): the registers fetched a stage ahead, [n][8].
 template <int NT>
-__device__ inline void load_group_f16(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t group, uint8_t *slot,
-                                      int lane, bool live) {
+__device__ inline void entry_f16(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t group, const uint32_t *held,
+                                 uint8_t *entry, int lane) {
     const int gid = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
         const uint32_t m = n * 8 + gid;
-        const bool valid = live && m < m_rows;
-        const size_t element = (size_t)m * K + (size_t)group * kGroup + 16 * t;
         uint32_t raw[8];
         float step_here = 1.0f;
         if (job.x_dtype == kF32) {
             float v[16];
-            fetch_x32(job.x, element, valid, v);
+            fetch_x32(job.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, v);
             uint32_t big = 0;
 #pragma unroll
             for (int i = 0; i < 16; ++i) big = max(big, __float_as_uint(v[i]) & 0x7fffffffu);
@@ -434,7 +410,8 @@ __device__ inline void load_group_f16(const DecodeJob &job, uint32_t m_rows, siz
                 raw[i] = *reinterpret_cast<const uint32_t *>(&pair);
             }
         } else {
-            fetch_x16(job.x, element, valid, raw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) raw[i] = held[n * 8 + i];
         }
         // group sums of x on the tensor pipe: a fragment of ones times the same B
         const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
@@ -444,15 +421,25 @@ __device__ inline void load_group_f16(const DecodeJob &job, uint32_t m_rows, siz
         // accumulator columns 2t, 2t+1 are activation rows 8n + 2t, 8n + 2t + 1: their steps sit in lanes 8t, 8t + 4
         const float step0 = __shfl_sync(0xffffffffu, step_here, 8 * t);
         const float step1 = __shfl_sync(0xffffffffu, step_here, 8 * t + 4);
-        if (live) {
-            uint4 *out = reinterpret_cast<uint4 *>(slot + n * 1024 + lane * 32);
-            out[0] = make_uint4(raw[0], raw[1], raw[2], raw[3]);
-            out[1] = make_uint4(raw[4], raw[5], raw[6], raw[7]);
-            if (gid == 0) {
-                *reinterpret_cast<float4 *>(slot + NT * 1024 + (n * 8 + 2 * t) * 8) =
-                    make_float4(step0, step0 * total[0], step1, step1 * total[1]);
-            }
+        uint4 *out = reinterpret_cast<uint4 *>(entry + n * 1024 + lane * 32);
+        out[0] = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+        out[1] = make_uint4(raw[4], raw[5], raw[6], raw[7]);
+        if (gid == 0) {
+            *reinterpret_cast<float4 *>(entry + NT * 1024 + (n * 8 + 2 * t) * 8) =
+                make_float4(step0, step0 * total[0], step1, step1 * total[1]);
         }
+    }
+}
+
+// fp16 form: this lane's fp16 activations of one group into `held` [NT][8] (rows 8 n + gid)
+template <int NT>
+__device__ inline void fetch_held(const DecodeJob &job, uint32_t m_rows, size_t K, uint32_t group, int lane,
+                                  uint32_t *held) {
+    const int gid = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        const uint32_t m = n * 8 + gid;
+        fetch_x16(job.x, (size_t)m * K + (size_t)group * kGroup + 16 * t, m < m_rows, held + n * 8);
     }
 }
 
@@ -460,26 +447,31 @@ __device__ inline void load_group_f16(const DecodeJob &job, uint32_t m_rows, siz
 // a consumer warp's work on one tile of one group
 // ---------------------------------------------------------------------------
 // Integer form: lane (gid, t) accumulates rows gid (acc[0]) and gid + 8 (acc[1]) of activation row t.
-__device__ inline void tile_digits(const uint8_t *tile, const uint8_t *slot, int lane, float acc[2]) {
+__device__ inline void tile_digits(const uint8_t *tile, const uint8_t *entry, uint32_t m_rows, int lane, float acc[2]) {
     const int gid = lane >> 2, t = lane & 3;
     const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
     const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
-    const uint4 b = *reinterpret_cast<const uint4 *>(slot + lane * 16);
-    const float2 ss = *reinterpret_cast<const float2 *>(slot + 512 + t * 8);
-    // even nibbles: row gid, odd nibbles: row gid + 8; word i covers columns 4i .. 4i+3 of this lane's 16
-    const uint32_t a0[4] = {codes.x & 0x0F0F0F0Fu, (codes.x >> 4) & 0x0F0F0F0Fu,
-                            codes.y & 0x0F0F0F0Fu, (codes.y >> 4) & 0x0F0F0F0Fu};
-    const uint32_t a1[4] = {codes.z & 0x0F0F0F0Fu, (codes.z >> 4) & 0x0F0F0F0Fu,
-                            codes.w & 0x0F0F0F0Fu, (codes.w >> 4) & 0x0F0F0F0Fu};
+    uint4 b = make_uint4(0u, 0u, 0u, 0u);
+    if ((uint32_t)lane < 8 * m_rows) b = *reinterpret_cast<const uint4 *>(entry + lane * 16);
+    float2 ss = make_float2(0.0f, 0.0f);
+    if ((uint32_t)t < m_rows) ss = *reinterpret_cast<const float2 *>(entry + 128 * m_rows + t * 8);
+    // Word i covers columns 4i .. 4i+3 of this lane's 16; its even nibbles are row gid, its odd nibbles row gid + 8.
+    // Row gid gets the masked nibbles.  Row gid + 8 gets the RAW bytes, 16 * (its code) + (row gid's code): its
+    // integer sum is then 16 * (the wanted sum) + (row gid's sum), and one subtraction after the MMAs replaces
+    // eight shift-and-mask instructions before them (bytes up to 255 times digits up to 128 over 64 columns stay
+    // far inside 32 bits).
+    const uint32_t a0[4] = {codes.x & 0x0F0F0F0Fu, codes.x, codes.y & 0x0F0F0F0Fu, codes.y};
+    const uint32_t a1[4] = {codes.z & 0x0F0F0F0Fu, codes.z, codes.w & 0x0F0F0F0Fu, codes.w};
     int c[4];
     mma_16832_u8s8(c, a0, b.x, b.y, true);
     mma_16832_u8s8(c, a1, b.z, b.w, false);
-    const float top_row = (float)(c[0] * 256 + c[1]);
-    const float low_row = (float)(c[2] * 256 + c[3]);
+    const int top = c[0] * 256 + c[1];
+    const float top_row = (float)top;
+    const float low_row = (float)(c[2] * 256 + c[3] - top);  // 16 x the sum of row gid + 8
     const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&meta.x));
     const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&meta.y));
     acc[0] = fmaf(lo.x * ss.x, top_row, fmaf(lo.y, ss.y, acc[0]));
-    acc[1] = fmaf(hi.x * ss.x, low_row, fmaf(hi.y, ss.y, acc[1]));
+    acc[1] = fmaf(hi.x * (0.0625f * ss.x), low_row, fmaf(hi.y, ss.y, acc[1]));
 }
 
 // fp16 form: lane (gid, t), column tile n: acc[4n + j] = (row gid + 8 (j >> 1), activation row 8n + 2t + (j & 1))
@@ -532,39 +524,41 @@ template <int MODE, bool SEQ>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 decode_kernel(const __grid_constant__ PassParams p) {
     using F = Form<MODE>;
-    constexpr int NT = F::NT, VALS = F::VALS, STAGES = F::STAGES;
-    constexpr uint32_t kChunkBytes = kChunkGroups * F::XGROUP;
+    constexpr int NT = F::NT, VALS = F::VALS;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     if (!SEQ) asm volatile("griddepcontrol.launch_dependents;");  // the next launch may start prefetching weights
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, t = lane & 3;
     const uint32_t cta = blockIdx.x, ctas = gridDim.x;
+    const uint32_t m_rows = p.m_rows, stages = p.stages;
+    const uint32_t entry_bytes = F::entry_bytes(m_rows);
 
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[4], empty[4], xfull[2], xempty[2]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[3], empty[3], xfull[3], xempty[3]
     volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem_raw + 96);
+    uint32_t *published = reinterpret_cast<uint32_t *>(smem_raw + 100);  // tiles this CTA finished since it last said so
     uint8_t *ring = smem_raw + 128;
-    uint8_t *xring = ring + STAGES * kStageBytes;
-    float *xchg = reinterpret_cast<float *>(xring + kChunks * kChunkBytes);
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 32, xfull0 = full0 + 64, xempty0 = full0 + 80;
+    uint8_t *entries = ring + stages * kStageBytes;  // [kEntrySets][8 groups][entry_bytes]
+    float *xchg = reinterpret_cast<float *>(entries + kEntrySets * kStageGroups * entry_bytes);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 24, xfull0 = full0 + 48, xempty0 = full0 + 72;
     const uint32_t ring0 = smem_u32(ring);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, kConsumers);
         }
-        for (uint32_t c = 0; c < kChunks; ++c) {
-            mbar_init(xfull0 + 8 * c, 1);
+        for (uint32_t c = 0; c < kEntrySets; ++c) {
+            mbar_init(xfull0 + 8 * c, kConsumers);
             mbar_init(xempty0 + 8 * c, kConsumers);
         }
         *failed = 0;
+        *published = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     const uint32_t job_count = SEQ ? p.job_count : 1u;
-    const uint32_t m_rows = p.m_rows;
 
     if (warp == kProducerWarp) {
         // ---- weight producer: one thread streams every unit of every job, never draining the ring ----
@@ -572,6 +566,17 @@ decode_kernel(const __grid_constant__ PassParams p) {
             uint32_t it = 0, issued = 0;
             for (uint32_t j = 0; j < job_count; ++j) {
                 const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
+                if (SEQ) {
+                    // This thread reads its way through the job table far ahead of the consumers, one dependent
+                    // load after another: the descriptors of the next two jobs start for L1 now, so that walking
+                    // into them later costs no round trip to L2 with the copy engine idle meanwhile.
+                    for (uint32_t ahead = 1; ahead <= 2 && j + ahead < job_count; ++ahead) {
+                        const uint8_t *next = reinterpret_cast<const uint8_t *>(p.jobs + j + ahead);
+                        for (uint32_t line = 0; line < sizeof(DecodeJob); line += 128) {
+                            asm volatile("prefetch.global.L1 [%0];" ::"l"(next + line));
+                        }
+                    }
+                }
                 const uint32_t G = job.groups;
                 for (uint32_t index = cta; index < job.units; index += ctas) {
                     const Unit u = unit_of(job, index);
@@ -580,8 +585,8 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     const uint8_t *b = job.fused ? job.up_tiles + (size_t)u.local * G * kUnitBytes
                                                  : a + (size_t)G * kUnitBytes;
                     for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
-                        const uint32_t s = it % STAGES;
-                        if (it >= (uint32_t)STAGES) mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, failed, 0x91u);
+                        const uint32_t s = it % stages;
+                        if (it >= stages) mbar_wait(empty0 + 8 * s, ((it / stages) - 1) & 1, failed, 0x91u);
                         if (*failed != 0) continue;  // no new copies once a wait has expired
                         const uint32_t bytes = min(kStageGroups, u.g1 - g) * kUnitBytes;
                         mbar_expect_tx(full0 + 8 * s, u.has_b ? 2 * bytes : bytes);
@@ -597,157 +602,205 @@ decode_kernel(const __grid_constant__ PassParams p) {
             if (*failed != 0) {
                 // the copies already issued must land before this CTA's shared memory is released: the last
                 // fill of every stage (a bounded spin of its own, whatever the failure flag says)
-                for (uint32_t i = issued > (uint32_t)STAGES ? issued - STAGES : 0; i < issued; ++i) {
+                for (uint32_t i = issued > stages ? issued - stages : 0; i < issued; ++i) {
                     const long long start = clock64();
-                    while (!mbar_try_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1) &&
+                    while (!mbar_try_wait(full0 + 8 * (i % stages), (i / stages) & 1) &&
                            clock64() - start < kWaitLimitCycles) {
-                    }
-                }
-            }
-        }
-    } else if (warp >= kLoaderWarp) {
-        // ---- activation loaders: loader L fills slot L of the ring, i.e. every other chunk ----
-        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // x may be what the previous launch wrote
-        const uint32_t which = (uint32_t)(warp - kLoaderWarp);
-        uint32_t epoch = 0;
-        if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
-        Cursor c = {};
-        c.index = cta;
-        cursor_settle<SEQ>(c, p, job_count, cta, ctas);
-        for (uint32_t skip = 0; skip < which && c.valid; ++skip) cursor_advance<SEQ>(c, p, job_count, cta, ctas);
-        uint32_t ready_job = 0;  // the outputs every job up to this one may read are complete
-        uint32_t fills = 0;      // chunks this loader has handed over
-        uint32_t held[kChunkGroups][8];  // integer form, fp16 x: the current chunk's activations, fetched a chunk ahead
-        bool have_held = false;
-        const uint32_t row = (uint32_t)gid >> 1;  // integer form: this lane's activation row
-        while (c.valid) {
-            const DecodeJob &job = SEQ ? p.jobs[c.j] : p.job;
-            const size_t K = (size_t)job.groups * kGroup;
-            if (SEQ && c.j > ready_job) {
-                // x of this job may be what the previous job wrote, on this or any rank: wait until every
-                // 16-row tile of it, on every rank, has been counted in this launch
-                const uint32_t expected = 4u * p.jobs[c.j - 1].expected_blocks * epoch;
-                const uint32_t *counter = p.done + ((size_t)(c.j - 1) * 8 + (lane & 7)) * kDoneStride;
-                const long long start = clock64();
-                for (;;) {
-                    uint32_t seen = 0;
-                    if (lane < 8) {
-                        if (p.world > 1) {
-                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-                        } else {
-                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-                        }
-                    }
-                    seen += __shfl_xor_sync(0xffffffffu, seen, 1);
-                    seen += __shfl_xor_sync(0xffffffffu, seen, 2);
-                    seen += __shfl_xor_sync(0xffffffffu, seen, 4);
-                    seen = __shfl_sync(0xffffffffu, seen, 0);
-                    if ((int32_t)(seen - expected) >= 0 || *failed != 0) break;
-                    if (clock64() - start > kWaitLimitCycles) {
-                        *failed = 0x95u;
-                        break;
-                    }
-                }
-                asm volatile("fence.acq_rel.gpu;" ::: "memory");
-                __syncwarp();
-                ready_job = c.j;
-                have_held = false;
-            }
-            const uint32_t count = min(kChunkGroups, c.u.g1 - c.g);
-            uint8_t *chunk = xring + which * kChunkBytes;
-            const uint32_t g = c.g, j = c.j;
-            // this loader's next chunk
-            for (int step = 0; step < kLoaders && c.valid; ++step) cursor_advance<SEQ>(c, p, job_count, cta, ctas);
-            bool fetch_next = false;
-            if (MODE == 0 && job.x_dtype != kF32) {
-                if (!have_held) {
-#pragma unroll
-                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
-                        fetch_x16(job.x, (size_t)row * K + (size_t)(g + q) * kGroup + 16 * t,
-                                  row < m_rows && q < count, held[q]);
-                    }
-                }
-                if (fills >= 1) mbar_wait(xempty0 + 8 * which, (fills - 1) & 1, failed, 0x94u);
-                digitize_chunk_f16(held, count, chunk, lane);
-                // this loader's next chunk of the same job leaves for the registers as soon as this one is handed
-                // over (below): its latency passes while the consumers work (the job after may not be written yet)
-                fetch_next = c.valid && c.j == j;
-            } else {
-                if (fills >= 1) mbar_wait(xempty0 + 8 * which, (fills - 1) & 1, failed, 0x94u);
-                if (MODE == 0) {
-                    digitize_chunk_f32(job, m_rows, K, g, count, chunk, lane);
-                } else {
-#pragma unroll
-                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
-                        load_group_f16<NT>(job, m_rows, K, g + q, chunk + q * F::XGROUP, lane, q < count);
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xfull0 + 8 * which);
-            ++fills;
-            if (MODE == 0) {
-                have_held = fetch_next;
-                if (fetch_next) {
-                    const uint32_t next_count = min(kChunkGroups, c.u.g1 - c.g);
-#pragma unroll
-                    for (uint32_t q = 0; q < kChunkGroups; ++q) {
-                        fetch_x16(job.x, (size_t)row * K + (size_t)(c.g + q) * kGroup + 16 * t,
-                                  row < m_rows && q < next_count, held[q]);
                     }
                 }
             }
         }
     } else {
         // ---- consumers: warp w owns tile w & 3 of block w >> 2 of every pair block this CTA visits ----
-        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // y, residual and scratch belong to stream order
+        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // x, y, residual and scratch belong to stream order
         const int k = warp >> 2, r = warp & 3;
-        uint32_t it = 0, xi = 0;
+        uint32_t epoch = 0;
+        if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
+        uint32_t it = 0;
+        // optional phase clocks: consumer warp 0 stamps its own progress (its lane 0 adds them up at the end)
+        const bool stamp = SEQ && p.profile != nullptr && warp == 0 && lane == 0;
+        long long *phase = reinterpret_cast<long long *>(xchg + 4 * 32 * F::XCHG_VALS);  // [kProfileSlots], this lane's alone
+        if (stamp) {
+            for (int slot = 0; slot < kProfileSlots; ++slot) phase[slot] = 0;
+        }
+        long long mark = stamp ? clock64() : 0;
+        const long long begun = mark;
+        auto lap = [&](int slot) {
+            if (stamp) {
+                const long long now = clock64();
+                phase[slot] += now - mark;
+                mark = now;
+            }
+        };
+        // Entries are made in passes: in the integer form one pass of a warp serves 4, 2 or 1 groups (M = 1, 2,
+        // 3..4), in the fp16 form one.  The warps take the passes of successive stages in turn, and every pass
+        // runs TWO stages ahead of the tiles that use it (three sets of entries, handed over through the mbarrier
+        // pairs xfull / xempty, eight arrivals each): a warp busy with a pass delays nobody, there is no barrier
+        // among the consumers.
+        const uint32_t shift = MODE != 0 ? 2u : m_rows == 1 ? 0u : m_rows == 2 ? 1u : 2u;
+        const uint32_t per_pass = 4u >> shift;
+        const uint8_t *lane_tiles = ring + (size_t)k * kStageGroups * kUnitBytes + r * kTileBytes;
         for (uint32_t j = 0; j < job_count; ++j) {
             const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
             const bool fused = job.fused != 0;
+            const bool x16 = job.x_dtype != kF32;
+            const size_t K = (size_t)job.groups * kGroup;
+            if (SEQ) {
+                // the next job's descriptor on its way into L1 while this job runs
+                if (warp == 0 && j + 1 < job_count && lane * 128u < sizeof(DecodeJob)) {
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(p.jobs + j + 1) + lane * 128));
+                }
+                if (j > 0 && cta < job.units) {
+                    // x of this job may be what the previous job wrote, on this or any rank: wait until every
+                    // 16-row tile of it, on every rank, has been counted in this launch.  One warp per CTA asks
+                    // (with a pause between questions: thousands of askers on eight lines of L2 would delay the
+                    // very additions they wait for); a barrier passes its answer on to the others.
+                    if (warp == 0) {
+                        const uint32_t expected = 4u * p.jobs[j - 1].expected_blocks * epoch;
+                        const uint32_t *counter = p.done + ((size_t)(j - 1) * 8 + (lane & 7)) * kDoneStride;
+                        const long long start = clock64();
+                        for (;;) {
+                            uint32_t seen = 0;
+                            if (lane < 8) {
+                                if (p.world > 1) {
+                                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                                } else {
+                                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                                }
+                            }
+                            seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+                            seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+                            seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+                            seen = __shfl_sync(0xffffffffu, seen, 0);
+                            if ((int32_t)(seen - expected) >= 0 || *failed != 0) break;
+                            if (clock64() - start > kWaitLimitCycles) {
+                                *failed = 0x95u;
+                                break;
+                            }
+                            __nanosleep(100);
+                        }
+                        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    lap(kProfileDependency);
+                }
+            }
             for (uint32_t index = cta; index < job.units; index += ctas) {
                 const Unit u = unit_of(job, index);
                 const bool active = k == 0 || u.has_b;
                 float acc[VALS];
 #pragma unroll
                 for (int v = 0; v < VALS; ++v) acc[v] = 0.0f;
-                for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
-                    const uint32_t s = it % STAGES;
-                    mbar_wait(full0 + 8 * s, (it / STAGES) & 1, failed, 0x92u);
-                    const uint8_t *stage = ring + s * kStageBytes + (size_t)k * kStageGroups * kUnitBytes + r * kTileBytes;
-                    const uint32_t in_stage = min(kStageGroups, u.g1 - g);
-                    for (uint32_t h = 0; h < in_stage; h += kChunkGroups, ++xi) {
-                        const uint32_t c = xi % kChunks;
-                        mbar_wait(xfull0 + 8 * c, (xi / kChunks) & 1, failed, 0x93u);
-                        const uint32_t count = min(kChunkGroups, in_stage - h);
-                        if (active) {
-                            const uint8_t *tiles = stage + (size_t)h * kUnitBytes;
-                            const uint8_t *slots = xring + c * kChunkBytes;
-                            if (count == kChunkGroups) {  // the common case without a branch between the tiles
+                // this warp's pass of the stage with counter `counter` (groups from `g`), if it has one: [first, +count)
+                auto my_pass = [&](uint32_t counter, uint32_t g, uint32_t &first, uint32_t &count) {
+                    const uint32_t groups_in_stage = min(kStageGroups, u.g1 - g);
+                    const uint32_t passes = (groups_in_stage + per_pass - 1) / per_pass;
+                    const uint32_t mine = ((uint32_t)warp - counter * (kStageGroups / per_pass)) & 7u;
+                    first = mine * per_pass;
+                    count = mine < passes ? min(per_pass, groups_in_stage - first) : 0u;
+                };
+                uint32_t raw[MODE == 0 ? 8 : 8 * NT];
+                // fetch == true: only send the loads off (fp16 x); false: make the entries from what was fetched
+                auto pass_step = [&](uint32_t counter, uint32_t g, bool fetch) {
+                    uint32_t first, count;
+                    my_pass(counter, g, first, count);
+                    if (count == 0) return;
+                    uint8_t *first_entry = entries + (size_t)(counter % kEntrySets) * kStageGroups * entry_bytes +
+                                           first * entry_bytes;
+                    if constexpr (MODE == 0) {
+                        const Pass pass = pass_of(lane, shift, count, m_rows);
+                        if (fetch) {
+                            if (x16) pass_fetch(job, K, g + first, pass, lane, raw);
+                        } else {
+                            pass_finish(job, K, g + first, pass, shift, count, m_rows, raw, first_entry, entry_bytes, lane);
+                        }
+                    } else {
+                        if (fetch) {
+                            if (x16) fetch_held<NT>(job, m_rows, K, g + first, lane, raw);
+                        } else {
+                            entry_f16<NT>(job, m_rows, K, g + first, raw, first_entry, lane);
+                        }
+                    }
+                };
+                auto hand_over = [&](uint32_t counter) {  // this warp's part of the stage's entries is in place
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xfull0 + 8 * (counter % kEntrySets));
+                };
+                auto wait_set_free = [&](uint32_t counter) {  // the tiles of three stages ago are done with the set
+                    if (counter >= kEntrySets) {
+                        mbar_wait(xempty0 + 8 * (counter % kEntrySets), ((counter / kEntrySets) - 1) & 1, failed, 0x94u);
+                    }
+                };
+                // the unit's first two stages: nothing to hide their entries behind.  With several groups to a pass
+                // a warp has a pass in at most one of the two, so the stages' passes run side by side on
+                // different warps; otherwise a warp makes its two passes one after the other.
+                if (per_pass > 1) {
+                    const uint32_t g2 = u.g0 + kStageGroups;
+                    uint32_t first, count;
+                    my_pass(it, u.g0, first, count);
+                    const bool second = count == 0 && g2 < u.g1;  // no pass in the first stage: maybe in the second
+                    wait_set_free(it);
+                    if (g2 < u.g1) wait_set_free(it + 1);
+                    pass_step(second ? it + 1 : it, second ? g2 : u.g0, true);
+                    pass_step(second ? it + 1 : it, second ? g2 : u.g0, false);
+                    hand_over(it);
+                    if (g2 < u.g1) hand_over(it + 1);
+                } else {
 #pragma unroll
-                                for (uint32_t q = 0; q < kChunkGroups; ++q) {
-                                    if (MODE == 0) {
-                                        tile_digits(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
-                                    } else {
-                                        tile_f16<NT>(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
-                                    }
+                    for (uint32_t d = 0; d < 2; ++d) {
+                        const uint32_t g = u.g0 + d * kStageGroups;
+                        if (g < u.g1) {
+                            wait_set_free(it + d);
+                            pass_step(it + d, g, true);
+                            pass_step(it + d, g, false);
+                            hand_over(it + d);
+                        }
+                    }
+                }
+                lap(kProfileEntries);
+                for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
+                    const uint32_t s = it % stages;
+                    const uint32_t in_stage = min(kStageGroups, u.g1 - g);
+                    const uint8_t *set = entries + (size_t)(it % kEntrySets) * kStageGroups * entry_bytes;
+                    const uint32_t g_ahead = g + 2 * kStageGroups;
+                    if (g_ahead < u.g1) pass_step(it + 2, g_ahead, true);  // loads first: they pass under the tiles
+                    mbar_wait(xfull0 + 8 * (it % kEntrySets), (it / kEntrySets) & 1, failed, 0x93u);
+                    lap(kProfileEntries);
+                    mbar_wait(full0 + 8 * s, (it / stages) & 1, failed, 0x92u);
+                    lap(kProfileWeights);
+                    if (active) {
+                        const uint8_t *tiles = lane_tiles + s * kStageBytes;
+                        if (in_stage == kStageGroups) {  // the common case without a branch between the tiles
+#pragma unroll
+                            for (uint32_t q = 0; q < kStageGroups; ++q) {
+                                if (MODE == 0) {
+                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, m_rows, lane, acc);
+                                } else {
+                                    tile_f16<NT>(tiles + q * kUnitBytes, set + q * entry_bytes, lane, acc);
                                 }
-                            } else {
-                                for (uint32_t q = 0; q < count; ++q) {
-                                    if (MODE == 0) {
-                                        tile_digits(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
-                                    } else {
-                                        tile_f16<NT>(tiles + q * kUnitBytes, slots + q * F::XGROUP, lane, acc);
-                                    }
+                            }
+                        } else {
+                            for (uint32_t q = 0; q < in_stage; ++q) {
+                                if (MODE == 0) {
+                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, m_rows, lane, acc);
+                                } else {
+                                    tile_f16<NT>(tiles + q * kUnitBytes, set + q * entry_bytes, lane, acc);
                                 }
                             }
                         }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(xempty0 + 8 * c);
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                    if (lane == 0) {
+                        mbar_arrive(xempty0 + 8 * (it % kEntrySets));
+                        mbar_arrive(empty0 + 8 * s);
+                    }
+                    lap(kProfileTiles);
+                    if (g_ahead < u.g1) {
+                        wait_set_free(it + 2);
+                        pass_step(it + 2, g_ahead, false);
+                        hand_over(it + 2);
+                        lap(kProfileEntries);
+                    }
                 }
 
                 // ---- the unit is done: finish this warp's tile ----
@@ -800,12 +853,26 @@ decode_kernel(const __grid_constant__ PassParams p) {
                             const int gate_warp = fused ? r : warp;
 #pragma unroll
                             for (int v = 0; v < VALS; ++v) acc[v] = 0.0f;
-                            for (uint32_t q = 0; q < job.parts; ++q) {
-                                const float *from = base + (size_t)q * (8 * 32 * VALS);
+                            // several parts' loads in flight at a time, added in part order
+                            for (uint32_t q0 = 0; q0 < job.parts; q0 += F::SUM_UNROLL) {
+                                float first[F::SUM_UNROLL][VALS], other[F::SUM_UNROLL][VALS];
 #pragma unroll
-                                for (int v = 0; v < VALS; ++v) {
-                                    acc[v] += __ldcg(from + (v * 8 + gate_warp) * 32 + lane);
-                                    if (fused) second[v] += __ldcg(from + (v * 8 + gate_warp + 4) * 32 + lane);
+                                for (int i = 0; i < F::SUM_UNROLL; ++i) {
+                                    const bool live = q0 + i < job.parts;
+                                    const float *from = base + (size_t)(q0 + i) * (8 * 32 * VALS);
+#pragma unroll
+                                    for (int v = 0; v < VALS; ++v) {
+                                        first[i][v] = live ? __ldcg(from + (v * 8 + gate_warp) * 32 + lane) : 0.0f;
+                                        other[i][v] = live && fused ? __ldcg(from + (v * 8 + gate_warp + 4) * 32 + lane) : 0.0f;
+                                    }
+                                }
+#pragma unroll
+                                for (int i = 0; i < F::SUM_UNROLL; ++i) {
+#pragma unroll
+                                    for (int v = 0; v < VALS; ++v) {
+                                        acc[v] += first[i][v];
+                                        second[v] += other[i][v];
+                                    }
                                 }
                             }
                         }
@@ -842,22 +909,38 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         }
                     }
                     if (SEQ) {
-                        // this tile is stored everywhere: count it on every rank
                         __syncwarp();
-                        if (lane == 0) {
-                            const size_t at = ((size_t)j * 8 + warp) * kDoneStride;
+                        if (lane == 0) atomicAdd(published, 1u);  // this tile is stored everywhere
+                    }
+                }
+                if (SEQ) {
+                    // One thread counts the CTA's finished tiles on every rank: one fence for all the warps'
+                    // stores (the barrier orders them before it), one addition per rank.
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (warp == 0 && lane == 0) {
+                        const uint32_t tiles_done = atomicExch(published, 0u);
+                        if (tiles_done > 0) {
+                            const size_t at = ((size_t)j * 8 + (cta & 7u)) * kDoneStride;
                             if (p.world > 1) {
                                 asm volatile("fence.acq_rel.sys;" ::: "memory");
                                 for (uint32_t rank = 0; rank < p.world; ++rank) {
                                     asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;"
-                                                 ::"l"(p.peer_done[rank] + at), "r"(1u) : "memory");
+                                                 ::"l"(p.peer_done[rank] + at), "r"(tiles_done) : "memory");
                                 }
                             } else {
-                                asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.done + at), "r"(1u) : "memory");
+                                asm volatile("red.release.gpu.global.add.u32 [%0], %1;"
+                                             ::"l"(p.done + at), "r"(tiles_done) : "memory");
                             }
                         }
                     }
                 }
+                lap(kProfileFinish);
+            }
+        }
+        if (stamp) {
+            phase[kProfileTotal] = clock64() - begun;
+            for (int slot = 0; slot < kProfileSlots; ++slot) {
+                p.profile[(size_t)cta * kProfileSlots + slot] += (unsigned long long)phase[slot];
             }
         }
     }
@@ -882,25 +965,34 @@ int mode_of(uint32_t m_rows, int variant) {
     return m_rows <= 8 ? 1 : 2;
 }
 
-size_t smem_of(int mode) {
-    return mode == 0 ? smem_bytes_of<0>() : mode == 1 ? smem_bytes_of<1>() : smem_bytes_of<2>();
+size_t smem_of(int mode, uint32_t m_rows, uint32_t *stages) {
+    return mode == 0 ? smem_bytes_of<0>(m_rows, stages) : mode == 1 ? smem_bytes_of<1>(m_rows, stages)
+                                                                    : smem_bytes_of<2>(m_rows, stages);
 }
 
 template <int MODE, bool SEQ>
 cudaError_t configure(size_t smem_bytes, int *blocks_per_sm) {
     auto kernel = decode_kernel<MODE, SEQ>;
-    static int resident[kMaxDevices];  // per instantiation and device; 0 = not configured yet
+    // per instantiation and device: the dynamic shared memory granted so far, and the last occupancy answer
+    static size_t granted[kMaxDevices], asked[kMaxDevices];
+    static int resident[kMaxDevices];
     const int slot = device_slot();
-    if (slot >= 0 && resident[slot] > 0) {
+    if (slot >= 0 && resident[slot] > 0 && asked[slot] == smem_bytes) {
         *blocks_per_sm = resident[slot];
         return cudaSuccess;
     }
-    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-    if (status != cudaSuccess) return status;
-    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, kernel, kDecodeThreads, smem_bytes);
+    if (slot < 0 || smem_bytes > granted[slot]) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (status != cudaSuccess) return status;
+        if (slot >= 0) granted[slot] = smem_bytes;
+    }
+    cudaError_t status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, kernel, kDecodeThreads, smem_bytes);
     if (status != cudaSuccess) return status;
     if (*blocks_per_sm < 1) return cudaErrorInvalidConfiguration;
-    if (slot >= 0) resident[slot] = *blocks_per_sm;
+    if (slot >= 0) {
+        resident[slot] = *blocks_per_sm;
+        asked[slot] = smem_bytes;
+    }
     return cudaSuccess;
 }
 
@@ -924,7 +1016,7 @@ uint32_t decode_max_m() { return 16; }
 // device addresses come from cudaGetSymbolAddress, looked up once per device
 // with that device current.
 // ---------------------------------------------------------------------------
-constexpr size_t kStaticScratchBytes = 2u << 20;  // 2 MiB of partial-sum slots
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB of partial-sum slots
 constexpr size_t kStaticCounterCount = 4096;      // one arrival counter per 16-row tile of a split pair block
 static __device__ __align__(256) float q4b_static_scratch[kStaticScratchBytes / sizeof(float)];
 static __device__ __align__(256) uint32_t q4b_static_counters[kStaticCounterCount];
@@ -960,7 +1052,7 @@ cudaError_t decode_static_scratch(float **scratch, uint32_t **counters, size_t *
 cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool sequence, DecodeGeometry *geometry) {
     if (m_rows == 0 || m_rows > decode_max_m()) return cudaErrorInvalidValue;
     geometry->mode = mode_of(m_rows, variant);
-    geometry->smem_bytes = smem_of(geometry->mode);
+    geometry->smem_bytes = smem_of(geometry->mode, m_rows, &geometry->stages);
     int per_sm = 0;
     cudaError_t status = configure_mode(geometry->mode, sequence, geometry->smem_bytes, &per_sm);
     if (status != cudaSuccess) return status;
@@ -968,6 +1060,9 @@ cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool seq
     const int wanted = variant & 0xf;
     if (wanted >= 1 && wanted < per_sm) per_sm = wanted;
     geometry->ctas = (uint32_t)(per_sm * sm_count);
+    // the K split is planned for two thread blocks per SM whatever is resident, so that a row's sum is grouped the
+    // same way in every form of the kernel (a grid that is smaller takes the units in turns)
+    geometry->plan_ctas = (uint32_t)(2 * sm_count);
     geometry->threads = kDecodeThreads;
     geometry->max_parts = (uint32_t)((variant >> 8) & 0xf);
     return cudaSuccess;
@@ -986,9 +1081,9 @@ void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geom
     // Fewer pair blocks than CTAs: cut K into equal parts so that the whole grid streams, a part no shorter
     // than four groups.  Otherwise every CTA takes whole pair blocks in turn.
     uint32_t parts = 1;
-    if (pairs < geometry.ctas) {
+    if (pairs < geometry.plan_ctas) {
         for (uint32_t k = 1; k <= G; ++k) {
-            if (pairs * k <= geometry.ctas && (G / k >= 4 || k == 1)) parts = k;
+            if (pairs * k <= geometry.plan_ctas && (G / k >= 4 || k == 1)) parts = k;
         }
     }
     if (geometry.max_parts > 0 && parts > geometry.max_parts) parts = geometry.max_parts;
@@ -1034,6 +1129,7 @@ cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeo
     p.job_count = 1;
     p.m_rows = m_rows;
     p.world = 1;
+    p.stages = geometry.stages;
     p.scratch = scratch;
     p.counters = counters;
     p.status = status;
@@ -1052,6 +1148,7 @@ cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream) {
     p.job_count = launch.job_count;
     p.m_rows = launch.m_rows;
     p.world = launch.world;
+    p.stages = launch.geometry.stages;
     p.epoch = launch.epoch;
     p.exit_count = launch.exit_count;
     p.done = launch.done;
@@ -1059,6 +1156,7 @@ cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream) {
     p.scratch = launch.scratch;
     p.counters = launch.counters;
     p.status = launch.status;
+    p.profile = launch.profile;
     switch (launch.geometry.mode) {
         case 0: return launch_kernel<0, true>(p, launch.geometry.ctas, launch.geometry.smem_bytes, false, stream);
         case 1: return launch_kernel<1, true>(p, launch.geometry.ctas, launch.geometry.smem_bytes, false, stream);

@@ -32,9 +32,9 @@ namespace q4b {
 namespace {
 
 // ring stages (one quantisation group each); a multiple of the number of warpgroups, see the dequantisation loop
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, bool Q8 = false>
 struct TcStages {
-    static constexpr int value = BN == 256 ? 4 : 8;
+    static constexpr int value = BN == 256 || Q8 ? 4 : 8;  // a Q8 stage holds 8.7 KB of weights, not 4.6
 };
 constexpr int kTcSlots = 8;        // A-operand slots in TMEM (32 columns each)
 constexpr int kTcWarpgroups = 4;   // dequantisation warpgroups; group g belongs to warpgroup g % 4
@@ -198,12 +198,15 @@ __device__ inline uint32_t tc_cta_of_iteration(const TcParams &p, uint32_t itera
 // BF   : bf16 activations against weights rounded to bf16 (the arithmetic of
 //        minimax_h3_q4_gemm_bf16_activation, minimax_h3_attention.metal:512-592, and of its CPU check,
 //        minimax_h3_m3_real_gemm.c:25-42); otherwise fp16 activations against fp16 weights
-template <int BN, bool FUSED, bool BF>
+// Q8   : the weights are an affine-Q8 stream (minimax_h3_q8_gemm_bf16_meta, minimax_h3_attention.metal:594-676):
+//        one 8704-byte tile per group, w = half(float(scale) * q + float(bias)) with bf16 scale and bias
+template <int BN, bool FUSED, bool BF, bool Q8 = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
-    constexpr int kTcStages = TcStages<BN, FUSED>::value;
+    static_assert(!Q8 || (!FUSED && !BF), "the Q8 sibling is a plain fp16 GEMM");
+    constexpr int kTcStages = TcStages<BN, FUSED, Q8>::value;
     constexpr uint32_t kXBytes = BN * 128;               // one group of X: BN rows x 64 halves
-    constexpr uint32_t kWBytes = 2 * kUnitBytes;         // two 64-row blocks, one group
+    constexpr uint32_t kWBytes = Q8 ? kQ8TileBytes : 2 * kUnitBytes;  // 128 rows of one group
     constexpr uint32_t kDCols = BN;
     constexpr uint32_t kTmemCols = kDCols + kTcSlots * 32 <= 256 ? 256 : 512;
     static_assert(kDCols + kTcSlots * 32 <= 512, "accumulators and A slots must fit the 512 TMEM columns");
@@ -274,12 +277,16 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t bar = full0 + 8 * s;
                     tc_mbar_expect_tx(bar, kWBytes + kXBytes);
                     const uint32_t wdst = tc_smem_u32(wbuf) + s * kWBytes;
+                    if constexpr (Q8) {
+                        tc_bulk_copy(wdst, tiles + ((size_t)nb * G + g) * kQ8TileBytes, kQ8TileBytes, bar);
+                    } else {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint8_t *stream = FUSED && h == 1 ? p.up.tiles : tiles;
-                        const uint32_t block = FUSED ? nb : nb * 2 + h;  // 64-row block of that stream
-                        const size_t offset = ((size_t)block * G + g) * kUnitBytes;
-                        tc_bulk_copy(wdst + h * kUnitBytes, stream + offset, kUnitBytes, bar);
+                        for (int h = 0; h < 2; ++h) {
+                            const uint8_t *stream = FUSED && h == 1 ? p.up.tiles : tiles;
+                            const uint32_t block = FUSED ? nb : nb * 2 + h;  // 64-row block of that stream
+                            const size_t offset = ((size_t)block * G + g) * kUnitBytes;
+                            tc_bulk_copy(wdst + h * kUnitBytes, stream + offset, kUnitBytes, bar);
+                        }
                     }
                     tc_tensor_copy_2d(tc_smem_u32(xbuf) + s * kXBytes, &p.x_map, (int)(g * kGroup), (int)(mb * BN), bar);
                 }
@@ -360,6 +367,33 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     // uses (a parity wait that skips a fill is satisfied by the fill before last), and a stage it is
                     // still waiting for cannot be refilled, since the MMA that frees it needs this warpgroup's A tile.
                     if (!tc_wait(full0 + 8 * s, (it / kTcStages) & 1)) { ok = false; break; }
+                    uint32_t regs[32];
+                    if constexpr (Q8) {
+                        // thread = weight row: 64 code bytes in four pieces, one {bf16 scale, bf16 bias} record;
+                        // 0x4B0000qq is the float 8388608 + q, so q comes out exact with one subtraction; the
+                        // product with the bf16 scale is exact in fp32, the sum rounds once, then once to fp16
+                        const uint8_t *tile_q8 = wbuf + s * kWBytes;
+                        const uint32_t record = reinterpret_cast<const uint32_t *>(tile_q8 + kQ8CodeBytes)[row];
+                        const float scale_f = __uint_as_float(record << 16), bias_f = __uint_as_float(record & 0xffff0000u);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const uint4 piece = reinterpret_cast<const uint4 *>(tile_q8)[q8_piece_index(row, t)];
+                            const uint32_t word[4] = {piece.x, piece.y, piece.z, piece.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float value[4];
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) {
+                                    const uint32_t bits = __byte_perm(word[i], 0x4B000000u, 0x7540 + b);
+                                    value[b] = __fmaf_rn(scale_f, __uint_as_float(bits) - 8388608.0f, bias_f);
+                                }
+                                const __half2 w01 = __floats2half2_rn(value[0], value[1]);
+                                const __half2 w23 = __floats2half2_rn(value[2], value[3]);
+                                regs[8 * t + 2 * i] = *reinterpret_cast<const uint32_t *>(&w01);
+                                regs[8 * t + 2 * i + 1] = *reinterpret_cast<const uint32_t *>(&w23);
+                            }
+                        }
+                    } else {
                     const uint8_t *tile_bytes = wbuf + s * kWBytes + tile_offset_bytes;
                     const uint32_t record = *reinterpret_cast<const uint32_t *>(tile_bytes + kTileCodeBytes + gid * 8 + hi * 4);
                     const __half2 sb = *reinterpret_cast<const __half2 *>(&record);
@@ -368,7 +402,6 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     // bf16 to begin with (every bf16 in fp16's normal range is an fp16)
                     const __nv_bfloat162 scale_b = __float2bfloat162_rn(__low2float(sb));
                     const __nv_bfloat162 bias_b = __float2bfloat162_rn(__high2float(sb));
-                    uint32_t regs[32];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
                         const uint4 piece = *reinterpret_cast<const uint4 *>(tile_bytes + piece_index(gid * 4 + t) * 16);
@@ -403,6 +436,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                             regs[8 * t + 2 * i] = *reinterpret_cast<const uint32_t *>(&w01);
                             regs[8 * t + 2 * i + 1] = *reinterpret_cast<const uint32_t *>(&w23);
                         }
+                    }
                     }
                     if (unit >= kTcSlots && !tc_wait(a_free0 + 8 * a, ((unit / kTcSlots) - 1) & 1)) { ok = false; break; }
                     tc_fence_after();
@@ -628,7 +662,7 @@ EncodeTiledFn encode_tiled() {
     return function;
 }
 
-template <int BN, bool FUSED, bool BF>
+template <int BN, bool FUSED, bool BF, bool Q8 = false>
 cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled();
     if (encode == nullptr) return cudaErrorNotSupported;
@@ -648,10 +682,10 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     if (p.m_group < 1) p.m_group = 1;
     if (p.m_group > p.m_blocks) p.m_group = p.m_blocks;
     const uint32_t tiles = p.n_blocks * p.m_blocks;
-    constexpr int kTcStages = TcStages<BN, FUSED>::value;
-    const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + 2 * kUnitBytes) +
+    constexpr int kTcStages = TcStages<BN, FUSED, Q8>::value;
+    const size_t smem_bytes = (size_t)kTcStages * (BN * 128 + (Q8 ? kQ8TileBytes : 2 * kUnitBytes)) +
                               (2 * kTcStages + 2 * kTcSlots + 2) * 8 + 16 + kTcWarpgroups * 16 * 128 * 4 + 1024;
-    auto kernel = tc_gemm_kernel<BN, FUSED, BF>;
+    auto kernel = tc_gemm_kernel<BN, FUSED, BF, Q8>;
     static bool configured[kMaxDevices];  // per instantiation and device
     const int slot = device_slot();
     if (slot < 0 || !configured[slot]) {
@@ -718,6 +752,11 @@ cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t st
     if (blocks == 0) return cudaSuccess;
     p.y_dtype = args.y_dtype;
     p.residual_dtype = args.residual_dtype;
+    if (args.w[0].kind == kQ8) {
+        if (args.x_bf16 || args.fused_silu || args.segments != 1) return cudaErrorInvalidValue;
+        return args.m_rows <= 128 ? launch_tc_instance<128, false, false, true>(p, args, sm_count, stream)
+                                  : launch_tc_instance<256, false, false, true>(p, args, sm_count, stream);
+    }
     if (args.x_bf16) {
         if (args.fused_silu) {
             return args.m_rows <= 128 ? launch_tc_instance<128, true, true>(p, args, sm_count, stream)

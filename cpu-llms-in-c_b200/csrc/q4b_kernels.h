@@ -27,6 +27,10 @@ cudaError_t launch_repack(const uint8_t *quants, const void *meta, const void *b
 // tile stream -> codes u8 [rows][K], w32 [rows][K], w16 [rows][K] (any may be null)
 cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
                           cudaStream_t stream);
+// affine Q8 planes (device): codes [N][G][64] bytes, bf16 scales / biases [N][G] -> the Q8 stream; and back
+cudaError_t launch_repack_q8(const uint8_t *quants, const uint16_t *scales, const uint16_t *biases, uint32_t groups,
+                             uint32_t row_begin, uint32_t row_count, uint8_t *tiles, cudaStream_t stream);
+cudaError_t launch_unpack_q8(WeightView w, uint8_t *codes, float *w32, __half *w16, cudaStream_t stream);
 // rows[i] (device, numbered in the whole matrix; row_base = first row this shard holds) dequantised into
 // out[i][K] fp16 or fp32; rows the shard does not hold give zeros
 cudaError_t launch_lookup_rows(WeightView w, const uint32_t *rows, uint32_t count, uint32_t row_base, void *out,
@@ -73,8 +77,10 @@ struct DecodeJob {
 struct DecodeGeometry {
     int mode;            // 0 integer form (M <= 4), 1 fp16 form M <= 8, 2 fp16 form M <= 16
     uint32_t ctas;       // CTAs that are resident at once (the grid of a sequence; the limit of a single launch)
+    uint32_t plan_ctas;  // the grid the K split is planned for (two CTAs per SM)
     uint32_t threads;
     uint32_t max_parts;  // 0: no limit on the K parts of a pair block
+    uint32_t stages;     // stages of the weight ring (3 when two CTAs then still share an SM, else 2)
     size_t smem_bytes;
 };
 struct SequenceLaunch {
@@ -88,7 +94,9 @@ struct SequenceLaunch {
     float *scratch;
     uint32_t *counters;
     uint32_t *status;
+    unsigned long long *profile;  // null, or device [ctas][kProfileSlots]: SM clocks by phase, added up per launch
 };
+constexpr int kProfileSlots = 6;  // dependency wait, entries, weight wait, tiles, finish, total
 // a projection as the entry points of the C ABI describe it, before it is routed to a kernel by M
 struct ProjectionArgs {
     // up to kMaxSegments matrices that share x (same K); fused gate/up uses

@@ -165,6 +165,78 @@ cudaError_t launch_unpack(WeightView w, uint8_t *codes, float *w32, __half *w16,
 }
 
 // ---------------------------------------------------------------------------
+// affine Q8: planes [N][G][64] bytes + bf16 scales / biases [N][G] -> the Q8 stream, and its inverse
+// ---------------------------------------------------------------------------
+// one thread per (128-row block, group, row, piece)
+__global__ void __launch_bounds__(256)
+repack_q8_kernel(const uint8_t *__restrict__ quants, const uint16_t *__restrict__ scales,
+                 const uint16_t *__restrict__ biases, uint32_t groups, uint32_t row_begin, uint32_t row_count,
+                 uint32_t blocks, uint8_t *__restrict__ tiles) {
+    const uint64_t thread = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (thread >= (uint64_t)blocks * groups * kQ8Rows * 4) return;
+    const uint32_t piece = (uint32_t)(thread & 3u), row = (uint32_t)((thread >> 2) & (kQ8Rows - 1));
+    const uint64_t tile = thread >> 9;  // block * groups + g
+    const uint32_t g = (uint32_t)(tile % groups), local = (uint32_t)(tile / groups) * kQ8Rows + row;
+    uint8_t *out = tiles + tile * kQ8TileBytes;
+    uint4 codes = make_uint4(0u, 0u, 0u, 0u);
+    uint32_t record = 0;
+    if (local < row_count) {
+        const size_t at = (size_t)(row_begin + local) * groups + g;
+        codes = *reinterpret_cast<const uint4 *>(quants + at * kGroup + 16 * piece);
+        record = (uint32_t)scales[at] | ((uint32_t)biases[at] << 16);
+    }
+    reinterpret_cast<uint4 *>(out)[q8_piece_index(row, piece)] = codes;
+    if (piece == 0) reinterpret_cast<uint32_t *>(out + kQ8CodeBytes)[row] = record;
+}
+
+cudaError_t launch_repack_q8(const uint8_t *quants, const uint16_t *scales, const uint16_t *biases, uint32_t groups,
+                             uint32_t row_begin, uint32_t row_count, uint8_t *tiles, cudaStream_t stream) {
+    const uint32_t blocks = ceil_div(row_count, kQ8Rows);
+    const uint64_t threads = (uint64_t)blocks * groups * kQ8Rows * 4;
+    if (threads == 0) return cudaSuccess;
+    repack_q8_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(quants, scales, biases, groups, row_begin,
+                                                                            row_count, blocks, tiles);
+    return cudaGetLastError();
+}
+
+// The Q8 dequantisation contract: half(float(scale) * float(q) + float(bias)), the product exact in fp32, the sum
+// rounded once in fp32, then once to fp16 (minimax_h3_attention.metal:627-633).
+__device__ inline float dequant_q8_w32(uint32_t code, uint32_t record) {
+    const float scale = __uint_as_float(record << 16), bias = __uint_as_float(record & 0xffff0000u);
+    return __fmaf_rn(scale, (float)code, bias);
+}
+
+__global__ void __launch_bounds__(256)
+unpack_q8_kernel(WeightView w, uint8_t *__restrict__ codes, float *__restrict__ w32, __half *__restrict__ w16) {
+    const uint64_t thread = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t blocks = ceil_div(w.rows, kQ8Rows);
+    if (thread >= (uint64_t)blocks * w.groups * kQ8Rows * 4) return;
+    const uint32_t piece = (uint32_t)(thread & 3u), row = (uint32_t)((thread >> 2) & (kQ8Rows - 1));
+    const uint64_t tile = thread >> 9;
+    const uint32_t g = (uint32_t)(tile % w.groups), local = (uint32_t)(tile / w.groups) * kQ8Rows + row;
+    if (local >= w.rows) return;
+    const uint8_t *in = w.tiles + tile * kQ8TileBytes;
+    const uint4 words = reinterpret_cast<const uint4 *>(in)[q8_piece_index(row, piece)];
+    const uint32_t record = reinterpret_cast<const uint32_t *>(in + kQ8CodeBytes)[row];
+    const size_t base = (size_t)local * w.groups * kGroup + (size_t)g * kGroup + 16 * piece;
+    if (codes != nullptr) *reinterpret_cast<uint4 *>(codes + base) = words;
+    const uint32_t word[4] = {words.x, words.y, words.z, words.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float value = dequant_q8_w32((word[i >> 2] >> (8 * (i & 3))) & 0xffu, record);
+        if (w32 != nullptr) w32[base + i] = value;
+        if (w16 != nullptr) w16[base + i] = __float2half_rn(value);
+    }
+}
+
+cudaError_t launch_unpack_q8(WeightView w, uint8_t *codes, float *w32, __half *w16, cudaStream_t stream) {
+    const uint64_t threads = (uint64_t)ceil_div(w.rows, kQ8Rows) * w.groups * kQ8Rows * 4;
+    if (threads == 0) return cudaSuccess;
+    unpack_q8_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(w, codes, w32, w16);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // rows of a matrix, dequantised: the embedding lookup
 // (qwen38_q4_embedding_lookup, qwen38_global.metal:13-28: out[c] = half(float(scale) * float(q) + float(bias)))
 // ---------------------------------------------------------------------------

@@ -76,6 +76,8 @@ def library() -> ctypes.CDLL:
         "q4b_weight_upload": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_weight_upload_planes": (_int, [_vp, _vp, _vp, _vp, _int, _u32, _u32, _u32, _u32,
                                             ctypes.POINTER(_vp)] + err),
+        "q4b_weight_upload_q8": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
+        "q4b_planes_narrowed": (_u64, [_vp, _vp, _int, _u64]),
         "q4b_weight_from_device": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_weight_synth": (_int, [_vp, _u64, _u32, _u32, _u32, _u32, _u32, ctypes.POINTER(_vp)] + err),
         "q4b_synth_x": (_int, [_vp, _u64, _u64, _vp, _u64, _u64] + err),
@@ -111,6 +113,7 @@ def library() -> ctypes.CDLL:
         "q4b_sequence_done_counters": (_vp, [_vp]),
         "q4b_sequence_set_peer_counters": (_int, [_vp, _u32, _vp]),
         "q4b_sequence_launch": (_int, [_vp, _vp] + err),
+        "q4b_sequence_profile": (_int, [_vp, _vp, ctypes.POINTER(_u64), _u32, ctypes.POINTER(_u32)] + err),
         "q4b_sequence_free": (None, [_vp, _vp]),
         "q4b_ipc_export": (_int, [_vp, _vp, _vp] + err),
         "q4b_ipc_open": (_int, [_vp, _vp, ctypes.POINTER(_vp)] + err),
@@ -311,6 +314,25 @@ class Q4Sequence:
         self.context._check(library().q4b_sequence_launch(self.context.handle, self.handle,
                                                           self.context._err, _ERR))
 
+    PROFILE_PHASES = ("dependency", "entries", "weights", "tiles", "finish", "total")
+
+    def profile(self):
+        """First call: switches the phase clocks on, returns None.  Later calls: [thread blocks, 6] SM clock
+        ticks added up by the launches since the previous call (q4b_sequence_profile)."""
+        blocks = _u32(0)
+        first = not getattr(self, "_profiling", False)
+        if first:
+            self.context._check(library().q4b_sequence_profile(self.context.handle, self.handle, None, 0,
+                                                               ctypes.byref(blocks), self.context._err, _ERR))
+            self._profiling = True
+            self._profile_blocks = blocks.value
+            return None
+        out = np.zeros((self._profile_blocks, 6), dtype=np.uint64)
+        self.context._check(library().q4b_sequence_profile(
+            self.context.handle, self.handle, out.ctypes.data_as(ctypes.POINTER(_u64)), out.size,
+            ctypes.byref(blocks), self.context._err, _ERR))
+        return out
+
     def free(self):
         if self.handle:
             library().q4b_sequence_free(self.context.handle, self.handle)
@@ -394,6 +416,16 @@ class Q4Context:
         self._check(library().q4b_weight_upload_planes(self.handle, quants.ctypes.data, scales.ctypes.data,
                                                        biases.ctypes.data, meta_dtype, rows, groups, row_begin,
                                                        count, ctypes.byref(handle), self._err, _ERR))
+        return Q4Weight(self, handle.value)
+
+    def upload_q8(self, quants, scales_bf16, biases_bf16, rows, groups, row_begin=0, row_count=None):
+        """Affine-Q8 planes (codes [rows, K] bytes, bf16 scales / biases [rows, K/64]) -> HBM (q4b_weight_upload_q8)."""
+        quants, scales, biases = (np.ascontiguousarray(a) for a in (quants, scales_bf16, biases_bf16))
+        handle = _vp()
+        count = rows - row_begin if row_count is None else row_count
+        self._check(library().q4b_weight_upload_q8(self.handle, quants.ctypes.data, scales.ctypes.data,
+                                                   biases.ctypes.data, rows, groups, row_begin, count,
+                                                   ctypes.byref(handle), self._err, _ERR))
         return Q4Weight(self, handle.value)
 
     def synth_weight(self, seed: int, projection: int, rows: int, groups: int, row_begin: int = 0,

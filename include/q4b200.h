@@ -81,7 +81,15 @@ int q4b_weight_upload(q4b_context *context, const void *quants, const void *meta
 /* Same, from separate scale and bias planes in fp16 or bf16 -- the un-converted
  * MLX metadata that minimax_h3_q4_projection carries (compiler/minimax-h3/
  * apple-m3-pro/minimax_h3_q4_layer.h:14-24); bf16 is converted like the packer
- * does (qwen38_m3_pack.c:173-178). */
+ * does (qwen38_m3_pack.c:173-178): bf16 -> fp32 -> fp16, round to nearest even.
+ * The device holds fp16 records, so the reference kernel that reads bf16 planes
+ * as they are (minimax_h3_q4_gemm_bf16_meta, minimax_h3_attention.metal:416-506,
+ * dequantising in fp32) is matched exactly where every scale and bias is an fp16
+ * number -- every bf16 value with 2^-14 <= |v| <= 65504 is -- and not otherwise:
+ * smaller magnitudes lose bits or become zero, larger ones become infinite.
+ * q4b_planes_narrowed counts the values of a plane pair that would change (host
+ * only, no GPU needed): 0 means the upload is exact. */
+uint64_t q4b_planes_narrowed(const void *scales, const void *biases, int meta_dtype, uint64_t values_per_plane);
 int q4b_weight_upload_planes(q4b_context *context, const void *quants, const void *scales,
                              const void *biases, int meta_dtype, uint32_t rows,
                              uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
@@ -122,6 +130,15 @@ int q4b_embedding_lookup(q4b_context *context, const q4b_weight *embedding, cons
  * asynchronous on the context's stream.  The reference's epsilon is 1e-6. */
 int q4b_rmsnorm(q4b_context *context, const void *input, int input_dtype, const float *weight, void *output_f16,
                 uint32_t hidden, uint32_t batch_rows, float epsilon, char *error_message, size_t error_capacity);
+/* The affine-Q8 sibling (minimax_h3_q8_gemm_bf16_meta, minimax_h3_attention.metal:594-676; host
+ * minimax_h3_m3_run_q8_gemm_benchmark, minimax_h3_m3_gemm.m:387-): one code BYTE per weight, 64 per group
+ * (quants [rows][K] bytes), bf16 scales and biases [rows][K/64], w = half(float(scale) * q + float(bias)).
+ * The metadata stay bf16 on the device, as that kernel reads them.  A Q8 weight is served by q4b_matmul (and
+ * q4b_matmul_host) alone, on the tcgen05 GEMM at every M, with fp16 or fp32 activations; q4b_weight_unpack
+ * returns its codes and dequantised values; the other entry points refuse it with status 1. */
+int q4b_weight_upload_q8(q4b_context *context, const void *quants, const void *scales_bf16, const void *biases_bf16,
+                         uint32_t rows, uint32_t groups_per_row, uint32_t row_begin, uint32_t row_count,
+                         q4b_weight **weight, char *error_message, size_t error_capacity);
 /* Dequantisation in isolation (the job of qwen38_q4_embedding_lookup,
  * qwen38_global.metal:13-28) over the whole shard, written to HOST buffers, any
  * of which may be NULL: codes uint8 [rows][K], w32 float [rows][K] =
@@ -185,7 +202,7 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
  * cudaMalloc and cudaFree cause) would stall other streams mid-token, or that
  * must give the same latency on the first token as on the thousandth.  This
  * variant runs the same kernel with its scratch in an array that is part of the
- * library image itself: 2 MiB of partial sums plus 4096 arrival counters, held
+ * library image itself: 1 MiB of partial sums plus 4096 arrival counters, held
  * by every GPU that loads the library until the process exits.  It calls no
  * cudaMalloc, cudaFree or other allocating routine.
  *
@@ -195,10 +212,10 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
  *     uses the scratch at all; larger matrices (the 248,320-row lm_head among
  *     them) need none and are served as they are.  A split matrix needs at most
  *     2 KB (M <= 4), 4 KB (M <= 8) or 8 KB (M <= 16) per resident thread block:
- *     everything up to M = 8 fits on a B200 (at most 1.2 MB); at M = 9..16 a
- *     matrix cut into more than 256 pieces (17408 -> 5120 is cut into 280) needs
- *     up to 2.4 MB and is refused with status 1 and a message that states both
- *     sizes: use q4b_matmul for it;
+ *     everything at M <= 4 -- decode and the verify step -- fits on a B200 (at
+ *     most 0.6 MB); at M = 5..16 a matrix cut into more than 256 (M <= 8) or 128
+ *     pieces (17408 -> 5120 is cut into 280 at M <= 8) is refused with status 1
+ *     and a message that states both sizes: use q4b_matmul for it;
  *   - no residual input; otherwise the arguments of q4b_matmul;
  *   - the first call on a device looks the array's device address up (once per
  *     device); make that first call before any stream capture begins;
@@ -308,6 +325,15 @@ void *q4b_sequence_done_counters(q4b_sequence *sequence);
 int q4b_sequence_set_peer_counters(q4b_sequence *sequence, uint32_t peer_rank, void *peer_counters);
 int q4b_sequence_launch(q4b_context *context, q4b_sequence *sequence,
                         char *error_message, size_t error_capacity);
+/* Where a sequence's time goes (the role of QWEN38_PROFILE, qwen38_m3_decode.m:1217-1283, which splits the
+ * command buffer by region).  The first call switches the clocks on (one allocation); every later call waits
+ * for the stream, copies out what the launches since the last call added up and clears it.  clocks receives,
+ * per resident thread block, six sums of SM clock ticks as one of its consumer warps saw them: waiting for the
+ * previous job's outputs; turning activations into tensor-pipe operands; waiting for weights to arrive from
+ * HBM; multiplying; finishing units (split sums, epilogue, publishing); and the whole launch.  capacity is in
+ * values (thread_blocks x 6 are needed; *thread_blocks is always set).  Synchronous; not while recording. */
+int q4b_sequence_profile(q4b_context *context, q4b_sequence *sequence, uint64_t *clocks, uint32_t capacity,
+                         uint32_t *thread_blocks, char *error_message, size_t error_capacity);
 void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence);
 
 /* ---- column-parallel ranks at M > 16 (prefill): the tensor-core GEMM stores a

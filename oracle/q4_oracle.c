@@ -495,3 +495,74 @@ void q4o_matmul_bf16(const uint8_t *quants, const uint16_t *scales_bf16,
         }
     }
 }
+
+/* RMS norm in front of the matmuls: the reference's CPU checks cpu_rms_half and cpu_rms_float
+ * (models/qwen3.8-27b/targets/apple-m3-pro/qwen38_m3_layer.m:395-420): the sum of squares in double over the
+ * row in index order, inv = 1 / sqrtf((float)(sum / hidden) + epsilon) in float, out = half(x * inv * weight)
+ * with both products in float, for every row of [batch][hidden].  input_dtype 0 = fp16, 1 = fp32. */
+void q4o_rms_norm(const void *input, int input_dtype, const float *weight,
+                  uint16_t *output, size_t hidden, size_t batch, float epsilon) {
+    for (size_t row = 0; row < batch; ++row) {
+        double squared = 0.0;
+        for (size_t index = 0; index < hidden; ++index) {
+            float value = load_value(input, input_dtype, row * hidden + index);
+            squared += (double)value * value;
+        }
+        float inv = 1.0f / sqrtf((float)(squared / (double)hidden) + epsilon);
+        for (size_t index = 0; index < hidden; ++index) {
+            float value = load_value(input, input_dtype, row * hidden + index);
+            output[row * hidden + index] = q4o_f32_to_f16(value * inv * weight[index]);
+        }
+    }
+}
+
+/* Affine Q8 (minimax_h3_q8_gemm_bf16_meta, models/minimax-h3/targets/apple-m3-pro/minimax_h3_attention.metal:
+ * 594-676): quants [rows][groups][64] code bytes, bf16 scales and biases [rows][groups];
+ * weight_tile = half(scale * float(code) + bias) with scale and bias widened to float (:625-633).  The
+ * reference has no CPU check of this kernel (its benchmark runs on zero-filled buffers,
+ * minimax_h3_m3_gemm.m:464-468), so this restatement of the kernel's own formula is all there is. */
+float q4o_q8_w32(uint8_t code, uint16_t scale_bf16, uint16_t bias_bf16) {
+    float scale = q4o_bf16_to_f32(scale_bf16), bias = q4o_bf16_to_f32(bias_bf16);
+    return scale * (float)code + bias;
+}
+
+void q4o_dequant_q8(const uint8_t *quants, const uint16_t *scales_bf16, const uint16_t *biases_bf16,
+                    size_t rows, size_t groups, float *w32, uint16_t *w16) {
+    for (size_t block = 0; block < rows * groups; ++block) {
+        for (size_t k = 0; k < 64; ++k) {
+            float value = q4o_q8_w32(quants[block * 64 + k], scales_bf16[block], biases_bf16[block]);
+            if (w32 != NULL) w32[block * 64 + k] = value;
+            if (w16 != NULL) w16[block * 64 + k] = q4o_f32_to_f16(value);
+        }
+    }
+}
+
+/* y[m][n] = sum_k half(w(n, k)) * x[m][k] for rows row_begin .. row_begin + row_count - 1: the half-rounded
+ * weights the kernel multiplies, summed in float (y32) and in double (y64) in column order; x fp16 or fp32. */
+void q4o_matmul_q8(const uint8_t *quants, const uint16_t *scales_bf16, const uint16_t *biases_bf16,
+                   size_t groups, size_t row_begin, size_t row_count, const void *x, int x_dtype,
+                   size_t m_rows, float *y32, double *y64, size_t ldy, int threads) {
+    size_t columns = groups * 64;
+    if (threads <= 0) threads = q4o_max_threads();
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (long long local = 0; local < (long long)row_count; ++local) {
+        size_t row = row_begin + (size_t)local;
+        for (size_t m = 0; m < m_rows; ++m) {
+            float sum32 = 0.0f;
+            double sum64 = 0.0;
+            for (size_t g = 0; g < groups; ++g) {
+                size_t block = row * groups + g;
+                for (size_t k = 0; k < 64; ++k) {
+                    float weight = q4o_f16_to_f32(q4o_f32_to_f16(
+                        q4o_q8_w32(quants[block * 64 + k], scales_bf16[block], biases_bf16[block])));
+                    float value = load_value(x, x_dtype, m * columns + g * 64 + k);
+                    sum32 += weight * value;
+                    sum64 += (double)weight * (double)value;
+                }
+            }
+            if (y32 != NULL) y32[m * ldy + (size_t)local] = sum32;
+            if (y64 != NULL) y64[m * ldy + (size_t)local] = sum64;
+        }
+    }
+}
+

@@ -93,6 +93,15 @@ void q4o_matmul_bf16(const uint8_t *quants, const uint16_t *scales_bf16,
                      size_t ldy, int threads);
 
 void q4o_round_f16(const float *in, uint16_t *out, size_t count);
+/* affine Q8 (minimax_h3_attention.metal:594-676): code bytes [rows][groups][64], bf16 scales / biases */
+void q4o_dequant_q8(const uint8_t *quants, const uint16_t *scales_bf16, const uint16_t *biases_bf16,
+                    size_t rows, size_t groups, float *w32, uint16_t *w16);
+void q4o_matmul_q8(const uint8_t *quants, const uint16_t *scales_bf16, const uint16_t *biases_bf16,
+                   size_t groups, size_t row_begin, size_t row_count, const void *x, int x_dtype,
+                   size_t m_rows, float *y32, double *y64, size_t ldy, int threads);
+/* cpu_rms_half / cpu_rms_float (qwen38_m3_layer.m:395-420) over [batch][hidden]; input_dtype 0 = fp16, 1 = fp32 */
+void q4o_rms_norm(const void *input, int input_dtype, const float *weight,
+                  uint16_t *output, size_t hidden, size_t batch, float epsilon);
 int q4o_max_threads(void);
 
 #ifdef __cplusplus

@@ -96,6 +96,11 @@ def lib() -> ctypes.CDLL:
             _u8p, _u16p, _u16p, _c_size, _c_size, _c_size, _u16p, _c_size,
             _f32p, _c_size, ctypes.c_int]
         handle.q4o_round_f16.argtypes = [_f32p, _u16p, _c_size]
+        handle.q4o_dequant_q8.argtypes = [_u8p, _u16p, _u16p, _c_size, _c_size, _f32p, _u16p]
+        handle.q4o_matmul_q8.argtypes = [_u8p, _u16p, _u16p, _c_size, _c_size, _c_size, ctypes.c_void_p, ctypes.c_int,
+                                         _c_size, _f32p, _f64p, _c_size, ctypes.c_int]
+        handle.q4o_rms_norm.argtypes = [ctypes.c_void_p, ctypes.c_int, _f32p, _u16p, _c_size, _c_size,
+                                        ctypes.c_float]
         _lib = handle
     return _lib
 
@@ -305,6 +310,21 @@ def rmsnorm(values: np.ndarray, weight: np.ndarray, epsilon: float = 1e-6) -> np
     return ((x * inv_rms[:, None]) * w[None, :]).astype(np.float16)
 
 
+def rmsnorm_reference(values: np.ndarray, weight: np.ndarray, epsilon: float = 1e-6) -> np.ndarray:
+    """The reference's own CPU check of the RMS norm, cpu_rms_half / cpu_rms_float
+    (qwen38_m3_layer.m:395-420), restated in C (q4o_rms_norm): double sum of squares, float
+    inverse, half(x * inv * weight).  The Metal kernel sums in float in another order, so the two agree
+    to an fp16 ulp, not bit for bit; `rmsnorm` above follows the kernel's order."""
+    x = np.ascontiguousarray(values)
+    assert x.dtype in (np.float16, np.float32)
+    batch, hidden = x.shape
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    out = np.empty((batch, hidden), dtype=np.uint16)
+    lib().q4o_rms_norm(x.ctypes.data, 0 if x.dtype == np.float16 else 1, _ptr(w, _f32p), _ptr(out.reshape(-1), _u16p),
+                       hidden, batch, epsilon)
+    return out.view(np.float16)
+
+
 def round_bf16(values: np.ndarray) -> np.ndarray:
     """float32 -> bf16 bits, round to nearest even: bfloat_bits of the H3 CPU check
     (benchmarks/minimax_h3_m3_real_gemm.c:18-23).  Finite inputs only."""
@@ -328,6 +348,44 @@ def dequant_wbf16(quants, scales_bf16, biases_bf16, rows, groups) -> np.ndarray:
     bias = bf16_to_f32(np.asarray(biases_bf16).reshape(rows, groups, 1))
     product = scale * codes                   # float32, exact
     return round_bf16(product + bias).reshape(rows, groups * 64)
+
+
+def synth_q8(seed: int, rows: int, groups: int):
+    """Seeded affine-Q8 planes in the layout of minimax_h3_q8_gemm_bf16_meta: codes uint8 [rows, groups * 64]
+    uniform in 0..255, bf16 scales uniform in [3e-5, 2.5e-4] and biases -128 * scale + N(0, 1e-3), so that the
+    weights cover the same range as the Q4 distributions."""
+    rng = np.random.default_rng(seed)
+    quants = rng.integers(0, 256, size=(rows, groups * 64), dtype=np.uint8)
+    scale = rng.uniform(3e-5, 2.5e-4, size=(rows, groups)).astype(np.float32)
+    scales = round_bf16(scale)
+    biases = round_bf16(-128.0 * bf16_to_f32(scales) + rng.standard_normal((rows, groups)).astype(np.float32) * 1e-3)
+    return quants, scales, biases
+
+
+def dequant_q8(quants, scales_bf16, biases_bf16, rows, groups):
+    """(w32, w16) of the Q8 contract half(float(scale) * q + float(bias)); w16 as float16."""
+    q = _flat(quants, np.uint8)
+    s, b = _flat(scales_bf16, np.uint16), _flat(biases_bf16, np.uint16)
+    w32 = np.empty(rows * groups * 64, dtype=np.float32)
+    w16 = np.empty(rows * groups * 64, dtype=np.uint16)
+    lib().q4o_dequant_q8(_ptr(q, _u8p), _ptr(s, _u16p), _ptr(b, _u16p), rows, groups, _ptr(w32, _f32p),
+                         _ptr(w16, _u16p))
+    return w32.reshape(rows, groups * 64), w16.view(np.float16).reshape(rows, groups * 64)
+
+
+def matmul_q8(quants, scales_bf16, biases_bf16, groups, x, row_begin=0, row_count=None, threads=0):
+    """[M, row_count] double sums of half(w) * x for the affine-Q8 matrix."""
+    q = _flat(quants, np.uint8)
+    s, b = _flat(scales_bf16, np.uint16), _flat(biases_bf16, np.uint16)
+    rows_total = q.size // (groups * 64)
+    if row_count is None:
+        row_count = rows_total - row_begin
+    x = np.ascontiguousarray(x)
+    m_rows = x.shape[0]
+    y64 = np.empty((m_rows, row_count), dtype=np.float64)
+    lib().q4o_matmul_q8(_ptr(q, _u8p), _ptr(s, _u16p), _ptr(b, _u16p), groups, row_begin, row_count,
+                        x.ctypes.data, _dtype_code(x), m_rows, None, _ptr(y64, _f64p), row_count, threads)
+    return y64
 
 
 def round_f16(values: np.ndarray) -> np.ndarray:

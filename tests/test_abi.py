@@ -3,6 +3,7 @@ declares, and refuses to work without a GPU instead of falling back."""
 import ctypes
 import os
 
+import numpy as np
 import pytest
 
 
@@ -60,3 +61,15 @@ def test_algorithmic_bytes_match_the_stated_anchors(q4b):
     single = q4b.Projection("config0", 1024, 3072)
     assert q4b.shapes.weight_bytes(single) == 1_769_472
     assert q4b.layer_flops(q4b.LAYER_27B, 1) == 681_574_400
+
+
+def test_bf16_planes_that_do_not_fit_fp16_are_counted(q4b):
+    """q4b_planes_narrowed: every bf16 value in fp16's normal range is an fp16 number; the others change."""
+    lib = q4b.library()
+    def bf16(values):
+        return (np.asarray(values, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    inside = bf16([1.0, -0.00390625, 6.103515625e-05, 65280.0, 0.0, -2.0 ** -14])
+    outside = bf16([1.0e-6, 1.0e5, -3.0e38, 2.0 ** -26])
+    assert lib.q4b_planes_narrowed(inside.ctypes.data, inside.ctypes.data, q4b.BF16, inside.size) == 0
+    assert lib.q4b_planes_narrowed(outside.ctypes.data, inside.ctypes.data, q4b.BF16, 4) == 4
+    assert lib.q4b_planes_narrowed(outside.ctypes.data, outside.ctypes.data, q4b.F16, 4) == 0

@@ -175,3 +175,32 @@ def test_gemm_fused_gate_up_full_width(q4b, orc, ctx, m):
     assert error <= 2e-3, f"fused gate/up M={m}: {error:.3e}"
     gate.free()
     up.free()
+
+
+@pytest.mark.parametrize("m", [4646, 15485])
+def test_h3_large_m_witness(q4b, orc, ctx, m):
+    """The reference's largest affine-Q4 GEMM: 5376 -> 14336 at M = 15,485 rows and its 4,646-row sample
+    (minimax_h3_m3_gemm.m:75-104 arithmetic fixture; models/minimax-h3/targets/apple-m3-pro/README.md:722-726),
+    fp16 in and out.  Checked like the reference checks itself -- the first 8 outputs against a scalar fp32 sum,
+    its bound 0.002581 -- and on sampled weight rows x sampled activation rows against the double sum."""
+    n, k = 14336, 5376
+    groups = k // 64
+    quants, meta, x = orc.h3_pattern(n, groups, m * k, 17)
+    x = x.reshape(m, k)
+    weight = ctx.upload(quants, meta, n, groups)
+    dx, dy = ctx.to_device(x), ctx.alloc(m * n * 2)
+    ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)
+    y = dy.download(np.float16, (m, n))
+    assert np.isfinite(y.astype(np.float32)).all()
+    ref32, _ = orc.matmul(quants, meta, groups, x[:1], row_count=8, want64=False)
+    assert np.max(np.abs(y[0, :8].astype(np.float32) - ref32[0])) <= 0.002581 + 2.0 ** -9  # + half an fp16 ulp of 2..4
+    rng = np.random.default_rng(m)
+    rows, acts = sampled(n, rng, 12), sampled(m, rng, 6)
+    cols = []
+    for row in rows:
+        cols.append(orc.matmul(quants, meta, groups, np.ascontiguousarray(x[acts]), row_begin=int(row), row_count=1,
+                               want32=False)[1])
+    ref = np.concatenate(cols, axis=1)
+    scale = float(np.max(np.abs(y.astype(np.float32))))
+    assert float(np.max(np.abs(y[np.ix_(acts, rows)].astype(np.float64) - ref))) / scale <= 2e-3
+    weight.free()

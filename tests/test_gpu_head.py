@@ -80,7 +80,7 @@ def test_row_range_of_a_weight_is_a_weight(q4b, orc, ctx, m):
         ctx.matmul(part, dx.ptr, q4b.F16, m, dy.ptr, q4b.F32)
         y = dy.download(np.float32, (m, count))
         assert_close(y, ref[:, begin:begin + count], f"rows [{begin}, +{count}) M={m}")
-        if m <= 16:  # the decode kernel gives a row the same bits wherever the range begins
+        if m <= 4:  # same split of K for the whole matrix and the range here: a row keeps its bits
             assert bits_equal(y, full[:, begin:begin + count])
         part.free()
     with pytest.raises(q4b.Q4Error):
