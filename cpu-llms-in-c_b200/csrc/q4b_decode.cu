@@ -109,6 +109,7 @@ struct PassParams {
     uint32_t m_rows;
     uint32_t world;
     uint32_t stages;                 // ring stages (2 or 3)
+    uint32_t cluster;                // single launch: the CTAs of one pair block are one thread-block cluster
     uint32_t *epoch;                 // sequence: launches completed so far (device word)
     uint32_t *exit_count;            // sequence: CTAs of this launch that have finished
     uint32_t *done;                  // sequence: [job][8] completion counters, kDoneStride words apart
@@ -161,6 +162,20 @@ __device__ inline void bulk_copy_to_shared(uint32_t destination, const void *sou
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(destination), "l"(source), "r"(bytes), "r"(bar)
                  : "memory");
+}
+// every thread of every CTA of the cluster, the same number of times
+__device__ inline void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// the address, in the cluster's shared window, of this CTA's shared address `local` inside CTA `rank`
+__device__ inline uint32_t cluster_address(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ inline void cluster_store(uint32_t address, float value) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
 }
 __device__ inline void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
@@ -559,6 +574,9 @@ decode_kernel(const __grid_constant__ PassParams p) {
     __syncthreads();
 
     const uint32_t job_count = SEQ ? p.job_count : 1u;
+    // One launch, K split over the CTAs of a cluster (CTA rank = part, one unit per CTA): the partial sums meet in
+    // the shared memory of the cluster's first CTA instead of global memory.  The same answer in every thread.
+    const bool clustered = !SEQ && p.cluster != 0 && p.job.parts > 1 && gridDim.x == p.job.units;
 
     if (warp == kProducerWarp) {
         // ---- weight producer: one thread streams every unit of every job, never draining the ring ----
@@ -609,6 +627,11 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     }
                 }
             }
+        }
+        __syncwarp();
+        if (clustered) {  // the two barriers of the consumers' split-K exchange count every thread of the cluster
+            cluster_barrier();
+            cluster_barrier();
         }
     } else {
         // ---- consumers: warp w owns tile w & 3 of block w >> 2 of every pair block this CTA visits ----
@@ -827,6 +850,32 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         }
                     }
                     finisher = fused ? k == 0 : active;
+                } else if (clustered) {
+                    // K is split over the CTAs of this cluster.  Once every CTA is through with its ring (first
+                    // barrier), each warp puts its sums into the first CTA's ring, part by part; after the
+                    // second barrier that CTA adds them in part order, the order of the path through global
+                    // memory below, so both give the same bits.
+                    cluster_barrier();
+                    if (active) {
+                        const uint32_t slot = cluster_address(ring0 + (((u.part * VALS) * 8 + warp) * 32 + lane) * 4u, 0u);
+#pragma unroll
+                        for (int v = 0; v < VALS; ++v) cluster_store(slot + (uint32_t)v * 8u * 32u * 4u, acc[v]);
+                    }
+                    cluster_barrier();
+                    finisher = u.part == 0 && (fused ? k == 0 : active);
+                    if (finisher) {
+                        const float *base = reinterpret_cast<const float *>(ring);
+                        const int gate_warp = fused ? r : warp;
+#pragma unroll
+                        for (int v = 0; v < VALS; ++v) acc[v] = 0.0f;
+                        for (uint32_t q = 0; q < job.parts; ++q) {
+#pragma unroll
+                            for (int v = 0; v < VALS; ++v) {
+                                acc[v] += base[((q * VALS + v) * 8 + gate_warp) * 32 + lane];
+                                if (fused) second[v] += base[((q * VALS + v) * 8 + gate_warp + 4) * 32 + lane];
+                            }
+                        }
+                    }
                 } else {
                     // K is split over CTAs: park the sums; the last warp to arrive for this tile adds every
                     // part's in part order (the same sum whoever is last)
@@ -996,6 +1045,41 @@ cudaError_t configure(size_t smem_bytes, int *blocks_per_sm) {
     return cudaSuccess;
 }
 
+// How many clusters of `parts` CTAs the device holds at once (0 when it cannot say): per instantiation, device,
+// cluster size and shared-memory size, asked once.
+template <int MODE>
+uint32_t resident_clusters(uint32_t parts, size_t smem_bytes) {
+    static int known[kMaxDevices][9];
+    static size_t asked[kMaxDevices][9];
+    static std::mutex guard;
+    const int slot = device_slot();
+    if (slot < 0 || parts < 2 || parts > 8) return 0;
+    std::lock_guard<std::mutex> lock(guard);
+    if (known[slot][parts] == 0 || asked[slot][parts] != smem_bytes) {
+        int unused = 0;
+        if (configure<MODE, false>(smem_bytes, &unused) != cudaSuccess) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(parts * 64);
+        config.blockDim = dim3(kDecodeThreads);
+        config.dynamicSmemBytes = smem_bytes;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = parts;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, decode_kernel<MODE, false>, &config) != cudaSuccess) {
+            cudaGetLastError();
+            clusters = -1;
+        }
+        known[slot][parts] = clusters > 0 ? clusters : -1;
+        asked[slot][parts] = smem_bytes;
+    }
+    return known[slot][parts] > 0 ? (uint32_t)known[slot][parts] : 0u;
+}
+
 cudaError_t configure_mode(int mode, bool sequence, size_t smem_bytes, int *per_sm) {
     if (sequence) {
         return mode == 0 ? configure<0, true>(smem_bytes, per_sm)
@@ -1048,11 +1132,24 @@ cudaError_t decode_static_scratch(float **scratch, uint32_t **counters, size_t *
 
 // variant encoding (0 = heuristics): bits 0-3 CTAs per SM (at most what fits), bit 4 the fp16 form also at
 // M <= 4 (default there: the integer form), bits 8-11 an upper limit on the K parts of a pair block,
-// bit 14 no programmatic dependent launch
+// bit 13 no thread-block clusters for a split K, bit 14 no programmatic dependent launch
 cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool sequence, DecodeGeometry *geometry) {
     if (m_rows == 0 || m_rows > decode_max_m()) return cudaErrorInvalidValue;
     geometry->mode = mode_of(m_rows, variant);
     geometry->smem_bytes = smem_of(geometry->mode, m_rows, &geometry->stages);
+    // The K split is planned around the clusters the device can hold of the integer form at M = 1 (asked once per
+    // device), so that every form, every M and a sequence split a projection alike; a launch then uses clusters
+    // when its own form's fit as well.
+    uint32_t stages_unused = 0;
+    const size_t plan_smem = smem_of(0, 1u, &stages_unused);
+    const size_t form_smem = smem_of(geometry->mode, geometry->mode == 0 ? 1u : m_rows, &stages_unused);
+    for (uint32_t k = 0; k <= 8; ++k) {
+        geometry->plan_room[k] = k < 2 ? 0u : resident_clusters<0>(k, plan_smem);
+        geometry->cluster_room[k] = k < 2                ? 0u
+                                    : geometry->mode == 0 ? geometry->plan_room[k]
+                                    : geometry->mode == 1 ? resident_clusters<1>(k, form_smem)
+                                                          : resident_clusters<2>(k, form_smem);
+    }
     int per_sm = 0;
     cudaError_t status = configure_mode(geometry->mode, sequence, geometry->smem_bytes, &per_sm);
     if (status != cudaSuccess) return status;
@@ -1087,6 +1184,14 @@ void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geom
         }
     }
     if (geometry.max_parts > 0 && parts > geometry.max_parts) parts = geometry.max_parts;
+    // 2..8 parts meet in the shared memory of a thread-block cluster when all the clusters fit on the device at
+    // once: rather one part fewer than a sum through global memory
+    while (parts >= 2 && parts <= 8 && geometry.plan_room[parts] < pairs) {
+        uint32_t fewer = parts - 1;
+        while (fewer >= 2 && geometry.plan_room[fewer] < pairs) --fewer;
+        if (fewer < 2) break;  // no cluster size fits: keep the split, summed through global memory
+        parts = fewer;
+    }
     job->parts = parts;
     job->units = pairs * parts;
     const size_t vals = geometry.mode == 0 ? 2 : geometry.mode == 1 ? 4 : 8;
@@ -1105,16 +1210,26 @@ cudaError_t launch_kernel(const PassParams &p, uint32_t ctas, size_t smem_bytes,
     config.blockDim = dim3(kDecodeThreads);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
+    cudaLaunchAttribute attribute[2];
+    config.numAttrs = 0;
     if (SEQ) {
         // the CTAs wait on one another: all of them must be resident
         attribute[0].id = cudaLaunchAttributeCooperative;
         attribute[0].val.cooperative = 1;
         config.numAttrs = 1;
     } else {
-        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attribute[0].val.programmaticStreamSerializationAllowed = 1;
-        config.numAttrs = dependent_launch ? 1 : 0;
+        if (dependent_launch) {
+            attribute[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attribute[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+            ++config.numAttrs;
+        }
+        if (p.cluster != 0) {
+            attribute[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
+            attribute[config.numAttrs].val.clusterDim.x = p.job.parts;
+            attribute[config.numAttrs].val.clusterDim.y = 1;
+            attribute[config.numAttrs].val.clusterDim.z = 1;
+            ++config.numAttrs;
+        }
     }
     config.attrs = attribute;
     return cudaLaunchKernelEx(&config, kernel, p);
@@ -1135,6 +1250,12 @@ cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeo
     p.status = status;
     const uint32_t ctas = job.units < geometry.ctas ? job.units : geometry.ctas;
     const bool pdl = ((variant >> 14) & 1) == 0;
+    // K split over 2..8 CTAs, every unit with a CTA of its own, and all the clusters resident at once: the parts of
+    // a pair block meet in shared memory
+    if (((variant >> 13) & 1) == 0 && job.parts >= 2 && job.parts <= 8 && ctas == job.units &&
+        geometry.cluster_room[job.parts] * job.parts >= job.units) {
+        p.cluster = 1;
+    }
     switch (geometry.mode) {
         case 0: return launch_kernel<0, false>(p, ctas, geometry.smem_bytes, pdl, stream);
         case 1: return launch_kernel<1, false>(p, ctas, geometry.smem_bytes, pdl, stream);

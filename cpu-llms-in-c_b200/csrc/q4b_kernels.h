@@ -82,6 +82,8 @@ struct DecodeGeometry {
     uint32_t max_parts;  // 0: no limit on the K parts of a pair block
     uint32_t stages;     // stages of the weight ring (3 when two CTAs then still share an SM, else 2)
     size_t smem_bytes;
+    uint32_t cluster_room[9];  // [k]: clusters of k CTAs of this form the device holds at once (k = 2..8; 0 = none)
+    uint32_t plan_room[9];     // the same for the integer form at M = 1: what the K split is planned around
 };
 struct SequenceLaunch {
     const DecodeJob *jobs;     // device

@@ -214,8 +214,9 @@ int q4b_matmul(q4b_context *context, const q4b_weight *weight, const void *x, in
  *     2 KB (M <= 4), 4 KB (M <= 8) or 8 KB (M <= 16) per resident thread block:
  *     everything at M <= 4 -- decode and the verify step -- fits on a B200 (at
  *     most 0.6 MB); at M = 5..16 a matrix cut into more than 256 (M <= 8) or 128
- *     pieces (17408 -> 5120 is cut into 280 at M <= 8) is refused with status 1
- *     and a message that states both sizes: use q4b_matmul for it;
+ *     pieces (17408 -> 5120 is cut into 240 or 280, which M = 16 cannot park) is
+ *     refused with status 1 and a message that states both sizes: use q4b_matmul
+ *     for it;
  *   - no residual input; otherwise the arguments of q4b_matmul;
  *   - the first call on a device looks the array's device address up (once per
  *     device); make that first call before any stream capture begins;

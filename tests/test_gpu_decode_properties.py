@@ -8,6 +8,8 @@
   fp16's range.
 * Non-finite activations give non-finite outputs in the row they sit in and leave the other rows alone.
 * A sequence launch recorded into a graph replays correctly (the launch count lives in device memory).
+* A K split whose parts meet in a cluster's shared memory gives the bits of the same split summed through
+  global memory (variant bit 13), for every arithmetic form, plain and fused.
 """
 import numpy as np
 import pytest
@@ -59,6 +61,34 @@ def test_row_result_does_not_depend_on_batch(q4b, orc, ctx, n, k, fused):
             for index, r in enumerate((0, 3, 7, 15)):
                 if r < m:
                     assert bits_equal(batch[r], single[index][0]), f"fp16 form M={m} row {r}"
+    finally:
+        ctx.set_variant(0)
+        weight.free()
+        if up is not None:
+            up.free()
+
+
+@pytest.mark.parametrize("n,k,fused", [(5120, 6144, False), (5120, 17408, False), (1024, 5120, False),
+                                       (3072, 1024, True), (200, 2048, False), (640, 6144, False)])
+def test_cluster_sum_equals_global_memory_sum(q4b, orc, ctx, n, k, fused):
+    groups = k // 64
+    weight = ctx.synth_weight(17, 0, n, groups)
+    up = ctx.synth_weight(17, 1, n, groups) if fused else None
+    x = orc.synth_x(17, 0, 16, k)
+    try:
+        for m, form in ((1, 0), (3, 0), (4, 0x10), (8, 0), (16, 0)):
+            got = {}
+            for clusters_off in (0, 0x2000):
+                ctx.set_variant(form | clusters_off)
+                got[clusters_off] = run(q4b, ctx, weight, x[:m], q4b.F32, up)
+                again = run(q4b, ctx, weight, x[:m], q4b.F32, up)
+                assert bits_equal(got[clusters_off], again), f"M={m} variant {form | clusters_off:#x} repeats"
+            assert bits_equal(got[0], got[0x2000]), f"M={m} form {form:#x}"
+        quants, meta = orc.synth_weight(17, 0, n, groups)
+        if not fused:
+            _, ref = orc.matmul(quants, meta, groups, x[:4], want32=False)
+            ctx.set_variant(0)
+            assert_close(run(q4b, ctx, weight, x[:4], q4b.F32), ref, "cluster sum against the oracle")
     finally:
         ctx.set_variant(0)
         weight.free()

@@ -40,9 +40,9 @@ def test_no_alloc_entry_point_matches_matmul_twice_in_a_row(q4b, orc):
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit(q4b, orc):
     with q4b.Q4Context(0) as ctx:
-        # 17408 -> 5120 has 40 blocks of 128 rows, so its K range is cut into 7 parts per block: 280 pieces.
-        # At M = 8 a piece parks 4 KB of sums: 1.1 MB, more than the 1 MiB the library carries.
-        n, k, m = 5120, 17408, 8
+        # 17408 -> 5120 has 40 blocks of 128 rows, so its K range is cut into 6 or 7 parts per block: 240 or 280
+        # pieces.  At M = 16 a piece parks 8 KB of sums: 1.9 MB or more, beyond the 1 MiB the library carries.
+        n, k, m = 5120, 17408, 16
         weight = ctx.synth_weight(0, 0, n, k // 64)
         dx = ctx.synth_x(0, 0, m, k)
         dy = ctx.alloc(m * n * 2)
