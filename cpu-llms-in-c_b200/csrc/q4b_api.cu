@@ -1191,6 +1191,40 @@ int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm
     return Q4B_OK;
 }
 
+int q4b_probe_signal(q4b_context *context, void *own_words, void *peer_words, uint32_t payload_bytes,
+                     uint32_t rounds, uint32_t rounds_before, int initiator, double *microseconds_per_round_trip,
+                     char *error_message, size_t error_capacity) {
+    int code = check_context(context, error_message, error_capacity);
+    if (code != Q4B_OK) return code;
+    if (own_words == nullptr || peer_words == nullptr || microseconds_per_round_trip == nullptr || rounds == 0 ||
+        payload_bytes > (1u << 20) || payload_bytes % 4 != 0 || context->capturing) {
+        set_error(error_message, error_capacity, "invalid signal probe arguments");
+        return Q4B_BAD_ARGUMENT;
+    }
+    // word 0: the flag; word 1: the status; the payload from byte 256 on
+    uint32_t *own = static_cast<uint32_t *>(own_words), *peer = static_cast<uint32_t *>(peer_words);
+    cudaError_t status = cudaMemsetAsync(own + 1, 0, 4, context->stream);
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_start, context->stream);
+    if (status == cudaSuccess) {
+        status = launch_probe_signal(own, peer, peer + 64, payload_bytes / 4, rounds, rounds_before, initiator, own + 1,
+                                     context->stream);
+    }
+    context->launches += 1;
+    if (status == cudaSuccess) status = cudaEventRecord(context->timer_stop, context->stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(context->stream);
+    float ms = 0.0f;
+    if (status == cudaSuccess) status = cudaEventElapsedTime(&ms, context->timer_start, context->timer_stop);
+    uint32_t gave_up = 0;
+    if (status == cudaSuccess) status = cudaMemcpy(&gave_up, own + 1, 4, cudaMemcpyDeviceToHost);
+    if (status != cudaSuccess) return device_failure(error_message, error_capacity, "signal probe", status);
+    if (gave_up != 0) {
+        set_error(error_message, error_capacity, "the peer did not answer in round %u", gave_up);
+        return Q4B_DEVICE_FAILURE;
+    }
+    *microseconds_per_round_trip = (double)ms * 1e3 / rounds;
+    return Q4B_OK;
+}
+
 /* ---------------------------------------------------------------- sequences */
 int q4b_sequence_create(q4b_context *context, uint32_t m_rows, uint32_t world, uint32_t rank,
                         q4b_sequence **sequence, char *error_message, size_t error_capacity) {

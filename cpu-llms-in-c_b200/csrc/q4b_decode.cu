@@ -110,6 +110,7 @@ struct PassParams {
     uint32_t world;
     uint32_t stages;                 // ring stages (2 or 3)
     uint32_t cluster;                // single launch: the CTAs of one pair block are one thread-block cluster
+    uint32_t throttle;               // single launch: hold the last stage of the first ring fill back
     uint32_t *epoch;                 // sequence: launches completed so far (device word)
     uint32_t *exit_count;            // sequence: CTAs of this launch that have finished
     uint32_t *done;                  // sequence: [job][8] completion counters, kDoneStride words apart
@@ -144,12 +145,28 @@ __device__ inline bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait.  Once any wait of the CTA has expired (*failed != 0) nobody waits any more.
+// the same, asking the hardware to keep the warp suspended for up to about `nanoseconds` while the phase is open
+__device__ inline bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t nanoseconds) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(nanoseconds)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait.  Once any wait of the CTA has expired (*failed != 0) nobody waits any more.  A waiting warp sleeps
+// inside try_wait and looks at the failure word and the clock only every sixteenth time it wakes: a spinning warp
+// takes issue slots from the warps that multiply.
 __device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *failed, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*failed != 0) return false;
     const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    uint32_t woken = 0;
+    while (!mbar_try_wait_for(bar, parity, 4000u)) {
+        if ((++woken & 15u) != 0) continue;
         if (*failed != 0) return false;
         if (clock64() - start > kWaitLimitCycles) {
             *failed = code;
@@ -158,9 +175,16 @@ __device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_
     }
     return true;
 }
-__device__ inline void bulk_copy_to_shared(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(destination), "l"(source), "r"(bytes), "r"(bar)
+// weights are read once per pass: they leave L2 first, the activations and partial sums that are read again stay
+__device__ inline uint64_t stream_once_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ inline void bulk_copy_to_shared(uint32_t destination, const void *source, uint32_t bytes, uint32_t bar,
+                                           uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(destination), "l"(source), "r"(bytes), "r"(bar), "l"(policy)
                  : "memory");
 }
 // every thread of every CTA of the cluster, the same number of times
@@ -462,14 +486,15 @@ __device__ inline void fetch_held(const DecodeJob &job, uint32_t m_rows, size_t 
 // a consumer warp's work on one tile of one group
 // ---------------------------------------------------------------------------
 // Integer form: lane (gid, t) accumulates rows gid (acc[0]) and gid + 8 (acc[1]) of activation row t.
-__device__ inline void tile_digits(const uint8_t *tile, const uint8_t *entry, uint32_t m_rows, int lane, float acc[2]) {
-    const int gid = lane >> 2, t = lane & 3;
+__device__ inline void tile_digits(const uint8_t *tile, const uint8_t *entry, uint32_t digits_at, uint32_t steps_at,
+                                   int lane, float acc[2]) {
+    const int gid = lane >> 2;
     const uint4 codes = *reinterpret_cast<const uint4 *>(tile + piece_index(lane) * 16);
     const uint2 meta = *reinterpret_cast<const uint2 *>(tile + kTileCodeBytes + gid * 8);
-    uint4 b = make_uint4(0u, 0u, 0u, 0u);
-    if ((uint32_t)lane < 8 * m_rows) b = *reinterpret_cast<const uint4 *>(entry + lane * 16);
-    float2 ss = make_float2(0.0f, 0.0f);
-    if ((uint32_t)t < m_rows) ss = *reinterpret_cast<const float2 *>(entry + 128 * m_rows + t * 8);
+    // B columns beyond the activation rows there are read some valid lane's digits and steps instead of zeros
+    // (digits_at, steps_at): their sums land in accumulators nobody stores, and the loads need no predicate
+    const uint4 b = *reinterpret_cast<const uint4 *>(entry + digits_at);
+    const float2 ss = *reinterpret_cast<const float2 *>(entry + steps_at);
     // Word i covers columns 4i .. 4i+3 of this lane's 16; its even nibbles are row gid, its odd nibbles row gid + 8.
     // Row gid gets the masked nibbles.  Row gid + 8 gets the RAW bytes, 16 * (its code) + (row gid's code): its
     // integer sum is then 16 * (the wanted sum) + (row gid's sum), and one subtraction after the MMAs replaces
@@ -582,6 +607,8 @@ decode_kernel(const __grid_constant__ PassParams p) {
         // ---- weight producer: one thread streams every unit of every job, never draining the ring ----
         if (lane == 0) {
             uint32_t it = 0, issued = 0;
+            const uint64_t policy = stream_once_policy();
+            const bool throttle = p.throttle != 0;
             for (uint32_t j = 0; j < job_count; ++j) {
                 const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
                 if (SEQ) {
@@ -605,13 +632,18 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
                         const uint32_t s = it % stages;
                         if (it >= stages) mbar_wait(empty0 + 8 * s, ((it / stages) - 1) & 1, failed, 0x91u);
+                        // A single launch starts before the launch it depends on has finished, and the ring would
+                        // fill while the consumers wait for their activations; then their first loads queue behind
+                        // a whole ring of weight requests.  The last stage of the first fill waits for the first
+                        // entries instead.
+                        if (!SEQ && throttle && it == stages - 1) mbar_wait(xfull0, 0, failed, 0x96u);
                         if (*failed != 0) continue;  // no new copies once a wait has expired
                         const uint32_t bytes = min(kStageGroups, u.g1 - g) * kUnitBytes;
                         mbar_expect_tx(full0 + 8 * s, u.has_b ? 2 * bytes : bytes);
-                        bulk_copy_to_shared(ring0 + s * kStageBytes, a + (size_t)g * kUnitBytes, bytes, full0 + 8 * s);
+                        bulk_copy_to_shared(ring0 + s * kStageBytes, a + (size_t)g * kUnitBytes, bytes, full0 + 8 * s, policy);
                         if (u.has_b) {
                             bulk_copy_to_shared(ring0 + s * kStageBytes + kStageGroups * kUnitBytes,
-                                                b + (size_t)g * kUnitBytes, bytes, full0 + 8 * s);
+                                                b + (size_t)g * kUnitBytes, bytes, full0 + 8 * s, policy);
                         }
                         issued = it + 1;
                     }
@@ -663,6 +695,9 @@ decode_kernel(const __grid_constant__ PassParams p) {
         const uint32_t shift = MODE != 0 ? 2u : m_rows == 1 ? 0u : m_rows == 2 ? 1u : 2u;
         const uint32_t per_pass = 4u >> shift;
         const uint8_t *lane_tiles = ring + (size_t)k * kStageGroups * kUnitBytes + r * kTileBytes;
+        // integer form: where this lane reads its B registers and its row's steps inside an entry
+        const uint32_t digits_at = ((uint32_t)lane < 8 * m_rows ? (uint32_t)lane : (uint32_t)lane & 7u) * 16u;
+        const uint32_t steps_at = 128u * m_rows + min((uint32_t)t, m_rows - 1) * 8u;
         for (uint32_t j = 0; j < job_count; ++j) {
             const DecodeJob &job = SEQ ? p.jobs[j] : p.job;
             const bool fused = job.fused != 0;
@@ -797,7 +832,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
 #pragma unroll
                             for (uint32_t q = 0; q < kStageGroups; ++q) {
                                 if (MODE == 0) {
-                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, m_rows, lane, acc);
+                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, digits_at, steps_at, lane, acc);
                                 } else {
                                     tile_f16<NT>(tiles + q * kUnitBytes, set + q * entry_bytes, lane, acc);
                                 }
@@ -805,7 +840,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         } else {
                             for (uint32_t q = 0; q < in_stage; ++q) {
                                 if (MODE == 0) {
-                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, m_rows, lane, acc);
+                                    tile_digits(tiles + q * kUnitBytes, set + q * entry_bytes, digits_at, steps_at, lane, acc);
                                 } else {
                                     tile_f16<NT>(tiles + q * kUnitBytes, set + q * entry_bytes, lane, acc);
                                 }
@@ -1132,7 +1167,8 @@ cudaError_t decode_static_scratch(float **scratch, uint32_t **counters, size_t *
 
 // variant encoding (0 = heuristics): bits 0-3 CTAs per SM (at most what fits), bit 4 the fp16 form also at
 // M <= 4 (default there: the integer form), bits 8-11 an upper limit on the K parts of a pair block,
-// bit 13 no thread-block clusters for a split K, bit 14 no programmatic dependent launch
+// bit 13 no thread-block clusters for a split K, bit 14 no programmatic dependent launch, bit 16 the first ring
+// fill of a single launch is not held back
 cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool sequence, DecodeGeometry *geometry) {
     if (m_rows == 0 || m_rows > decode_max_m()) return cudaErrorInvalidValue;
     geometry->mode = mode_of(m_rows, variant);
@@ -1250,6 +1286,7 @@ cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeo
     p.status = status;
     const uint32_t ctas = job.units < geometry.ctas ? job.units : geometry.ctas;
     const bool pdl = ((variant >> 14) & 1) == 0;
+    p.throttle = ((variant >> 16) & 1) == 0 ? 1u : 0u;
     // K split over 2..8 CTAs, every unit with a CTA of its own, and all the clusters resident at once: the parts of
     // a pair block meet in shared memory
     if (((variant >> 13) & 1) == 0 && job.parts >= 2 && job.parts <= 8 && ctas == job.units &&

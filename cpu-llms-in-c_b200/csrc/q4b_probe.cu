@@ -2,7 +2,8 @@
 // models/qwen3.8-27b/targets/jetson-orin/qwen38_jetson_memory_probe.cu:25-35):
 // what this GPU delivers to a kernel that only reads, (0) with plain 16-byte
 // loads, and (1, 2) with the producer/consumer bulk-copy ring of the GEMV kernel,
-// without (1) or with (2) the consumers reading the staged bytes.
+// without (1) or with (2) the consumers reading the staged bytes.  And a ping-pong between two GPUs: what one
+// publish-and-wait of the column-parallel decode sequence costs over NVLink.
 #include "q4b_kernels.h"
 
 namespace q4b {
@@ -92,6 +93,53 @@ __global__ void __launch_bounds__(288) probe_ring_kernel(const uint8_t *data, si
 }
 
 }  // namespace
+
+// One side of a ping-pong between two GPUs, the exchange the column-parallel decode sequence makes after every job:
+// `payload_words` plain stores into the peer's memory, a system-scope fence, one addition to the peer's flag; then
+// a wait for the own flag to reach the same round.  The initiator sends first, the responder answers.  Every wait
+// is bounded; *status receives the round at which a wait gave up (0: none did).
+__global__ void __launch_bounds__(32) probe_signal_kernel(uint32_t *own_flag, uint32_t *peer_flag, uint32_t *peer_payload,
+                                                          uint32_t payload_words, uint32_t rounds, uint32_t base,
+                                                          int initiator, uint32_t *status) {
+    const uint32_t lane = threadIdx.x;
+    bool alive = true;
+    for (uint32_t round = 1; round <= rounds && alive; ++round) {
+        for (int turn = 0; turn < 2; ++turn) {
+            const bool sending = (turn == 0) == (initiator != 0);
+            if (sending) {
+                for (uint32_t w = lane; w < payload_words; w += 32) peer_payload[w] = round;
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(peer_flag), "r"(1u) : "memory");
+                }
+            } else {
+                uint32_t seen = 0;
+                const long long start = clock64();
+                for (;;) {
+                    if (lane == 0) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own_flag) : "memory");
+                    seen = __shfl_sync(0xffffffffu, seen, 0);
+                    if ((int32_t)(seen - (base + round)) >= 0) break;
+                    if (clock64() - start > 2000000000ll) {  // about a second: the peer is not there
+                        alive = false;
+                        break;
+                    }
+                }
+                if (!alive) {
+                    if (lane == 0) *status = round;
+                    break;
+                }
+            }
+        }
+    }
+}
+
+cudaError_t launch_probe_signal(uint32_t *own_flag, uint32_t *peer_flag, uint32_t *peer_payload, uint32_t payload_words,
+                                uint32_t rounds, uint32_t base, int initiator, uint32_t *status, cudaStream_t stream) {
+    probe_signal_kernel<<<1, 32, 0, stream>>>(own_flag, peer_flag, peer_payload, payload_words, rounds, base, initiator,
+                                              status);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,
                          uint32_t *sink, cudaStream_t stream) {

@@ -127,6 +127,7 @@ def library() -> ctypes.CDLL:
         "q4b_all_gather_columns": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp] + err),
         "q4b_comm_free": (None, [_vp, _vp]),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_probe_signal": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_graph_begin": (_int, [_vp] + err),
@@ -537,6 +538,14 @@ class Q4Context:
         out = ctypes.c_double(0.0)
         self._check(library().q4b_probe_read(self.handle, mode, nbytes, ctas_per_sm, stages, stage_bytes,
                                              iterations, ctypes.byref(out), self._err, _ERR))
+        return out.value
+
+    def probe_signal(self, own: int, peer: int, payload_bytes: int, rounds: int, rounds_before: int,
+                     initiator: bool) -> float:
+        """Microseconds per round trip of the publish-and-wait exchange between two GPUs (see q4b_probe_signal)."""
+        out = ctypes.c_double(0.0)
+        self._check(library().q4b_probe_signal(self.handle, own, peer, payload_bytes, rounds, rounds_before,
+                                               1 if initiator else 0, ctypes.byref(out), self._err, _ERR))
         return out.value
 
     # -- graph replay -------------------------------------------------------

@@ -525,6 +525,20 @@ int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm
                    uint32_t stage_bytes, int iterations, double *gigabytes_per_second,
                    char *error_message, size_t error_capacity);
 
+/* One side of a ping-pong between two GPUs (no reference counterpart: the
+ * reference has one GPU).  Both ranks call it at about the same time, one with
+ * initiator = 1.  own_words / peer_words: 256 + payload_bytes of zeroed device
+ * memory on this GPU and the same buffer of the peer (q4b_ipc_open); word 0 is
+ * the flag.  A round trip is: payload stores into the peer, a system-scope fence,
+ * an addition to the peer's flag, and the wait for the answer -- the exchange a
+ * column-parallel decode sequence makes twice per gather point.  rounds_before:
+ * rounds earlier calls have already played on these buffers.  Waits are bounded
+ * (about a second); a peer that never answers gives status 2 and a message
+ * naming the round.  Synchronous. */
+int q4b_probe_signal(q4b_context *context, void *own_words, void *peer_words, uint32_t payload_bytes,
+                     uint32_t rounds, uint32_t rounds_before, int initiator, double *microseconds_per_round_trip,
+                     char *error_message, size_t error_capacity);
+
 /* ---- replay of a recorded call sequence (one command buffer per token in the
  * reference, qwen38_m3_decode.m:1614-1690): calls between begin and end are
  * captured instead of executed. */

@@ -38,10 +38,22 @@ def build(force: bool = False) -> str:
     return target
 
 
+def reference_root() -> str | None:
+    """A checkout of the reference project: REFERENCE in the environment, else a directory named `reference`
+    beside this repository."""
+    named = os.environ.get("REFERENCE", "")
+    if named:
+        return named if os.path.isdir(named) else None
+    beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return beside if os.path.isdir(beside) else None
+
+
 def build_ref() -> str | None:
-    """Compile oracle/_ref from the reference tree when it is present."""
-    subprocess.call(["make", "-s", "ref"], cwd=_HERE,
-                    stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    """Compile oracle/_ref from the reference tree when there is one; a prebuilt oracle/_ref is kept otherwise."""
+    root = reference_root()
+    if root is not None:
+        subprocess.call(["make", "-s", "ref", f"REFERENCE={root}"], cwd=_HERE,
+                        stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
     path = os.path.join(_HERE, "_ref", "libq4ref.so")
     return path if os.path.exists(path) else None
 

@@ -59,4 +59,7 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE", "")
+    if not root:
+        raise SystemExit("usage: make_image_offsets.py <reference checkout>   (or REFERENCE in the environment)")
+    main(root)

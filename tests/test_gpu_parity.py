@@ -239,8 +239,8 @@ def test_reference_fixture_patterns(q4b, orc, ctx):
 
 
 # bits 0-3 CTAs per SM, bit 4 fp16 form at M <= 4, bits 8-11 limit on K parts, bit 13 no clusters for a split K,
-# bit 14 no dependent launch
-@pytest.mark.parametrize("variant", [0x0001, 0x0002, 0x0010, 0x0100, 0x0300, 0x0211, 0x2000, 0x2010, 0x4000, 0x4012])
+# bit 14 no dependent launch, bit 16 first ring fill not held back
+@pytest.mark.parametrize("variant", [0x0001, 0x0002, 0x0010, 0x0100, 0x0300, 0x0211, 0x2000, 0x2010, 0x4000, 0x4012, 0x10000])
 def test_kernel_variants_agree(q4b, orc, ctx, variant):
     n, k = 2048, 5120
     quants, meta = orc.synth_weight(3, 0, n, k // 64)
