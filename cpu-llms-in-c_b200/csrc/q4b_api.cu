@@ -1192,12 +1192,12 @@ int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm
 }
 
 int q4b_probe_signal(q4b_context *context, void *own_words, void *peer_words, uint32_t payload_bytes,
-                     uint32_t rounds, uint32_t rounds_before, int initiator, double *microseconds_per_round_trip,
-                     char *error_message, size_t error_capacity) {
+                     uint32_t rounds, uint32_t rounds_before, int initiator, int mode,
+                     double *microseconds_per_round_trip, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
     if (own_words == nullptr || peer_words == nullptr || microseconds_per_round_trip == nullptr || rounds == 0 ||
-        payload_bytes > (1u << 20) || payload_bytes % 4 != 0 || context->capturing) {
+        payload_bytes > (1u << 20) || payload_bytes % 4 != 0 || mode < 0 || mode > 7 || context->capturing) {
         set_error(error_message, error_capacity, "invalid signal probe arguments");
         return Q4B_BAD_ARGUMENT;
     }
@@ -1206,7 +1206,7 @@ int q4b_probe_signal(q4b_context *context, void *own_words, void *peer_words, ui
     cudaError_t status = cudaMemsetAsync(own + 1, 0, 4, context->stream);
     if (status == cudaSuccess) status = cudaEventRecord(context->timer_start, context->stream);
     if (status == cudaSuccess) {
-        status = launch_probe_signal(own, peer, peer + 64, payload_bytes / 4, rounds, rounds_before, initiator, own + 1,
+        status = launch_probe_signal(own, peer, peer + 64, payload_bytes / 4, rounds, rounds_before, initiator, mode, own + 1,
                                      context->stream);
     }
     context->launches += 1;

@@ -667,8 +667,8 @@ decode_kernel(const __grid_constant__ PassParams p) {
         }
     } else {
         // ---- consumers: warp w owns tile w & 3 of block w >> 2 of every pair block this CTA visits ----
-        if (!SEQ) asm volatile("griddepcontrol.wait;" ::: "memory");  // x, y, residual and scratch belong to stream order
         const int k = warp >> 2, r = warp & 3;
+        bool in_stream_order = SEQ;  // a single launch: whether the launches before it are known to be complete
         uint32_t epoch = 0;
         if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
         uint32_t it = 0;
@@ -789,6 +789,11 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         mbar_wait(xempty0 + 8 * (counter % kEntrySets), ((counter / kEntrySets) - 1) & 1, failed, 0x94u);
                     }
                 };
+                if (!in_stream_order) {
+                    // x, y, residual and scratch belong to stream order; everything above (and the weights) does not
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    in_stream_order = true;
+                }
                 // the unit's first two stages: nothing to hide their entries behind.  With several groups to a pass
                 // a warp has a pass in at most one of the two, so the stages' passes run side by side on
                 // different warps; otherwise a warp makes its two passes one after the other.

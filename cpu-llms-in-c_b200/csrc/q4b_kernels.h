@@ -168,7 +168,8 @@ void context_count_launch(q4b_context *context);  // one more kernel of this lib
 
 // ---- q4b_probe.cu ----
 cudaError_t launch_probe_signal(uint32_t *own_flag, uint32_t *peer_flag, uint32_t *peer_payload, uint32_t payload_words,
-                                uint32_t rounds, uint32_t base, int initiator, uint32_t *status, cudaStream_t stream);
+                                uint32_t rounds, uint32_t base, int initiator, int mode, uint32_t *status,
+                                cudaStream_t stream);
 cudaError_t launch_probe(int mode, const uint8_t *data, size_t bytes, int ctas, uint32_t stages, uint32_t stage_bytes,
                          uint32_t *sink, cudaStream_t stream);
 

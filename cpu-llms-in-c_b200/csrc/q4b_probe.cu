@@ -98,9 +98,12 @@ __global__ void __launch_bounds__(288) probe_ring_kernel(const uint8_t *data, si
 // `payload_words` plain stores into the peer's memory, a system-scope fence, one addition to the peer's flag; then
 // a wait for the own flag to reach the same round.  The initiator sends first, the responder answers.  Every wait
 // is bounded; *status receives the round at which a wait gave up (0: none did).
+// mode: 0 as described; bit 0: the flag is raised by one st.release.sys instead of fence + red; bit 1: the
+// waiter polls with relaxed loads and makes one system-scope fence once the flag is up; bit 2: no fence on the
+// sender at all and a relaxed flag store (NOT an ordering a consumer may rely on: it shows what the fence costs)
 __global__ void __launch_bounds__(32) probe_signal_kernel(uint32_t *own_flag, uint32_t *peer_flag, uint32_t *peer_payload,
                                                           uint32_t payload_words, uint32_t rounds, uint32_t base,
-                                                          int initiator, uint32_t *status) {
+                                                          int initiator, int mode, uint32_t *status) {
     const uint32_t lane = threadIdx.x;
     bool alive = true;
     for (uint32_t round = 1; round <= rounds && alive; ++round) {
@@ -110,14 +113,26 @@ __global__ void __launch_bounds__(32) probe_signal_kernel(uint32_t *own_flag, ui
                 for (uint32_t w = lane; w < payload_words; w += 32) peer_payload[w] = round;
                 __syncwarp();
                 if (lane == 0) {
-                    asm volatile("fence.acq_rel.sys;" ::: "memory");
-                    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(peer_flag), "r"(1u) : "memory");
+                    if (mode & 4) {
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(base + round) : "memory");
+                    } else if (mode & 1) {
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(base + round) : "memory");
+                    } else {
+                        asm volatile("fence.acq_rel.sys;" ::: "memory");
+                        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(peer_flag), "r"(1u) : "memory");
+                    }
                 }
             } else {
                 uint32_t seen = 0;
                 const long long start = clock64();
                 for (;;) {
-                    if (lane == 0) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own_flag) : "memory");
+                    if (lane == 0) {
+                        if (mode & 2) {
+                            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own_flag) : "memory");
+                        } else {
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own_flag) : "memory");
+                        }
+                    }
                     seen = __shfl_sync(0xffffffffu, seen, 0);
                     if ((int32_t)(seen - (base + round)) >= 0) break;
                     if (clock64() - start > 2000000000ll) {  // about a second: the peer is not there
@@ -129,15 +144,17 @@ __global__ void __launch_bounds__(32) probe_signal_kernel(uint32_t *own_flag, ui
                     if (lane == 0) *status = round;
                     break;
                 }
+                if (mode & 2) asm volatile("fence.acq_rel.sys;" ::: "memory");
             }
         }
     }
 }
 
 cudaError_t launch_probe_signal(uint32_t *own_flag, uint32_t *peer_flag, uint32_t *peer_payload, uint32_t payload_words,
-                                uint32_t rounds, uint32_t base, int initiator, uint32_t *status, cudaStream_t stream) {
+                                uint32_t rounds, uint32_t base, int initiator, int mode, uint32_t *status,
+                                cudaStream_t stream) {
     probe_signal_kernel<<<1, 32, 0, stream>>>(own_flag, peer_flag, peer_payload, payload_words, rounds, base, initiator,
-                                              status);
+                                              mode, status);
     return cudaGetLastError();
 }
 

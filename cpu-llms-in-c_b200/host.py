@@ -127,7 +127,7 @@ def library() -> ctypes.CDLL:
         "q4b_all_gather_columns": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp] + err),
         "q4b_comm_free": (None, [_vp, _vp]),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
-        "q4b_probe_signal": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_probe_signal": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _int, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_graph_begin": (_int, [_vp] + err),
@@ -541,11 +541,11 @@ class Q4Context:
         return out.value
 
     def probe_signal(self, own: int, peer: int, payload_bytes: int, rounds: int, rounds_before: int,
-                     initiator: bool) -> float:
+                     initiator: bool, mode: int = 0) -> float:
         """Microseconds per round trip of the publish-and-wait exchange between two GPUs (see q4b_probe_signal)."""
         out = ctypes.c_double(0.0)
         self._check(library().q4b_probe_signal(self.handle, own, peer, payload_bytes, rounds, rounds_before,
-                                               1 if initiator else 0, ctypes.byref(out), self._err, _ERR))
+                                               1 if initiator else 0, mode, ctypes.byref(out), self._err, _ERR))
         return out.value
 
     # -- graph replay -------------------------------------------------------

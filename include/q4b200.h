@@ -532,12 +532,16 @@ int q4b_probe_read(q4b_context *context, int mode, size_t bytes, int ctas_per_sm
  * the flag.  A round trip is: payload stores into the peer, a system-scope fence,
  * an addition to the peer's flag, and the wait for the answer -- the exchange a
  * column-parallel decode sequence makes twice per gather point.  rounds_before:
- * rounds earlier calls have already played on these buffers.  Waits are bounded
+ * rounds earlier calls have already played on these buffers.  mode 0 is that
+ * exchange; bit 0 raises the flag with one release store instead of fence +
+ * addition, bit 1 polls with relaxed loads and fences once at the end, bit 2
+ * drops the sender's fence (not an ordering to rely on: it prices the fence).
+ * Waits are bounded
  * (about a second); a peer that never answers gives status 2 and a message
  * naming the round.  Synchronous. */
 int q4b_probe_signal(q4b_context *context, void *own_words, void *peer_words, uint32_t payload_bytes,
-                     uint32_t rounds, uint32_t rounds_before, int initiator, double *microseconds_per_round_trip,
-                     char *error_message, size_t error_capacity);
+                     uint32_t rounds, uint32_t rounds_before, int initiator, int mode,
+                     double *microseconds_per_round_trip, char *error_message, size_t error_capacity);
 
 /* ---- replay of a recorded call sequence (one command buffer per token in the
  * reference, qwen38_m3_decode.m:1614-1690): calls between begin and end are
