@@ -581,6 +581,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
     uint8_t *entries = ring + stages * kStageBytes;  // [kEntrySets][8 groups][entry_bytes]
     float *xchg = reinterpret_cast<float *>(entries + kEntrySets * kStageGroups * entry_bytes);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 24, xfull0 = full0 + 48, xempty0 = full0 + 72;
+    const uint32_t opened0 = full0 + 104;  // completes once: the first entries of a single launch are in place
     const uint32_t ring0 = smem_u32(ring);
 
     if (threadIdx.x == 0) {
@@ -592,6 +593,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
             mbar_init(xfull0 + 8 * c, kConsumers);
             mbar_init(xempty0 + 8 * c, kConsumers);
         }
+        mbar_init(opened0, kConsumers);
         *failed = 0;
         *published = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -635,8 +637,10 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         // A single launch starts before the launch it depends on has finished, and the ring would
                         // fill while the consumers wait for their activations; then their first loads queue behind
                         // a whole ring of weight requests.  The last stage of the first fill waits for the first
-                        // entries instead.
-                        if (!SEQ && throttle && it == stages - 1) mbar_wait(xfull0, 0, failed, 0x96u);
+                        // entries instead (a barrier of its own that completes once: one that keeps cycling could
+                        // run two phases ahead of a thread that only watches it, and the watcher would wait for
+                        // a third).
+                        if (!SEQ && throttle && it == stages - 1) mbar_wait(opened0, 0, failed, 0x96u);
                         if (*failed != 0) continue;  // no new copies once a wait has expired
                         const uint32_t bytes = min(kStageGroups, u.g1 - g) * kUnitBytes;
                         mbar_expect_tx(full0 + 8 * s, u.has_b ? 2 * bytes : bytes);
@@ -669,6 +673,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
         // ---- consumers: warp w owns tile w & 3 of block w >> 2 of every pair block this CTA visits ----
         const int k = warp >> 2, r = warp & 3;
         bool in_stream_order = SEQ;  // a single launch: whether the launches before it are known to be complete
+        bool opened = false;         // a single launch: whether this warp has reported its first entries
         uint32_t epoch = 0;
         if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
         uint32_t it = 0;
@@ -819,6 +824,10 @@ decode_kernel(const __grid_constant__ PassParams p) {
                             hand_over(it + d);
                         }
                     }
+                }
+                if (!SEQ && !opened) {  // this warp's share of the launch's first entries is in place
+                    opened = true;
+                    if (lane == 0) mbar_arrive(opened0);
                 }
                 lap(kProfileEntries);
                 for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
