@@ -317,6 +317,19 @@ def run_ours(args):
                 model.step()
             modes[candidate] = timed_steps(ctx, barrier, max_over_ranks, model.step, 5) / 5
         model.mode = min(modes, key=modes.get)
+    elif mode == "auto" and args.gather == "push":
+        # ranks that push: the persistent launch against a recorded graph of launches with barriers between the
+        # ranks (the same weights); every rank takes the same decision from the max-over-ranks times
+        other = sharded.ShardedLayerStack(ctx, q4b.LAYER_27B, LAYERS, args.m, rank, world, dist, gather=args.gather,
+                                          mode="graph", layers=model.layers)
+        for name, candidate in (("sequence", model), ("graph", other)):
+            for _ in range(3):
+                candidate.step()
+            modes[name] = timed_steps(ctx, barrier, max_over_ranks, candidate.step, 5) / 5
+        if modes["graph"] < modes["sequence"]:
+            model.owns_layers, other.owns_layers = False, True
+            model, other = other, model
+        other.free()
     mode = model.mode
 
     # ---- device-resident measurement ----

@@ -395,12 +395,9 @@ int run_projection(q4b_context *context, ProjectionArgs args, char *error_messag
         }
         return run_tensor_core(context, args, error_message, error_capacity);
     }
-    if (context->push_peers != 0) {
-        context->push_peers = 0;
-        set_error(error_message, error_capacity,
-                  "pushed outputs are for M > %u; up to that, ranks share outputs through a sequence", limit);
-        return Q4B_BAD_ARGUMENT;
-    }
+    // q4b_context_push_outputs: this call's outputs also go into the peers' copies (consumed by this call)
+    const uint32_t push_peers = built_in_scratch ? 0u : context->push_peers;
+    context->push_peers = 0;
     for (uint32_t m0 = 0; m0 < total; m0 += limit) {
         const uint32_t m_rows = total - m0 < limit ? total - m0 : limit;
         DecodeJob job = {};
@@ -409,6 +406,18 @@ int run_projection(q4b_context *context, ProjectionArgs args, char *error_messag
             job.rows[s] = args.w[s].rows;
             job.ldy[s] = args.ldy[s];
             job.y[s][0] = static_cast<uint8_t *>(args.y[s]) + (size_t)m0 * args.ldy[s] * dtype_bytes(args.y_dtype);
+        }
+        uint32_t world = 1;
+        for (uint32_t r = 0; r < push_peers; ++r) {  // the peers that were named, packed after the own copy
+            bool named = false;
+            for (int s = 0; s < args.segments; ++s) named = named || context->push_y[s][r] != nullptr;
+            if (!named) continue;
+            for (int s = 0; s < args.segments; ++s) {
+                uint8_t *peer = static_cast<uint8_t *>(context->push_y[s][r]);
+                job.y[s][world] = peer == nullptr ? nullptr
+                                                  : peer + (size_t)m0 * args.ldy[s] * dtype_bytes(args.y_dtype);
+            }
+            if (++world == (uint32_t)kMaxPeers) break;
         }
         job.segments = (uint32_t)args.segments;
         job.groups = args.w[0].groups;
@@ -454,8 +463,8 @@ int run_projection(q4b_context *context, ProjectionArgs args, char *error_messag
             scratch = context->scratch;
             counters = context->counters;
         }
-        status = launch_decode(job, m_rows, geometry, context->variant, scratch, counters, context->status_device,
-                               context->stream);
+        status = launch_decode(job, m_rows, world, geometry, context->variant, scratch, counters,
+                               context->status_device, context->stream);
         if (!context->capturing) ++context->launches;  // recorded launches count at replay
         if (status != cudaSuccess) return device_failure(error_message, error_capacity, "decode launch", status);
     }
@@ -850,7 +859,7 @@ int q4b_context_push_outputs(q4b_context *context, uint32_t world, void *const *
 struct q4b_barrier {
     uint32_t *counter;                 // own arrivals, device memory, counts up for ever
     uint32_t *counters[kMaxPeers];     // every rank's (own included)
-    uint32_t world, rank, round;
+    uint32_t world, rank;
     int device;
 };
 
@@ -889,8 +898,8 @@ int q4b_barrier_set_peer(q4b_barrier *barrier, uint32_t peer_rank, void *peer_co
 int q4b_barrier_queue(q4b_context *context, q4b_barrier *barrier, char *error_message, size_t error_capacity) {
     int code = check_context(context, error_message, error_capacity);
     if (code != Q4B_OK) return code;
-    if (barrier == nullptr || barrier->device != context->device || context->capturing) {
-        set_error(error_message, error_capacity, "no barrier, another device's, or called while recording");
+    if (barrier == nullptr || barrier->device != context->device) {
+        set_error(error_message, error_capacity, "no barrier, or another device's");
         return Q4B_BAD_ARGUMENT;
     }
     for (uint32_t r = 0; r < barrier->world; ++r) {
@@ -899,11 +908,12 @@ int q4b_barrier_queue(q4b_context *context, q4b_barrier *barrier, char *error_me
             return Q4B_BAD_ARGUMENT;
         }
     }
-    ++barrier->round;
-    Q4B_CUDA(launch_rank_barrier(barrier->counters, barrier->world, barrier->rank, barrier->world * barrier->round,
+    // the number of the round lives in device memory (the second 128 bytes of the own counter's allocation), so a
+    // recorded barrier counts on at every replay
+    Q4B_CUDA(launch_rank_barrier(barrier->counters, barrier->world, barrier->rank, barrier->counter + 32,
                                  context->status_device, context->stream),
              "rank barrier");
-    ++context->launches;
+    if (!context->capturing) ++context->launches;
     return Q4B_OK;
 }
 

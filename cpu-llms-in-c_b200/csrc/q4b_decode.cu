@@ -1234,6 +1234,10 @@ void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geom
         }
     }
     if (geometry.max_parts > 0 && parts > geometry.max_parts) parts = geometry.max_parts;
+    // A small matrix (a rank's slice of a projection, say) would be cut into more than eight parts: eight parts
+    // that meet in a cluster's shared memory finish sooner than many that meet in global memory, as long as a
+    // part stays within a few ring stages
+    if (parts > 8 && geometry.plan_room[8] >= pairs && G / 8 <= 5 * kStageGroups) parts = 8;
     // 2..8 parts meet in the shared memory of a thread-block cluster when all the clusters fit on the device at
     // once: rather one part fewer than a sum through global memory
     while (parts >= 2 && parts <= 8 && geometry.plan_room[parts] < pairs) {
@@ -1287,13 +1291,13 @@ cudaError_t launch_kernel(const PassParams &p, uint32_t ctas, size_t smem_bytes,
 
 }  // namespace
 
-cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeometry &geometry, int variant,
+cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, uint32_t world, const DecodeGeometry &geometry, int variant,
                           float *scratch, uint32_t *counters, uint32_t *status, cudaStream_t stream) {
     PassParams p = {};
     p.job = job;
     p.job_count = 1;
     p.m_rows = m_rows;
-    p.world = 1;
+    p.world = world;  // the own copy of the outputs and world - 1 peers' (job.y[segment][0 .. world - 1])
     p.stages = geometry.stages;
     p.scratch = scratch;
     p.counters = counters;

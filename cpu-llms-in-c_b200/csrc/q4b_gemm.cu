@@ -783,41 +783,56 @@ __global__ void convert_f32_to_f16_kernel(const float *in, __half *out, size_t c
 
 struct RankBarrierParams {
     uint32_t *counters[kMaxPeers];
-    uint32_t world, rank, expected;
+    uint32_t world, rank;
+    uint32_t *round;  // device word of this rank: barriers passed so far
     uint32_t *status;
 };
-// Kernels of different GPUs wait for one another here, never two launches on one GPU.
+// Kernels of different GPUs wait for one another here, never two launches on one GPU.  Launched as a programmatic
+// dependent of the kernel before it and letting its own successor start early: the next projection's weights
+// stream while the ranks meet.
 __global__ void rank_barrier_kernel(const RankBarrierParams p) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the launches before this one are complete and visible
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const uint32_t round = *p.round + 1;
+    *p.round = round;
     // everything this GPU stored into the peers' memory before this launch is ordered before the adds
     asm volatile("fence.acq_rel.sys;" ::: "memory");
     for (uint32_t r = 0; r < p.world; ++r) {
         asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.counters[r]), "r"(1u) : "memory");
     }
+    const uint32_t expected = p.world * round;
     const long long start = clock64();
     for (;;) {
         uint32_t seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters[p.rank]) : "memory");
-        if ((int32_t)(seen - p.expected) >= 0) break;
+        if ((int32_t)(seen - expected) >= 0) break;
         if (clock64() - start > kTcWaitLimit) {
             atomicExch(p.status, 0x91u);
             break;
         }
-        __nanosleep(100);
     }
 }
 
-cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t expected,
+cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t *round,
                                 uint32_t *status, cudaStream_t stream) {
     if (world == 0 || world > (uint32_t)kMaxPeers || rank >= world) return cudaErrorInvalidValue;
     RankBarrierParams p = {};
     for (uint32_t r = 0; r < world; ++r) p.counters[r] = counters[r];
     p.world = world;
     p.rank = rank;
-    p.expected = expected;
+    p.round = round;
     p.status = status;
-    rank_barrier_kernel<<<1, 32, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1);
+    config.blockDim = dim3(32);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, rank_barrier_kernel, p);
 }
 
 cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream) {

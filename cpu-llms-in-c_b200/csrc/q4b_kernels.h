@@ -123,7 +123,7 @@ cudaError_t decode_geometry(uint32_t m_rows, int variant, int sm_count, bool seq
 // fills pair_begin, parts and units of `job`; returns the split-K scratch it needs (0 when K is not split)
 void plan_decode_job(DecodeJob *job, uint32_t m_rows, const DecodeGeometry &geometry, size_t *scratch_bytes,
                      size_t *counter_bytes);
-cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, const DecodeGeometry &geometry, int variant,
+cudaError_t launch_decode(const DecodeJob &job, uint32_t m_rows, uint32_t world, const DecodeGeometry &geometry, int variant,
                           float *scratch, uint32_t *counters, uint32_t *status, cudaStream_t stream);
 cudaError_t launch_sequence(const SequenceLaunch &launch, cudaStream_t stream);
 // device addresses and sizes of the library's built-in (never allocated) scratch on the current device
@@ -157,9 +157,10 @@ struct TcGemmArgs {
 };
 cudaError_t launch_tc_gemm(const TcGemmArgs &args, int sm_count, cudaStream_t stream);
 cudaError_t launch_convert_f32_to_f16(const float *in, __half *out, size_t count, cudaStream_t stream);
-// One thread: system-scope fence, add 1 to every rank's counter, wait (bounded) until the own counter shows
-// `expected` arrivals; a wait that expires stores a code in *status.
-cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t expected,
+// One thread: after the launches before it are complete, a system-scope fence, 1 added to every rank's counter,
+// and a bounded wait until the own counter shows world x (the round, counted in *round) arrivals; a wait that
+// expires stores a code in *status.  A programmatic dependent of its predecessor, and its successor of it.
+cudaError_t launch_rank_barrier(uint32_t *const *counters, uint32_t world, uint32_t rank, uint32_t *round,
                                 uint32_t *status, cudaStream_t stream);
 
 // ---- q4b_api.cu: what the other host files need to know of a context ----

@@ -69,9 +69,11 @@ class ShardedLayerStack:
         self.d2h_bytes_per_step = self.y_layer_bytes * n_layers
         self.comm = None
         self.barrier = None
-        if world > 1 and gather == "push" and m_rows <= 16:
+        if world > 1 and gather == "push" and m_rows <= 16 and self.mode == "sequence":
             self._setup_push()
         elif world > 1 and gather == "push":
+            # one launch per projection group, each storing into every rank's y, and a barrier between the ranks
+            # after it; at M <= 16 the whole pass is recorded into a graph
             self._setup_push_gemm()
         elif world > 1:
             self.gather = "nccl"
@@ -211,7 +213,16 @@ class ShardedLayerStack:
             self._queue_sharded_nccl()
             return
         if self.barrier is not None:
-            self._queue_sharded_push_gemm()
+            if self.m > 16:
+                self._queue_sharded_push_gemm()
+                return
+            if self.graph is None:
+                self._queue_sharded_push_gemm()  # plain launches once (sets kernel attributes, allocates scratch)
+                self.ctx.sync()
+                self.ctx.graph_begin()
+                self._queue_sharded_push_gemm()
+                self.graph = self.ctx.graph_end()
+            self.graph.launch()
             return
         if self.mode == "sequence":
             if self.sequence is None:

@@ -337,16 +337,18 @@ int q4b_sequence_profile(q4b_context *context, q4b_sequence *sequence, uint64_t 
                          uint32_t *thread_blocks, char *error_message, size_t error_capacity);
 void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence);
 
-/* ---- column-parallel ranks at M > 16 (prefill): the tensor-core GEMM stores a
+/* ---- column-parallel ranks, one launch per projection: the kernel stores a
  * rank's slice straight into every rank's copy of the output, and a one-thread
  * barrier kernel per gather point replaces the all-gather (the reference has one
  * GPU; this is the NCCL all-gather of the slices done by the producing kernel).
+ * Works at every M: the tensor-core GEMM above M = 16, the decode kernel up to it
+ * (where a sequence, above, is the other way to share outputs).
  *
  * q4b_context_push_outputs: for the NEXT q4b_matmul / q4b_matmul_group /
- * q4b_gate_up_silu call (M > 16; smaller M is refused -- use a sequence), name
- * where its output block(s) live in the other ranks' memory: peer_y[s * world + r]
- * is segment s's block on rank r, obtained with q4b_ipc_open, pointing at the same
- * element as the call's own y[s]; NULL entries (the own rank) are skipped.
+ * q4b_gate_up_silu call, name where its output block(s) live in the other ranks'
+ * memory: peer_y[s * world + r] is segment s's block on rank r, obtained with
+ * q4b_ipc_open, pointing at the same element as the call's own y[s]; NULL entries
+ * (the own rank) are skipped.  q4b_matmul_no_alloc ignores it.
  *
  * q4b_barrier_*: create one per context, exchange q4b_barrier_counter between the
  * ranks (q4b_ipc_export / q4b_ipc_open), install with q4b_barrier_set_peer.
@@ -354,7 +356,11 @@ void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence);
  * queued before this is stored" and waits (bounded, status 2 at the next
  * q4b_sync when it expires) until every rank has said so; work queued after it
  * may read what the peers pushed.  Every rank must queue the same barriers in
- * the same order; not recordable into a graph (the round number is an argument). */
+ * the same order.  The round number lives in device memory, so barriers may be
+ * recorded into a graph (q4b_graph_begin) together with the launches between
+ * them; the barrier is a programmatic dependent of the launch before it and lets
+ * the launch after it start early, so the next projection's weights stream while
+ * the ranks meet. */
 typedef struct q4b_barrier q4b_barrier;
 int q4b_context_push_outputs(q4b_context *context, uint32_t world, void *const *peer_y, int count);
 int q4b_barrier_create(q4b_context *context, uint32_t world, uint32_t rank, q4b_barrier **barrier,

@@ -2,7 +2,8 @@
 
 Every rank holds its N-slice of every projection, runs the small layer stack
 twice and must end with the WHOLE [M, N] of every projection equal to the
-oracle's, both through the fused push gather and through the NCCL baseline."""
+oracle's: through the persistent launch that pushes, through per-projection launches that push
+with a barrier between the ranks, and through the NCCL baseline."""
 import importlib
 import os
 import sys
@@ -31,10 +32,15 @@ def main():
     ctx = q4b.Q4Context(local)
     # M = 64 and 300 take the tensor-core GEMM on every rank's slice
     sizes = (1, 4, 64, 300) if layer_set is q4b.LAYER_SMALL else (1, 4)
-    for gather in ("push", "nccl"):
+    # the ranks share outputs through one persistent launch whose epilogue stores into every rank's copy, through
+    # one launch per projection that does the same with a barrier between the ranks after it (recorded into a
+    # graph at M <= 16), or through NCCL all-gathers
+    for gather, mode in (("push", "sequence"), ("push", "graph"), ("nccl", "graph")):
         for m in sizes:
-            stack = sharded.ShardedLayerStack(ctx, layer_set, layers, m, rank, world, dist, gather=gather)
-            assert stack.gather == gather
+            if mode == "sequence" and m > 16:
+                continue
+            stack = sharded.ShardedLayerStack(ctx, layer_set, layers, m, rank, world, dist, gather=gather, mode=mode)
+            assert stack.gather == gather and (stack.mode == mode or m > 16)
             for _ in range(3):
                 stack.step()
             ctx.sync()
@@ -44,7 +50,7 @@ def main():
                 got = stack.outputs(index)
                 want = oracle_layer(orc, layer_set, index, m)
                 for name in want:
-                    assert_close(got[name], want[name], f"rank {rank} {gather} layer {index} {name} M={m}")
+                    assert_close(got[name], want[name], f"rank {rank} {gather} {mode} layer {index} {name} M={m}")
             dist.barrier()
             stack.free()
     ctx.close()
