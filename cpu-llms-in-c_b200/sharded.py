@@ -73,7 +73,7 @@ class ShardedLayerStack:
             self._setup_push()
         elif world > 1 and gather == "push":
             # one launch per projection group, each storing into every rank's y, and a barrier between the ranks
-            # after it; at M <= 16 the whole pass is recorded into a graph
+            # after it; the whole pass is recorded into a graph
             self._setup_push_gemm()
         elif world > 1:
             self.gather = "nccl"
@@ -213,9 +213,6 @@ class ShardedLayerStack:
             self._queue_sharded_nccl()
             return
         if self.barrier is not None:
-            if self.m > 16:
-                self._queue_sharded_push_gemm()
-                return
             if self.graph is None:
                 self._queue_sharded_push_gemm()  # plain launches once (sets kernel attributes, allocates scratch)
                 self.ctx.sync()

@@ -34,7 +34,7 @@ def main():
     sizes = (1, 4, 64, 300) if layer_set is q4b.LAYER_SMALL else (1, 4)
     # the ranks share outputs through one persistent launch whose epilogue stores into every rank's copy, through
     # one launch per projection that does the same with a barrier between the ranks after it (recorded into a
-    # graph at M <= 16), or through NCCL all-gathers
+    # graph), or through NCCL all-gathers
     for gather, mode in (("push", "sequence"), ("push", "graph"), ("nccl", "graph")):
         for m in sizes:
             if mode == "sequence" and m > 16:
