@@ -97,6 +97,26 @@ __global__ void interleave_slices_kernel(const uint4 *staging, uint4 *full, uint
     }
 }
 
+// peers[r][m][c] = local[m][c] for a block of `m_rows` rows of `row_vectors` 16-byte pieces, rows `ld_vectors`
+// apart: consecutive threads take consecutive pieces of one destination (whole 512-byte requests per warp on the
+// link), the destinations rotate with the thread block so that every link is busy from the start
+struct PushParams {
+    const uint4 *local;
+    uint4 *peers[kMaxPeers];
+    uint32_t peer_count, m_rows, row_vectors, ld_vectors;
+};
+__global__ void __launch_bounds__(256) push_rows_kernel(const PushParams p) {
+    const size_t per_peer = (size_t)p.m_rows * p.row_vectors;
+    const size_t chunks = (per_peer + 255) / 256;  // 256 pieces = one thread block's turn on one destination
+    for (size_t turn = blockIdx.x; turn < chunks * p.peer_count; turn += gridDim.x) {
+        const uint32_t peer = (uint32_t)(turn % p.peer_count);
+        const size_t at = (turn / p.peer_count) * 256 + threadIdx.x;
+        if (at >= per_peer) continue;
+        const size_t m = at / p.row_vectors, c = at % p.row_vectors;
+        p.peers[peer][m * p.ld_vectors + c] = __ldcg(p.local + m * p.ld_vectors + c);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -189,6 +209,41 @@ int q4b_all_gather_columns(q4b_context *context, q4b_comm *comm, const void *sli
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) {
         comm_message(error_message, error_capacity, "slice interleave: %s", cudaGetErrorString(status));
+        return Q4B_DEVICE_FAILURE;
+    }
+    context_count_launch(context);
+    return Q4B_OK;
+}
+
+int q4b_push_rows(q4b_context *context, const void *local, void *const *peers, uint32_t peer_count, uint32_t m_rows,
+                  uint32_t row_bytes, uint32_t ld_bytes, char *error_message, size_t error_capacity) {
+    if (context == nullptr || local == nullptr || peers == nullptr || peer_count == 0 || peer_count > (uint32_t)kMaxPeers ||
+        m_rows == 0 || row_bytes == 0 || row_bytes % 16 != 0 || ld_bytes % 16 != 0 || ld_bytes < row_bytes ||
+        (reinterpret_cast<uintptr_t>(local) & 15u) != 0) {
+        comm_message(error_message, error_capacity,
+                     "1..%d peers; rows and row pitch in whole 16-byte pieces, 16-byte aligned blocks", kMaxPeers);
+        return Q4B_BAD_ARGUMENT;
+    }
+    PushParams p = {};
+    p.local = static_cast<const uint4 *>(local);
+    for (uint32_t r = 0; r < peer_count; ++r) {
+        if (peers[r] == nullptr || (reinterpret_cast<uintptr_t>(peers[r]) & 15u) != 0) {
+            comm_message(error_message, error_capacity, "peer %u: no block, or not 16-byte aligned", r);
+            return Q4B_BAD_ARGUMENT;
+        }
+        p.peers[r] = static_cast<uint4 *>(peers[r]);
+    }
+    p.peer_count = peer_count;
+    p.m_rows = m_rows;
+    p.row_vectors = row_bytes / 16;
+    p.ld_vectors = ld_bytes / 16;
+    const size_t turns = (((size_t)m_rows * p.row_vectors + 255) / 256) * peer_count;
+    const unsigned blocks = (unsigned)(turns < 1184 ? turns : 1184);
+    cudaSetDevice(context_device(context));
+    push_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(q4b_context_stream(context))>>>(p);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) {
+        comm_message(error_message, error_capacity, "row push: %s", cudaGetErrorString(status));
         return Q4B_DEVICE_FAILURE;
     }
     context_count_launch(context);

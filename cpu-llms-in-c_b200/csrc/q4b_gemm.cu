@@ -695,19 +695,33 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
     }
     unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
     // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last round
-    // (160 on 148).  Split the iterations evenly instead when that wins: a CTA then works through
-    // iterations / SMs groups plus about 48 groups' worth of leaving and adding a 128 x BN partial tile
-    // (measured: 5120 -> 6144 at M = 512, 96 tiles of 80 groups, is faster whole).
+    // (160 on 148).  The iterations can be split evenly over any number of CTAs instead.  In units of one
+    // group's MMAs a CTA then works through iterations / CTAs, and a tile that is cut costs about 48 for leaving
+    // and adding the first partial tile plus 25 for every further part, which its owner adds one after the
+    // other (fitted: 17408 -> 5120 at M = 512 whole 129 us, over 148 CTAs 104 us; an eighth of it over 148
+    // CTAs 108 us, i.e. worse than whole).  The cheapest count wins, whole tiles included.
     const uint32_t rounds = ceil_div(tiles, (uint32_t)sm_count);
     const uint64_t iterations = (uint64_t)tiles * p.groups;
     const double whole_cost = (double)rounds * p.groups;
-    const double split_cost = (double)iterations / sm_count + 48.0;
-    p.split = 0;
-    if (args.workspace != nullptr && getenv("Q4B_GEMM_WHOLE_TILES") == nullptr && split_cost < 0.92 * whole_cost &&
-        iterations >= (uint64_t)sm_count * 8 &&
+    double best_cost = whole_cost;
+    unsigned best_grid = 0;
+    if (args.workspace != nullptr && getenv("Q4B_GEMM_WHOLE_TILES") == nullptr &&
         (size_t)sm_count * 128 * BN * sizeof(float) <= args.workspace_bytes) {
+        for (unsigned candidate = 2; candidate <= (unsigned)sm_count; ++candidate) {
+            if (iterations < (uint64_t)candidate * 8) break;
+            const double parts = (double)candidate / tiles;  // CTAs per tile (tiles per CTA when below one)
+            const double cut = parts > 1.0 ? 48.0 + 25.0 * (parts - 1.0) : 48.0;
+            const double cost = (double)ceil_div((uint32_t)iterations, candidate) + cut;
+            if (cost < 0.92 * whole_cost && cost < best_cost) {
+                best_cost = cost;
+                best_grid = candidate;
+            }
+        }
+    }
+    p.split = 0;
+    if (best_grid != 0) {
         p.split = 1;
-        grid = (unsigned)sm_count;
+        grid = best_grid;
         p.iters_per_cta = (uint32_t)(iterations / grid);
         p.iters_extra = (uint32_t)(iterations % grid);
         p.workspace = args.workspace;

@@ -127,6 +127,7 @@ def library() -> ctypes.CDLL:
         "q4b_all_gather_columns": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp] + err),
         "q4b_comm_free": (None, [_vp, _vp]),
         "q4b_probe_read": (_int, [_vp, _int, _sz, _int, _u32, _u32, _int, ctypes.POINTER(ctypes.c_double)] + err),
+        "q4b_push_rows": (_int, [_vp, _vp, ctypes.POINTER(_vp), _u32, _u32, _u32, _u32] + err),
         "q4b_probe_signal": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _int, _int, ctypes.POINTER(ctypes.c_double)] + err),
         "q4b_timer_start": (_int, [_vp] + err),
         "q4b_sync": (_int, [_vp, ctypes.POINTER(ctypes.c_double)] + err),
@@ -539,6 +540,12 @@ class Q4Context:
         self._check(library().q4b_probe_read(self.handle, mode, nbytes, ctas_per_sm, stages, stage_bytes,
                                              iterations, ctypes.byref(out), self._err, _ERR))
         return out.value
+
+    def push_rows(self, local: int, peers: list[int], m_rows: int, row_bytes: int, ld_bytes: int):
+        """Copy a block of this rank's output into the same place of every peer's (see q4b_push_rows)."""
+        array = (_vp * len(peers))(*peers)
+        self._check(library().q4b_push_rows(self.handle, local, array, len(peers), m_rows, row_bytes, ld_bytes,
+                                            self._err, _ERR))
 
     def probe_signal(self, own: int, peer: int, payload_bytes: int, rounds: int, rounds_before: int,
                      initiator: bool, mode: int = 0) -> float:

@@ -167,8 +167,12 @@ class ShardedLayerStack:
             for kind, members in layer.launch_plan():
                 offsets = [index * self.y_layer_bytes + self.y_offsets[p.name] + layer.slices[p.name][0] * 2
                            for p in members]
-                ctx.push_outputs(self.world, [[None if r == self.rank else self.peer_y[r] + offset
-                                               for r in range(self.world)] for offset in offsets])
+                # small M: the kernel's epilogue stores into the peers; large M: a copy kernel after the GEMM
+                # (wide requests on every link at once; the epilogue's 32-byte stores between tiles are far slower)
+                in_epilogue = self.m <= 16
+                if in_epilogue:
+                    ctx.push_outputs(self.world, [[None if r == self.rank else self.peer_y[r] + offset
+                                                   for r in range(self.world)] for offset in offsets])
                 x = x_ptrs[members[0].k]
                 if kind == "group":
                     ctx.matmul_group([layer.weights[p.name][0] for p in members], x, F16, self.m,
@@ -179,6 +183,11 @@ class ShardedLayerStack:
                 else:
                     ctx.matmul(layer.weights[members[0].name][0], x, F16, self.m, self.y_base + offsets[0], F16,
                                members[0].n)
+                if not in_epilogue:
+                    for p, offset in zip(members, offsets):
+                        ctx.push_rows(self.y_base + offset, [self.peer_y[r] + offset for r in range(self.world)
+                                                            if r != self.rank],
+                                      self.m, layer.slices[p.name][1] * 2, p.n * 2)
                 self.barrier.queue()
 
     def _pinned(self, nbytes: int) -> int:

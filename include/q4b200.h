@@ -361,6 +361,16 @@ void q4b_sequence_free(q4b_context *context, q4b_sequence *sequence);
  * them; the barrier is a programmatic dependent of the launch before it and lets
  * the launch after it start early, so the next projection's weights stream while
  * the ranks meet. */
+/* q4b_push_rows: the other way to put a finished slice into the peers' copies, for
+ * large M: one kernel after the launch that copies a block of m_rows rows of
+ * row_bytes each (rows ld_bytes apart, the same pitch on every rank) from this
+ * rank's output into the same place of every peer's (peers[r]: the block's address
+ * there, from q4b_ipc_open) with whole 512-byte requests per warp on every link at
+ * once.  A GEMM epilogue stores 32-64 bytes per thread per peer between tiles and
+ * reaches a fraction of the link's rate; at M = 512 on eight ranks this call is
+ * the difference.  Queue the barrier after it. */
+int q4b_push_rows(q4b_context *context, const void *local, void *const *peers, uint32_t peer_count, uint32_t m_rows,
+                  uint32_t row_bytes, uint32_t ld_bytes, char *error_message, size_t error_capacity);
 typedef struct q4b_barrier q4b_barrier;
 int q4b_context_push_outputs(q4b_context *context, uint32_t world, void *const *peer_y, int count);
 int q4b_barrier_create(q4b_context *context, uint32_t world, uint32_t rank, q4b_barrier **barrier,
