@@ -474,7 +474,7 @@ class Q4Context:
                                                y_dtype, strides, self._err, _ERR))
 
     def push_outputs(self, world: int, peer_ptrs):
-        """peer_ptrs[s][r]: where segment s of the NEXT M > 16 call lives on rank r (None: skip)."""
+        """peer_ptrs[s][r]: where segment s of the NEXT matmul call lives on rank r (None: skip)."""
         count = len(peer_ptrs)
         flat = (_vp * (count * world))(*[peer_ptrs[s][r] for s in range(count) for r in range(world)])
         if library().q4b_context_push_outputs(self.handle, world, flat, count) != 0:

@@ -33,7 +33,7 @@ NCU_GATE_UP_TRAFFIC_BYTES = 103.9e6
 
 class ShardedLayerStack:
     def __init__(self, ctx: Q4Context, layer_set, n_layers: int, m_rows: int, rank: int = 0, world: int = 1,
-                 dist=None, gather: str = "push", mode: str = "graph", layers=None):
+                 dist=None, gather: str = "push", mode: str = "graph", layers=None, push_in_epilogue=None):
         self.ctx, self.layer_set, self.n_layers, self.m = ctx, tuple(layer_set), n_layers, m_rows
         self.rank, self.world, self.dist, self.gather = rank, world, dist, gather
         # weights do not depend on M: a second stack (another M) may share the first one's layers
@@ -43,6 +43,8 @@ class ShardedLayerStack:
         self.ks = sorted({p.k for p in self.layer_set})
         self.graph = None
         self.sequence = None
+        # large M, ranks that push: from the GEMM's epilogue, or by a copy kernel after it (None: by rank count)
+        self.push_in_epilogue = push_in_epilogue
         # "sequence": the whole pass is one persistent launch (M <= 16); "graph": one launch per projection
         # group, replayed from a recorded graph
         self.mode = mode if m_rows <= 16 else "graph"
@@ -169,7 +171,8 @@ class ShardedLayerStack:
                            for p in members]
                 # small M: the kernel's epilogue stores into the peers; large M: a copy kernel after the GEMM
                 # (wide requests on every link at once; the epilogue's 32-byte stores between tiles are far slower)
-                in_epilogue = self.m <= 16
+                in_epilogue = self.m <= 16 or (self.push_in_epilogue if self.push_in_epilogue is not None
+                                               else self.world <= 2)
                 if in_epilogue:
                     ctx.push_outputs(self.world, [[None if r == self.rank else self.peer_y[r] + offset
                                                    for r in range(self.world)] for offset in offsets])

@@ -53,6 +53,36 @@ def main():
                     assert_close(got[name], want[name], f"rank {rank} {gather} {mode} layer {index} {name} M={m}")
             dist.barrier()
             stack.free()
+    # large M with the slice pushed by the copy kernel after the GEMM (the default from three ranks on)
+    for m in ((64, 300) if layer_set is q4b.LAYER_SMALL else ()):
+        stack = sharded.ShardedLayerStack(ctx, layer_set, layers, m, rank, world, dist, gather="push",
+                                          push_in_epilogue=False)
+        for _ in range(3):
+            stack.step()
+        ctx.sync()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for index in range(layers):
+            got = stack.outputs(index)
+            want = oracle_layer(orc, layer_set, index, m)
+            for name in want:
+                assert_close(got[name], want[name], f"rank {rank} copy-kernel push layer {index} {name} M={m}")
+        dist.barrier()
+        stack.free()
+    # the publish-and-wait exchange between ranks 0 and 1 answers within its bounded waits
+    if layer_set is q4b.LAYER_SMALL:
+        words = ctx.to_device(np.zeros(1024, dtype=np.uint32))
+        handles = [None] * world
+        dist.all_gather_object(handles, ctx.ipc_export(words.ptr))
+        peer = ctx.ipc_open(handles[1 - rank]) if rank < 2 else None
+        ctx.sync()
+        dist.barrier()
+        if rank < 2:
+            round_trip_us = ctx.probe_signal(words.ptr, peer, 1024, 200, 0, rank == 0)
+            assert 0.5 < round_trip_us < 200.0, round_trip_us
+        dist.barrier()
+        if rank < 2:
+            ctx.ipc_close(peer)
     ctx.close()
     dist.barrier()
     dist.destroy_process_group()

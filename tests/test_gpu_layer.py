@@ -100,3 +100,38 @@ def test_shapes_of_one_rank_among_many(q4b, orc, world, m, mode):
                 assert np.max(np.abs(got[p.name][:, row:row + 1] - want)) / scale <= 2e-3, (p.name, row, m, mode)
             index += 2 if p.fused else 1
         stack.free()
+
+
+def test_push_rows_and_pushing_decode_launch_on_one_device(q4b, orc):
+    """The two ways a rank's slice reaches the other ranks' copies, with the "peers" played by further buffers
+    of the same GPU: the decode kernel's epilogue storing into them (q4b_context_push_outputs, M <= 16) and the
+    copy kernel (q4b_push_rows); the bytes between the slices stay as they were."""
+    with q4b.Q4Context(0) as ctx:
+        n_total, n_local, begin, k, m = 1024, 256, 384, 2048, 3
+        groups = k // 64
+        quants, meta = orc.synth_weight(5, 0, n_local, groups)
+        weight = ctx.upload(quants, meta, n_local, groups)
+        x = orc.synth_x(5, 0, m, k)
+        dx = ctx.to_device(x)
+        _, ref = orc.matmul(quants, meta, groups, x, want32=False)
+        fill = np.full((m, n_total), 7.0, dtype=np.float16)
+        own, peer_a, peer_b = (ctx.to_device(fill) for _ in range(3))
+        offset = begin * 2
+        ctx.push_outputs(3, [[None, peer_a.ptr + offset, peer_b.ptr + offset]])
+        ctx.matmul(weight, dx.ptr, q4b.F16, m, own.ptr + offset, q4b.F16, n_total)
+        ctx.sync()
+        for buffer in (own, peer_a, peer_b):
+            got = buffer.download(np.float16, (m, n_total))
+            assert_close(got[:, begin:begin + n_local], ref, "pushed by the epilogue")
+            assert (got[:, :begin] == 7.0).all() and (got[:, begin + n_local:] == 7.0).all()
+        # the copy kernel: the own block into two fresh "peers"
+        peer_c, peer_d = (ctx.to_device(fill) for _ in range(2))
+        ctx.push_rows(own.ptr + offset, [peer_c.ptr + offset, peer_d.ptr + offset], m, n_local * 2, n_total * 2)
+        ctx.sync()
+        want = own.download(np.float16, (m, n_total))
+        for buffer in (peer_c, peer_d):
+            got = buffer.download(np.float16, (m, n_total))
+            assert (got.view(np.uint16) == want.view(np.uint16)).all()
+        with pytest.raises(q4b.Q4Error):
+            ctx.push_rows(own.ptr + offset, [peer_c.ptr + offset], m, n_local * 2 + 2, n_total * 2)
+        weight.free()
