@@ -608,7 +608,13 @@ decode_kernel(const __grid_constant__ PassParams p) {
     if (warp == kProducerWarp) {
         // ---- weight producer: one thread streams every unit of every job, never draining the ring ----
         if (lane == 0) {
-            uint32_t it = 0, issued = 0;
+            uint32_t it = 0, issued = 0, slot = 0, lap_parity = 0;
+            auto ring_step = [stages](uint32_t &at, uint32_t &parity) {
+                if (++at == stages) {
+                    at = 0;
+                    parity ^= 1u;
+                }
+            };
             const uint64_t policy = stream_once_policy();
             const bool throttle = p.throttle != 0;
             for (uint32_t j = 0; j < job_count; ++j) {
@@ -631,9 +637,9 @@ decode_kernel(const __grid_constant__ PassParams p) {
                                        (size_t)(job.fused ? u.local : 2 * u.local) * G * kUnitBytes;
                     const uint8_t *b = job.fused ? job.up_tiles + (size_t)u.local * G * kUnitBytes
                                                  : a + (size_t)G * kUnitBytes;
-                    for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
-                        const uint32_t s = it % stages;
-                        if (it >= stages) mbar_wait(empty0 + 8 * s, ((it / stages) - 1) & 1, failed, 0x91u);
+                    for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it, ring_step(slot, lap_parity)) {
+                        const uint32_t s = slot;  // it % stages, and lap_parity = (it / stages) & 1, kept without dividing
+                        if (it >= stages) mbar_wait(empty0 + 8 * s, lap_parity ^ 1u, failed, 0x91u);
                         // A single launch starts before the launch it depends on has finished, and the ring would
                         // fill while the consumers wait for their activations; then their first loads queue behind
                         // a whole ring of weight requests.  The last stage of the first fill waits for the first
@@ -676,7 +682,18 @@ decode_kernel(const __grid_constant__ PassParams p) {
         bool opened = false;         // a single launch: whether this warp has reported its first entries
         uint32_t epoch = 0;
         if (SEQ) epoch = *reinterpret_cast<volatile uint32_t *>(p.epoch) + 1;
-        uint32_t it = 0;
+        // the stage counter, and what it says about the rings, kept without dividing: slot = it % stages with
+        // lap_parity = (it / stages) & 1, entry set e = it % kEntrySets with e_parity = (it / kEntrySets) & 1
+        uint32_t it = 0, slot = 0, lap_parity = 0, e = 0, e_parity = 0;
+        // entry set and lap parity of the stage `ahead` (0..2) stages after the current one
+        auto set_at = [&](uint32_t ahead, uint32_t &index, uint32_t &parity) {
+            index = e + ahead;
+            parity = e_parity;
+            if (index >= kEntrySets) {
+                index -= kEntrySets;
+                parity ^= 1u;
+            }
+        };
         // optional phase clocks: consumer warp 0 stamps its own progress (its lane 0 adds them up at the end)
         const bool stamp = SEQ && p.profile != nullptr && warp == 0 && lane == 0;
         long long *phase = reinterpret_cast<long long *>(xchg + 4 * 32 * F::XCHG_VALS);  // [kProfileSlots], this lane's alone
@@ -698,7 +715,7 @@ decode_kernel(const __grid_constant__ PassParams p) {
         // pairs xfull / xempty, eight arrivals each): a warp busy with a pass delays nobody, there is no barrier
         // among the consumers.
         const uint32_t shift = MODE != 0 ? 2u : m_rows == 1 ? 0u : m_rows == 2 ? 1u : 2u;
-        const uint32_t per_pass = 4u >> shift;
+        const uint32_t per_pass = 4u >> shift, pass_log = 2u - shift;  // groups per pass and their logarithm
         const uint8_t *lane_tiles = ring + (size_t)k * kStageGroups * kUnitBytes + r * kTileBytes;
         // integer form: where this lane reads its B registers and its row's steps inside an entry
         const uint32_t digits_at = ((uint32_t)lane < 8 * m_rows ? (uint32_t)lane : (uint32_t)lane & 7u) * 16u;
@@ -757,19 +774,19 @@ decode_kernel(const __grid_constant__ PassParams p) {
                 // this warp's pass of the stage with counter `counter` (groups from `g`), if it has one: [first, +count)
                 auto my_pass = [&](uint32_t counter, uint32_t g, uint32_t &first, uint32_t &count) {
                     const uint32_t groups_in_stage = min(kStageGroups, u.g1 - g);
-                    const uint32_t passes = (groups_in_stage + per_pass - 1) / per_pass;
-                    const uint32_t mine = ((uint32_t)warp - counter * (kStageGroups / per_pass)) & 7u;
+                    const uint32_t passes = (groups_in_stage + per_pass - 1) >> pass_log;
+                    const uint32_t mine = ((uint32_t)warp - counter * (kStageGroups >> pass_log)) & 7u;
                     first = mine * per_pass;
                     count = mine < passes ? min(per_pass, groups_in_stage - first) : 0u;
                 };
                 uint32_t raw[MODE == 0 ? 8 : 8 * NT];
                 // fetch == true: only send the loads off (fp16 x); false: make the entries from what was fetched
-                auto pass_step = [&](uint32_t counter, uint32_t g, bool fetch) {
-                    uint32_t first, count;
-                    my_pass(counter, g, first, count);
+                auto pass_step = [&](uint32_t ahead, uint32_t g, bool fetch) {  // the stage `ahead` after the current
+                    uint32_t first, count, index, parity;
+                    my_pass(it + ahead, g, first, count);
                     if (count == 0) return;
-                    uint8_t *first_entry = entries + (size_t)(counter % kEntrySets) * kStageGroups * entry_bytes +
-                                           first * entry_bytes;
+                    set_at(ahead, index, parity);
+                    uint8_t *first_entry = entries + (size_t)index * kStageGroups * entry_bytes + first * entry_bytes;
                     if constexpr (MODE == 0) {
                         const Pass pass = pass_of(lane, shift, count, m_rows);
                         if (fetch) {
@@ -785,13 +802,17 @@ decode_kernel(const __grid_constant__ PassParams p) {
                         }
                     }
                 };
-                auto hand_over = [&](uint32_t counter) {  // this warp's part of the stage's entries is in place
+                auto hand_over = [&](uint32_t ahead) {  // this warp's part of that stage's entries is in place
+                    uint32_t index, parity;
+                    set_at(ahead, index, parity);
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(xfull0 + 8 * (counter % kEntrySets));
+                    if (lane == 0) mbar_arrive(xfull0 + 8 * index);
                 };
-                auto wait_set_free = [&](uint32_t counter) {  // the tiles of three stages ago are done with the set
-                    if (counter >= kEntrySets) {
-                        mbar_wait(xempty0 + 8 * (counter % kEntrySets), ((counter / kEntrySets) - 1) & 1, failed, 0x94u);
+                auto wait_set_free = [&](uint32_t ahead) {  // the tiles of three stages before that one are done with the set
+                    if (it + ahead >= kEntrySets) {
+                        uint32_t index, parity;
+                        set_at(ahead, index, parity);
+                        mbar_wait(xempty0 + 8 * index, parity ^ 1u, failed, 0x94u);
                     }
                 };
                 if (!in_stream_order) {
@@ -807,21 +828,21 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     uint32_t first, count;
                     my_pass(it, u.g0, first, count);
                     const bool second = count == 0 && g2 < u.g1;  // no pass in the first stage: maybe in the second
-                    wait_set_free(it);
-                    if (g2 < u.g1) wait_set_free(it + 1);
-                    pass_step(second ? it + 1 : it, second ? g2 : u.g0, true);
-                    pass_step(second ? it + 1 : it, second ? g2 : u.g0, false);
-                    hand_over(it);
-                    if (g2 < u.g1) hand_over(it + 1);
+                    wait_set_free(0);
+                    if (g2 < u.g1) wait_set_free(1);
+                    pass_step(second ? 1u : 0u, second ? g2 : u.g0, true);
+                    pass_step(second ? 1u : 0u, second ? g2 : u.g0, false);
+                    hand_over(0);
+                    if (g2 < u.g1) hand_over(1);
                 } else {
 #pragma unroll
                     for (uint32_t d = 0; d < 2; ++d) {
                         const uint32_t g = u.g0 + d * kStageGroups;
                         if (g < u.g1) {
-                            wait_set_free(it + d);
-                            pass_step(it + d, g, true);
-                            pass_step(it + d, g, false);
-                            hand_over(it + d);
+                            wait_set_free(d);
+                            pass_step(d, g, true);
+                            pass_step(d, g, false);
+                            hand_over(d);
                         }
                     }
                 }
@@ -830,15 +851,26 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     if (lane == 0) mbar_arrive(opened0);
                 }
                 lap(kProfileEntries);
-                for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, ++it) {
-                    const uint32_t s = it % stages;
+                auto next_stage = [&]() {
+                    ++it;
+                    if (++slot == stages) {
+                        slot = 0;
+                        lap_parity ^= 1u;
+                    }
+                    if (++e == kEntrySets) {
+                        e = 0;
+                        e_parity ^= 1u;
+                    }
+                };
+                for (uint32_t g = u.g0; g < u.g1; g += kStageGroups, next_stage()) {
+                    const uint32_t s = slot;
                     const uint32_t in_stage = min(kStageGroups, u.g1 - g);
-                    const uint8_t *set = entries + (size_t)(it % kEntrySets) * kStageGroups * entry_bytes;
+                    const uint8_t *set = entries + (size_t)e * kStageGroups * entry_bytes;
                     const uint32_t g_ahead = g + 2 * kStageGroups;
-                    if (g_ahead < u.g1) pass_step(it + 2, g_ahead, true);  // loads first: they pass under the tiles
-                    mbar_wait(xfull0 + 8 * (it % kEntrySets), (it / kEntrySets) & 1, failed, 0x93u);
+                    if (g_ahead < u.g1) pass_step(2, g_ahead, true);  // loads first: they pass under the tiles
+                    mbar_wait(xfull0 + 8 * e, e_parity, failed, 0x93u);
                     lap(kProfileEntries);
-                    mbar_wait(full0 + 8 * s, (it / stages) & 1, failed, 0x92u);
+                    mbar_wait(full0 + 8 * s, lap_parity, failed, 0x92u);
                     lap(kProfileWeights);
                     if (active) {
                         const uint8_t *tiles = lane_tiles + s * kStageBytes;
@@ -863,14 +895,14 @@ decode_kernel(const __grid_constant__ PassParams p) {
                     }
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(xempty0 + 8 * (it % kEntrySets));
+                        mbar_arrive(xempty0 + 8 * e);
                         mbar_arrive(empty0 + 8 * s);
                     }
                     lap(kProfileTiles);
                     if (g_ahead < u.g1) {
-                        wait_set_free(it + 2);
-                        pass_step(it + 2, g_ahead, false);
-                        hand_over(it + 2);
+                        wait_set_free(2);
+                        pass_step(2, g_ahead, false);
+                        hand_over(2);
                         lap(kProfileEntries);
                     }
                 }
