@@ -28,7 +28,7 @@ from .layer import Q4Layer, slice_of
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on the 27B gate/up pair at M = 1
-NCU_GATE_UP_TRAFFIC_BYTES = 103.9e6
+NCU_GATE_UP_TRAFFIC_BYTES = 103.8e6
 
 
 class ShardedLayerStack:
