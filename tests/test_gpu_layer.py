@@ -135,3 +135,34 @@ def test_push_rows_and_pushing_decode_launch_on_one_device(q4b, orc):
         with pytest.raises(q4b.Q4Error):
             ctx.push_rows(own.ptr + offset, [peer_c.ptr + offset], m, n_local * 2 + 2, n_total * 2)
         weight.free()
+
+
+def test_recorded_barrier_counts_on_at_every_replay(q4b, orc):
+    """A barrier's round lives in device memory: recorded into a graph between two launches it passes at every
+    replay (a one-rank barrier meets itself), and a barrier queued afterwards outside the graph still agrees with
+    the count."""
+    with q4b.Q4Context(0) as ctx:
+        n, k, m = 512, 1024, 2
+        quants, meta = orc.synth_weight(9, 0, n, k // 64)
+        weight = ctx.upload(quants, meta, n, k // 64)
+        x = orc.synth_x(9, 0, m, k)
+        dx = ctx.to_device(x)
+        dy = ctx.alloc(m * n * 2)
+        barrier = q4b.Q4Barrier(ctx, 1, 0)
+        ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)  # once outside: attributes and scratch
+        barrier.queue()
+        ctx.sync()
+        ctx.graph_begin()
+        for _ in range(3):
+            ctx.matmul(weight, dx.ptr, q4b.F16, m, dy.ptr)
+            barrier.queue()
+        graph = ctx.graph_end()
+        for _ in range(4):
+            graph.launch()
+        barrier.queue()
+        ctx.sync()  # a barrier that lost count would run into its bounded wait: status 2 here
+        _, ref = orc.matmul(quants, meta, k // 64, x, want32=False)
+        assert_close(dy.download(np.float16, (m, n)), ref, "after the replays")
+        graph.free()
+        barrier.free()
+        weight.free()
