@@ -1,6 +1,6 @@
 // C ABI of libq4b200 (declared in include/q4b200.h): contexts, the weight-image
 // loader, matmul dispatch, completion/timing and graph replay.  Host code only;
-// the kernels live in q4b_pack.cu, q4b_gemv.cu and q4b_gemm.cu.
+// the kernels live in q4b_pack.cu, q4b_decode.cu and q4b_gemm.cu.
 #include "../../include/q4b200.h"
 #include "q4b_kernels.h"
 

@@ -694,7 +694,7 @@ cudaError_t launch_tc_instance(TcParams &p, const TcGemmArgs &args, int sm_count
         if (slot >= 0) configured[slot] = true;
     }
     unsigned grid = tiles < (uint32_t)sm_count ? tiles : (unsigned)sm_count;
-    // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last round
+    // Few tiles for many SMs: whole tiles would leave SMs idle (80 tiles on 148 SMs) or a thin last wave
     // (160 on 148).  The iterations can be split evenly over any number of CTAs instead.  In units of one
     // group's MMAs a CTA then works through iterations / CTAs, and a tile that is cut costs about 48 for leaving
     // and adding the first partial tile plus 25 for every further part, which its owner adds one after the
