@@ -192,12 +192,15 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, world):
+def workload_config(args, world, mode=None):
+    how = {"graph": "every launch stores its slice into all ranks' outputs, a barrier between the ranks after it, "
+                    "the pass replayed from a graph",
+           "sequence": "one persistent launch per pass whose epilogue stores into all ranks' outputs"}
+    gather = "NCCL all-gather per projection" if args.gather == "nccl" else how.get(mode, args.gather)
     return {"workload": f"27B-shape Q4 layer set (q,k,v,o,gate+up SiLU,down) x {LAYERS} layers, M={args.m}, "
                         f"seed=layer index",
             "m_rows": args.m, "layers": LAYERS, "group": 64,
-            "parallelism": ("single GPU" if world == 1 else
-                            f"column-parallel N/{world} + all-gather ({args.gather})"),
+            "parallelism": ("single GPU" if world == 1 else f"column-parallel N/{world}: {gather}"),
             "l2": "inputs_exceed_l2 (12.27 GB of distinct weights per step)"}
 
 
@@ -430,7 +433,7 @@ def run_ours(args):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": warmup, "repeats": repeats, "timed_region_ms": device_ms, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4*f16->f32",
-                "data": "synthetic", "config": workload_config(args, world), "roofline": roofline, "e2e": e2e,
+                "data": "synthetic", "config": workload_config(args, world, mode), "roofline": roofline, "e2e": e2e,
                 "gpu_launches": launches, "clocks": clocks, "parity_max_rel_err": worst,
                 "parity": {**parity, "tolerance": TOLERANCE,
                            "how": "every rank, sampled weight rows of layers 0 and 63 (first and last rows of the "
@@ -642,8 +645,9 @@ def sharded_prefill(q4b, sharded, orc, ctx, rank, world, dist, peaks, barrier, m
     barrier()
     stack.free()
     return [{"m_rows": m, "ms_per_layer": ms, "tflops": tflops,
-             "gather": ("slices stored into every rank's output by the GEMM epilogue + rank barrier" if gather == "push"
-                        else "nccl all-gather per projection"),
+             "gather": ("nccl all-gather per projection" if gather != "push" else
+                        "slices stored into every rank's output by the GEMM epilogue + rank barrier" if world <= 2 else
+                        "slices copied into every rank's output by a copy kernel after the GEMM + rank barrier"),
              "frac_of_measured_bf16_burst_per_gpu": tflops / world / peaks["bf16_tflops"]}]
 
 
