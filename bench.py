@@ -370,13 +370,20 @@ def run_ours(args):
            "h2d_bytes_per_step": model.h2d_bytes_per_step, "d2h_bytes_per_step": model.d2h_bytes_per_step,
            "ms_per_step": e2e_ms, "steps": e2e_steps}
 
-    # ---- every launch group alone over the 64 layers' distinct weights (one launch per layer, graph-free) ----
+    # ---- every launch group alone over the 64 layers' distinct weights: one launch per layer, the 64 launches
+    # replayed from a graph like the whole pass (issued one by one from Python the short ones would wait for the host)
     per_projection = {}
     for kind, members in model.layers[0].launch_plan():
         name = members[0].name
         model.projection_pass(name)
-        reps = 5
-        ms = timed_steps(ctx, barrier, max_over_ranks, lambda: model.projection_pass(name), reps) / (reps * LAYERS)
+        ctx.sync()
+        ctx.graph_begin()
+        model.projection_pass(name)
+        chain = ctx.graph_end()
+        chain.launch()
+        reps = 10
+        ms = timed_steps(ctx, barrier, max_over_ranks, chain.launch, reps) / (reps * LAYERS)
+        chain.free()
         nbytes = sum(q4b.algorithmic_bytes(p, args.m) for p in members) / world
         per_projection["+".join(p.name for p in members)] = {
             "us_per_launch": ms * 1e3, "algorithmic_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
